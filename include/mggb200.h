@@ -1,0 +1,177 @@
+/* mggb200.h - C ABI of the B200-native MGG hot path (libmggb200.so).
+ *
+ * Every entry point replaces one piece of the reference's operator surface; the comment above each
+ * declaration names the reference interface it stands in for (paths relative to the reference
+ * project's root).  Conventions:
+ *   - plain pointers and sizes only; no C++ or framework types cross this boundary;
+ *   - every function returns an int status (MGGB_OK == 0); nothing exits or throws.  The reference
+ *     instead prints and calls exit(-1) on a CUDA error (include/neighbor_utils.cuh:836-840) and
+ *     validates nothing; mggb_last_error() returns the message of the calling thread's last failure;
+ *   - the caller owns every buffer; the library keeps no pointer after a call returns;
+ *   - device work is enqueued on the given stream (a cudaStream_t passed as void*, NULL = default
+ *     stream) of the CURRENT device and is NOT synchronised (the reference synchronises the device
+ *     after every launch, include/neighbor_utils.cuh:835);
+ *   - node ids are int32 (the reference's nidType, include/neighbor_utils.cuh:15); element offsets
+ *     into embedding buffers are computed in 64 bits.
+ */
+#ifndef MGGB200_H
+#define MGGB200_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    MGGB_OK = 0,
+    MGGB_ERR_INVALID_ARG = 1, /* bad size, NULL pointer, unsupported knob value */
+    MGGB_ERR_CUDA = 2,        /* a CUDA runtime call or launch failed */
+    MGGB_ERR_UNSUPPORTED = 3, /* valid request that this build cannot serve */
+    MGGB_ERR_PEER = 4,        /* peer access / IPC mapping unavailable between two devices */
+    MGGB_ERR_IO = 5           /* file missing, short or inconsistent */
+};
+
+/* Flags of the aggregation entry points. */
+enum {
+    MGGB_AGG_ACCUMULATE = 1 /* out += sum (what the reference does, include/neighbor_utils.cuh:1456-1458);
+                               without it out = sum, which needs no zero-fill between passes */
+};
+
+/* Flags of mggb_dense_forward. */
+enum {
+    MGGB_DENSE_RELU = 1,      /* clamp the result at 0 (the reference's timed path has no activation) */
+    MGGB_DENSE_TF32 = 2,      /* single-pass TF32 tensor-core product (about 1e-3 relative) */
+    MGGB_DENSE_SIMT = 4       /* force the fp32 CUDA-core kernel */
+};
+
+#define MGGB_MAX_PES 16
+
+/* Library version (major*10000 + minor*100 + patch). */
+int mggb_version(void);
+/* Message of the calling thread's most recent failing call ("" if none). */
+const char* mggb_last_error(void);
+
+/* ---- node-range shard ------------------------------------------------------------------------
+ * Replaces the inline arithmetic of src/mgg_np_div_mem.cu:85-88:
+ * nodes_per_pe = ceil(N/G), lb = pe*nodes_per_pe, ub = min(lb+nodes_per_pe, N). */
+int mggb_shard_range(int64_t num_nodes, int num_pes, int pe,
+                     int64_t* nodes_per_pe, int64_t* lb, int64_t* ub);
+
+/* ---- partitioner (host, parallel) ---------------------------------------------------------------
+ * Replaces split_CSR<T> (include/neighbor_utils.cuh:381-405).  For rows [lb,ub) of the global CSR,
+ * each neighbor list is split, order preserved, into ids inside [lb,ub) (local) and the rest
+ * (remote); ids stay global; both pointer arrays start at 0 and have ub-lb+1 entries.
+ * Two calls: _count returns the two column counts, _fill writes into caller buffers of those sizes.
+ * The _i64 forms take 64-bit global row pointers (graphs whose edge count exceeds 2^31); the
+ * shard-local pointer arrays stay int32 and _count fails with MGGB_ERR_UNSUPPORTED if a shard's
+ * half would not fit. */
+int mggb_split_csr_count(const int32_t* row_ptr, const int32_t* col_idx, int32_t lb, int32_t ub,
+                         int64_t* n_local, int64_t* n_remote);
+int mggb_split_csr_fill(const int32_t* row_ptr, const int32_t* col_idx, int32_t lb, int32_t ub,
+                        int32_t* local_ptr, int32_t* remote_ptr,
+                        int32_t* local_col, int32_t* remote_col);
+int mggb_split_csr_count_i64(const int64_t* row_ptr, const int32_t* col_idx, int32_t lb, int32_t ub,
+                             int64_t* n_local, int64_t* n_remote);
+int mggb_split_csr_fill_i64(const int64_t* row_ptr, const int32_t* col_idx, int32_t lb, int32_t ub,
+                            int32_t* local_ptr, int32_t* remote_ptr,
+                            int32_t* local_col, int32_t* remote_col);
+
+/* Replaces build_part<T> (include/neighbor_utils.cuh:411-460): explicit neighbor partitions of at
+ * most part_size edges.  part_ptr has P+1 entries, part2node P, node2part num_nodes+2 (the
+ * reference appends the total twice, :420-429).  With exact_sentinel == 0 the closing entry
+ * part_ptr[P] reproduces the reference bit for bit, including its corner case (:453-454): when the
+ * last node has no edges the sentinel is left 0.  exact_sentinel != 0 always writes indptr[num_nodes].
+ * The reference also prints one line per call (:457-458); this function prints nothing. */
+int mggb_build_part_count(const int32_t* indptr, int32_t num_nodes, int32_t part_size,
+                          int64_t* num_parts);
+int mggb_build_part_fill(const int32_t* indptr, int32_t num_nodes, int32_t part_size,
+                         int exact_sentinel,
+                         int32_t* part_ptr, int32_t* part2node, int32_t* node2part);
+
+/* ---- symmetric (peer-readable) buffers ----------------------------------------------------------
+ * Replace nvshmem_malloc (src/mgg_np_div_mem.cu:139; include/layer_new.cuh:314) and the address
+ * translation hidden inside nvshmemx_float_get_warp (include/neighbor_utils.cuh:1445).  A symmetric
+ * buffer is an ordinary device allocation of the same size on every PE; what makes it symmetric is
+ * that every PE holds a table of all PEs' base pointers and hands it to the aggregation call.
+ *   one process, several devices: mggb_enable_peer_access(a, b) once per ordered pair, then use
+ *       the owners' pointers directly;
+ *   one process per device: the owner exports a 64-byte handle, the other processes import it
+ *       (CUDA IPC) and get a pointer valid in their own address space. */
+int mggb_sym_alloc(size_t bytes, void** dev_ptr);            /* on the current device; zero-filled */
+int mggb_sym_free(void* dev_ptr);
+int mggb_sym_export(void* dev_ptr, unsigned char handle_out[64]);
+int mggb_sym_import(const unsigned char handle[64], void** peer_ptr); /* maps a peer's buffer */
+int mggb_sym_close(void* peer_ptr);                          /* unmaps an imported buffer */
+int mggb_enable_peer_access(int device, int peer_device);    /* MGGB_ERR_PEER if impossible */
+
+/* ---- neighbor aggregation ----------------------------------------------------------------------
+ * Replaces mgg_SAG_np_div (launcher include/neighbor_utils.cuh:787-841, kernel :1351-1460).
+ *   output      [ub-lb, dim] on this device (may itself be a symmetric buffer)
+ *   peer_input  HOST array of num_pes device pointers: PE p's symmetric embedding buffer
+ *               [node_per_pe, dim] as addressable from this device; peer_input[pe] is this PE's own
+ *               (the reference passes only the local address and lets NVSHMEM translate it)
+ *   row_ptr_l/col_idx_l, row_ptr_r/col_idx_r  the split CSR of this shard, on this device
+ *   part_size, warp_per_block, interleaved_dist  the reference's ps / wpb / dist knobs: one thread
+ *               block of warp_per_block warps per node, each warp taking interleaved_dist*part_size
+ *               consecutive neighbors per turn, local list first, then remote (:1395-1400, :1432-1437)
+ *   row_scale   NULL, or [ub-lb] factors applied to each output row before it is stored (used for
+ *               symmetric normalisation; not in the reference)
+ *   flags       MGGB_AGG_*
+ * Results do not depend on ps/wpb/dist except through fp32 summation order; for fixed knobs they
+ * are bit-reproducible (one writer per output row, no atomics). */
+int mggb_sag_np_div(float* output, const float* const* peer_input, int num_pes,
+                    const int32_t* row_ptr_l, const int32_t* col_idx_l,
+                    const int32_t* row_ptr_r, const int32_t* col_idx_r,
+                    int32_t lb, int32_t ub, int dim, int32_t node_per_pe, int pe,
+                    int part_size, int warp_per_block, int interleaved_dist,
+                    const float* row_scale, int flags, void* stream);
+
+/* Replaces mgg_GIN_np_div (launcher include/neighbor_utils.cuh:902-958, kernel :1554-1667):
+ * output[b,:] = (1+eps) * x_self[b,:] + sum, where x_self is this PE's own symmetric buffer
+ * (:1660-1665).  The output row is written once, so output must not alias peer_input[pe]. */
+int mggb_gin_np_div(float* output, const float* const* peer_input, int num_pes,
+                    const int32_t* row_ptr_l, const int32_t* col_idx_l,
+                    const int32_t* row_ptr_r, const int32_t* col_idx_r,
+                    int32_t lb, int32_t ub, int dim, int32_t node_per_pe, int pe,
+                    int part_size, int warp_per_block, int interleaved_dist,
+                    float eps, int flags, void* stream);
+
+/* ---- dense node update and softmax ---------------------------------------------------------------
+ * Replaces dense_beg_new_forward / dense_hidden_new_forward (include/gnn_layer.cuh:42-52) on the
+ * parameter structs of include/layer_new.cuh:272-393: row-major out[n, dim2] = x[n, dim1] * w[dim1, dim2],
+ * alpha = 1, beta = 0, no bias.  The reference's call passes d_out as the B operand and never reads
+ * d_in; this function computes the intended product from x.  row_scale (NULL or [n]) multiplies
+ * output row i.  Precision: fp32-equivalent by default (3-pass split on the tensor cores, or the
+ * CUDA-core kernel); MGGB_DENSE_TF32 selects one TF32 pass. */
+int mggb_dense_forward(float* out, const float* x, const float* w,
+                       int64_t n, int dim1, int dim2,
+                       const float* row_scale, int flags, void* stream);
+
+/* Replaces softmax_new_forward (include/gnn_layer.cuh:36-40; descriptors include/layer_new.cuh:80-85):
+ * max-subtracted softmax over the dim classes of each row; in and out may alias. */
+int mggb_softmax_forward(float* out, const float* in, int64_t n, int dim, void* stream);
+
+/* out[i,:] = scale[i] * in[i,:] (in and out may alias); scale[i] = 1/sqrt(row_ptr[i+1]-row_ptr[i]),
+ * 0 for empty rows.  Helpers for symmetric normalisation; no counterpart in the reference, whose
+ * aggregation is an unnormalised sum. */
+int mggb_row_scale(float* out, const float* in, const float* scale, int64_t n, int dim, void* stream);
+int mggb_inv_sqrt_degree(float* scale, const int32_t* row_ptr_l, const int32_t* row_ptr_r,
+                         int64_t n, void* stream);
+
+/* ---- binary CSR files ---------------------------------------------------------------------------
+ * Replaces the loader graph<long,long,int,int,int,int> (include/graph.hpp:9-129): <name>_beg_pos.bin
+ * holds N+1 int64 offsets, <name>_csr.bin E int64 neighbor ids, <name>_weight.bin E int32 weights
+ * (read by the reference, never used).  _info returns the counts; _load narrows ids to int32 into
+ * caller buffers (row_ptr64 N+1 entries, col_idx E entries); weights are not read. */
+int mggb_graph_file_info(const char* beg_file, const char* csr_file, int64_t* num_nodes, int64_t* num_edges);
+int mggb_graph_file_load(const char* beg_file, const char* csr_file, int64_t num_nodes, int64_t num_edges,
+                         int64_t* row_ptr64, int32_t* col_idx);
+int mggb_graph_file_write(const char* beg_file, const char* csr_file, const char* weight_file,
+                          const int64_t* row_ptr64, const int32_t* col_idx, int64_t num_nodes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MGGB200_H */

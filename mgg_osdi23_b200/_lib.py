@@ -1,0 +1,79 @@
+"""ctypes binding of ``libmggb200.so``.
+
+The library is the only compute path of this package: if it is missing or fails to load, importing
+this module raises - there is no Python or CPU substitute behind it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "libmggb200.so")
+
+OK, ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_PEER, ERR_IO = range(6)
+AGG_ACCUMULATE = 1
+DENSE_RELU, DENSE_TF32, DENSE_SIMT = 1, 2, 4
+MAX_PES = 16
+
+
+class MggbError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"mggb status {code}: {msg}")
+        self.code = code
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m mgg_osdi23_b200.build` "
+            "(nvcc, sm_100a). This package has no fallback path.")
+    return C.CDLL(LIB_PATH)
+
+
+lib = _load()
+
+_vp, _i32, _i64, _int, _f = C.c_void_p, C.c_int32, C.c_int64, C.c_int, C.c_float
+_pi64 = C.POINTER(C.c_int64)
+
+# name -> argtypes; every function returns int status unless noted.
+SIGNATURES = {
+    "mggb_shard_range": [_i64, _int, _int, _pi64, _pi64, _pi64],
+    "mggb_split_csr_count": [_vp, _vp, _i32, _i32, _pi64, _pi64],
+    "mggb_split_csr_fill": [_vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp],
+    "mggb_split_csr_count_i64": [_vp, _vp, _i32, _i32, _pi64, _pi64],
+    "mggb_split_csr_fill_i64": [_vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp],
+    "mggb_build_part_count": [_vp, _i32, _i32, _pi64],
+    "mggb_build_part_fill": [_vp, _i32, _i32, _int, _vp, _vp, _vp],
+    "mggb_sym_alloc": [C.c_size_t, C.POINTER(_vp)],
+    "mggb_sym_free": [_vp],
+    "mggb_sym_export": [_vp, C.c_char_p],
+    "mggb_sym_import": [C.c_char_p, C.POINTER(_vp)],
+    "mggb_sym_close": [_vp],
+    "mggb_enable_peer_access": [_int, _int],
+    "mggb_sag_np_div": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
+                        _int, _int, _int, _vp, _int, _vp],
+    "mggb_gin_np_div": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
+                        _int, _int, _int, _f, _int, _vp],
+    "mggb_dense_forward": [_vp, _vp, _vp, _i64, _int, _int, _vp, _int, _vp],
+    "mggb_softmax_forward": [_vp, _vp, _i64, _int, _vp],
+    "mggb_row_scale": [_vp, _vp, _vp, _i64, _int, _vp],
+    "mggb_inv_sqrt_degree": [_vp, _vp, _vp, _i64, _vp],
+    "mggb_graph_file_info": [C.c_char_p, C.c_char_p, _pi64, _pi64],
+    "mggb_graph_file_load": [C.c_char_p, C.c_char_p, _i64, _i64, _vp, _vp],
+    "mggb_graph_file_write": [C.c_char_p, C.c_char_p, C.c_char_p, _vp, _vp, _i64],
+}
+
+for _name, _args in SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.argtypes = _args
+    _fn.restype = C.c_int
+lib.mggb_version.restype = C.c_int
+lib.mggb_last_error.restype = C.c_char_p
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise MggbError(status, lib.mggb_last_error().decode(errors="replace"))

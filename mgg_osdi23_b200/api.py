@@ -1,0 +1,250 @@
+"""Host-side mirror of the reference's operator surface, on top of the C ABI.
+
+Names, argument order and meaning follow the reference's header-defined functions and structs:
+
+=============================  ==============================================================
+here                           reference
+=============================  ==============================================================
+``split_CSR``                  ``include/neighbor_utils.cuh:381-405``
+``build_part``                 ``include/neighbor_utils.cuh:411-460``
+``mgg_SAG_np_div``             ``include/neighbor_utils.cuh:787-841``
+``mgg_GIN_np_div``             ``include/neighbor_utils.cuh:902-958``
+``dense_param_new_beg`` etc.   ``include/layer_new.cuh:59-103, 272-393``
+``dense_*_new_forward`` etc.   ``include/gnn_layer.cuh:36-52``
+=============================  ==============================================================
+
+Device buffers are torch CUDA tensors (torch is used for memory and streams only); host arrays are
+numpy.  Work is enqueued on torch's current stream and not synchronised.  There is no CPU path:
+every compute function needs a CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import lib, check
+
+__all__ = [
+    "shard_range", "split_CSR", "build_part", "mgg_SAG_np_div", "mgg_GIN_np_div",
+    "dense_param_new_beg", "dense_param_new_hidden", "softmax_new_param",
+    "dense_beg_new_forward", "dense_hidden_new_forward", "softmax_new_forward",
+    "dense_forward", "softmax_forward", "row_scale", "inv_sqrt_degree",
+]
+
+
+# ---- helpers ------------------------------------------------------------------------------------
+
+def _np_ptr(a: np.ndarray | None):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _dev_ptr(t: torch.Tensor | None, dtype=None, name="tensor"):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (this package has no CPU compute path)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _peer_table(input_) -> tuple:
+    """Accepts a plain tensor (single PE), a sequence of tensors / raw pointers (one per PE), or an
+    object with a ``peer_ptrs`` attribute (see symmem.SymmetricBuffer)."""
+    if isinstance(input_, torch.Tensor):
+        _dev_ptr(input_, torch.float32, "input")
+        ptrs = [input_.data_ptr()]
+    elif hasattr(input_, "peer_ptrs"):
+        ptrs = list(input_.peer_ptrs)
+    else:
+        ptrs = [p.data_ptr() if isinstance(p, torch.Tensor) else int(p) for p in input_]
+    return (C.c_void_p * len(ptrs))(*ptrs), len(ptrs)
+
+
+# ---- partitioner --------------------------------------------------------------------------------
+
+def shard_range(num_nodes: int, num_gpus: int, pe: int):
+    """(nodesPerPE, lb, ub) of PE ``pe``: ``src/mgg_np_div_mem.cu:85-88``."""
+    a, b, c = C.c_int64(), C.c_int64(), C.c_int64()
+    check(lib.mggb_shard_range(num_nodes, num_gpus, pe, C.byref(a), C.byref(b), C.byref(c)))
+    return a.value, b.value, c.value
+
+
+def split_CSR(origin_ptr, origin_col_idx, lb: int, ub: int):
+    """Returns ``[local_ptr, remote_ptr, local_col_idx, remote_col_idx]`` (int32 numpy arrays), in the
+    reference's order.  ``origin_ptr`` may be int32 or int64."""
+    ptr = np.ascontiguousarray(origin_ptr)
+    if ptr.dtype not in (np.int32, np.int64):
+        ptr = ptr.astype(np.int64)
+    col = np.ascontiguousarray(origin_col_idx, dtype=np.int32)
+    if ub > len(ptr) - 1:
+        raise ValueError(f"ub={ub} exceeds the {len(ptr) - 1} rows of the graph")
+    wide = ptr.dtype == np.int64
+    count = lib.mggb_split_csr_count_i64 if wide else lib.mggb_split_csr_count
+    fill = lib.mggb_split_csr_fill_i64 if wide else lib.mggb_split_csr_fill
+    nl, nr = C.c_int64(), C.c_int64()
+    check(count(_np_ptr(ptr), _np_ptr(col), lb, ub, C.byref(nl), C.byref(nr)))
+    local_ptr = np.empty(ub - lb + 1, np.int32)
+    remote_ptr = np.empty(ub - lb + 1, np.int32)
+    local_col = np.empty(nl.value, np.int32)
+    remote_col = np.empty(nr.value, np.int32)
+    check(fill(_np_ptr(ptr), _np_ptr(col), lb, ub, _np_ptr(local_ptr), _np_ptr(remote_ptr),
+               _np_ptr(local_col), _np_ptr(remote_col)))
+    return [local_ptr, remote_ptr, local_col, remote_col]
+
+
+def build_part(name: str, indptr, num_nodes: int, partSize: int, exact_sentinel: bool = False):
+    """Returns ``[partPtr, part2Node, node2Part]`` exactly as the reference does (``node2Part`` has
+    num_nodes+2 entries; the closing ``partPtr`` entry is 0 when the last node has no edges unless
+    ``exact_sentinel``).  ``name`` is accepted for signature parity; nothing is printed."""
+    del name
+    indptr = np.ascontiguousarray(indptr, dtype=np.int32)
+    if len(indptr) < num_nodes + 1:
+        raise ValueError("indptr shorter than num_nodes+1")
+    n = C.c_int64()
+    check(lib.mggb_build_part_count(_np_ptr(indptr), num_nodes, partSize, C.byref(n)))
+    part_ptr = np.empty(n.value + 1, np.int32)
+    part2node = np.empty(n.value, np.int32)
+    node2part = np.empty(num_nodes + 2, np.int32)
+    check(lib.mggb_build_part_fill(_np_ptr(indptr), num_nodes, partSize, int(exact_sentinel),
+                                   _np_ptr(part_ptr), _np_ptr(part2node), _np_ptr(node2part)))
+    return [part_ptr, part2node, node2part]
+
+
+# ---- aggregation --------------------------------------------------------------------------------
+
+def mgg_SAG_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r, column_index_r,
+                   lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist,
+                   *, accumulate: bool = True, row_scale_: torch.Tensor | None = None):
+    """``output[b,:] (+)= sum of the local and remote neighbors' rows`` for the shard ``[lb, ub)``.
+
+    ``input`` is this PE's symmetric embedding buffer: a tensor when there is one PE, otherwise the
+    table of all PEs' buffers (see ``_peer_table``).  ``accumulate=True`` is the reference's
+    behaviour (it adds on top of ``output``'s contents)."""
+    table, num_pes = _peer_table(input)
+    check(lib.mggb_sag_np_div(
+        _dev_ptr(output, torch.float32, "output"), table, num_pes,
+        _dev_ptr(row_pointers_l, torch.int32, "row_pointers_l"), _dev_ptr(column_index_l, torch.int32, "column_index_l"),
+        _dev_ptr(row_pointers_r, torch.int32, "row_pointers_r"), _dev_ptr(column_index_r, torch.int32, "column_index_r"),
+        lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist,
+        _dev_ptr(row_scale_, torch.float32, "row_scale"), _lib.AGG_ACCUMULATE if accumulate else 0, _stream()))
+
+
+def mgg_GIN_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r, column_index_r,
+                   lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist, eps):
+    """``output[b,:] = (1+eps) * input_self[b,:] + sum`` (``include/neighbor_utils.cuh:1660-1665``)."""
+    table, num_pes = _peer_table(input)
+    check(lib.mggb_gin_np_div(
+        _dev_ptr(output, torch.float32, "output"), table, num_pes,
+        _dev_ptr(row_pointers_l, torch.int32, "row_pointers_l"), _dev_ptr(column_index_l, torch.int32, "column_index_l"),
+        _dev_ptr(row_pointers_r, torch.int32, "row_pointers_r"), _dev_ptr(column_index_r, torch.int32, "column_index_r"),
+        lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist, float(eps), 0, _stream()))
+
+
+# ---- dense update and softmax ---------------------------------------------------------------------
+
+def dense_forward(out, x, w, row_scale_=None, relu=False, flags=0):
+    n, dim1 = x.shape
+    dim2 = w.shape[1]
+    if w.shape[0] != dim1 or tuple(out.shape) != (n, dim2):
+        raise ValueError(f"shape mismatch: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    check(lib.mggb_dense_forward(_dev_ptr(out, torch.float32, "out"), _dev_ptr(x, torch.float32, "x"),
+                                 _dev_ptr(w, torch.float32, "w"), n, dim1, dim2,
+                                 _dev_ptr(row_scale_, torch.float32, "row_scale"),
+                                 flags | (_lib.DENSE_RELU if relu else 0), _stream()))
+
+
+def softmax_forward(out, inp):
+    n, dim = inp.shape
+    check(lib.mggb_softmax_forward(_dev_ptr(out, torch.float32, "out"), _dev_ptr(inp, torch.float32, "in"),
+                                   n, dim, _stream()))
+
+
+def row_scale(out, inp, scale):
+    n, dim = inp.shape
+    check(lib.mggb_row_scale(_dev_ptr(out, torch.float32, "out"), _dev_ptr(inp, torch.float32, "in"),
+                             _dev_ptr(scale, torch.float32, "scale"), n, dim, _stream()))
+
+
+def inv_sqrt_degree(scale, row_ptr_l, row_ptr_r=None):
+    n = scale.numel()
+    check(lib.mggb_inv_sqrt_degree(_dev_ptr(scale, torch.float32, "scale"), _dev_ptr(row_ptr_l, torch.int32, "row_ptr_l"),
+                                   _dev_ptr(row_ptr_r, torch.int32, "row_ptr_r"), n, _stream()))
+
+
+class _dense_param:
+    """Common part of the reference's dense parameter structs: the caller supplies ``d_in`` and
+    ``d_out`` (``[numNodes, dim1]`` and ``[numNodes, dim2]`` views are taken of them); the struct owns
+    ``d_W`` ``[dim1, dim2]``, filled with 1.0 as in the reference (``include/layer_new.cuh:307``).
+    ``set_weight`` uploads other values (the reference has no such entry point)."""
+
+    def __init__(self, name_in: str, d_in_ext: torch.Tensor, d_out_ext: torch.Tensor, numNodes_in: int,
+                 dim1_in: int, dim2_in: int):
+        self.name = name_in[:8]
+        self.numNodes, self.dim1, self.dim2 = numNodes_in, dim1_in, dim2_in
+        self.m, self.n, self.k = dim2_in, numNodes_in, dim1_in
+        self.ldx, self.ldw, self.ldout = dim1_in, dim2_in, dim2_in
+        self.alpha, self.beta = 1.0, 0.0
+        self.d_in, self.d_out = d_in_ext, d_out_ext
+        if d_in_ext.numel() < numNodes_in * dim1_in or d_out_ext.numel() < numNodes_in * dim2_in:
+            raise ValueError("d_in / d_out smaller than numNodes*dim1 / numNodes*dim2 floats")
+        self.d_W = torch.ones(dim1_in, dim2_in, dtype=torch.float32, device=d_in_ext.device)
+        self.row_scale = None
+        self.relu = False
+        self.flags = 0
+
+    def set_weight(self, w: torch.Tensor):
+        if tuple(w.shape) != (self.dim1, self.dim2):
+            raise ValueError(f"weight must be [{self.dim1}, {self.dim2}]")
+        self.d_W.copy_(w)
+
+    def _forward(self):
+        x = self.d_in.reshape(-1)[: self.numNodes * self.dim1].view(self.numNodes, self.dim1)
+        o = self.d_out.reshape(-1)[: self.numNodes * self.dim2].view(self.numNodes, self.dim2)
+        dense_forward(o, x, self.d_W, self.row_scale, self.relu, self.flags)
+
+
+class dense_param_new_beg(_dense_param):
+    """``include/layer_new.cuh:272-333``."""
+
+
+class dense_param_new_hidden(_dense_param):
+    """``include/layer_new.cuh:336-393``."""
+
+
+class softmax_new_param:
+    """``include/layer_new.cuh:59-103``: row softmax of ``d_in`` ``[numNodes, dim]`` into ``d_out``."""
+
+    def __init__(self, name_in: str, d_in_input: torch.Tensor, d_out_ext: torch.Tensor, numNodes_in: int, dim_in: int):
+        self.name = name_in[:8]
+        self.numNodes, self.dim = numNodes_in, dim_in
+        self.d_in, self.d_out = d_in_input, d_out_ext
+        self.alpha, self.beta = 1.0, 0.0
+
+
+def dense_beg_new_forward(dp: dense_param_new_beg):
+    """``include/gnn_layer.cuh:42-46``.  Computes d_out = d_in * d_W (the reference's call passes d_out
+    as the right-hand operand and never reads d_in; the intended product is computed here)."""
+    dp._forward()
+
+
+def dense_hidden_new_forward(dp: dense_param_new_hidden):
+    """``include/gnn_layer.cuh:48-52``."""
+    dp._forward()
+
+
+def softmax_new_forward(smx: softmax_new_param):
+    """``include/gnn_layer.cuh:36-40``."""
+    i = smx.d_in.reshape(-1)[: smx.numNodes * smx.dim].view(smx.numNodes, smx.dim)
+    o = smx.d_out.reshape(-1)[: smx.numNodes * smx.dim].view(smx.numNodes, smx.dim)
+    softmax_forward(o, i)

@@ -1,0 +1,257 @@
+// Neighbor aggregation over a node shard with in-kernel remote fetch (sm_100a).
+//
+// Stands in for the reference's np_div kernels (include/neighbor_utils.cuh:1351-1460 for the plain
+// sum, :1554-1667 for the GIN form) and keeps their work decomposition: one thread block per node
+// of the shard, `wpb` warps per block, and each warp taking `dist*ps` consecutive neighbors per
+// turn with a block stride of `dist*wpb*ps` (:1395-1400 for the local list, :1432-1437 for the
+// remote list; the local list is walked first).
+//
+// What is different from the reference:
+//   * a row of `dim` floats is read by a SUB-WARP of LPR lanes with one 128-bit load per lane, so
+//     a warp gathers 32/LPR neighbor rows per load instruction (8 rows at dim 16) and keeps up to
+//     32 independent row loads in flight, instead of one row per iteration with half the lanes idle;
+//   * the running sum lives in registers, not in shared memory that is read-modify-written per
+//     element (:1409);
+//   * a remote neighbor's row is read straight from the owner's memory through a peer-mapped
+//     pointer (owner = id / nodePerPE, row = id % nodePerPE, :1440-1441) with the same vector loads,
+//     so remote and local rows are in flight together; there is no blocking per-neighbor get (:1445);
+//   * the warps' partial sums meet in shared memory and ONE thread group stores the output row.
+//     No atomics (:1456-1458 uses a spin on atomicExch), so the result is reproducible for fixed
+//     knobs, and the epilogue (accumulate / GIN combine / row scale) is applied exactly once.
+#include "common.h"
+
+namespace {
+
+struct AggParams {
+    float* out;
+    const float* peer[MGGB_MAX_PES];
+    const int32_t* rp_l;
+    const int32_t* ci_l;
+    const int32_t* rp_r;
+    const int32_t* ci_r;
+    const float* row_scale;
+    int32_t lb;
+    int32_t num_rows;
+    int32_t node_per_pe;
+    int dim;
+    int pe;
+    int num_pes;
+    int chunk;             // dist * ps: neighbors a warp takes per turn
+    unsigned long long div_magic;  // owner = (id * div_magic) >> div_shift
+    int div_shift;
+    int mode;              // 0 overwrite, 1 accumulate, 2 GIN combine
+    float self_scale;      // 1 + eps (GIN)
+};
+
+enum { MODE_OVERWRITE = 0, MODE_ACCUMULATE = 1, MODE_GIN = 2 };
+
+template <int VEC> struct Vec;
+template <> struct Vec<4> {
+    float4 v;
+    __device__ __forceinline__ void zero() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
+    __device__ __forceinline__ void load(const float* p) { v = __ldg(reinterpret_cast<const float4*>(p)); }
+    __device__ __forceinline__ void add(const Vec& o) { v.x += o.v.x; v.y += o.v.y; v.z += o.v.z; v.w += o.v.w; }
+    __device__ __forceinline__ void xor_reduce(int off) {
+        v.x += __shfl_xor_sync(0xffffffffu, v.x, off);
+        v.y += __shfl_xor_sync(0xffffffffu, v.y, off);
+        v.z += __shfl_xor_sync(0xffffffffu, v.z, off);
+        v.w += __shfl_xor_sync(0xffffffffu, v.w, off);
+    }
+    __device__ __forceinline__ void store_smem(float* p) const { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec<1> {
+    float v;
+    __device__ __forceinline__ void zero() { v = 0.f; }
+    __device__ __forceinline__ void load(const float* p) { v = __ldg(p); }
+    __device__ __forceinline__ void add(const Vec& o) { v += o.v; }
+    __device__ __forceinline__ void xor_reduce(int off) { v += __shfl_xor_sync(0xffffffffu, v, off); }
+    __device__ __forceinline__ void store_smem(float* p) const { *p = v; }
+};
+
+// Gathers the edges [beg, end) of one neighbor list that belong to this warp and adds their rows
+// (columns [col, col+VEC) of each) into acc.  REMOTE selects the owner lookup.
+template <int LPR, int VEC, bool REMOTE>
+__device__ __forceinline__ void gather_list(Vec<VEC>& acc, const AggParams& P, const float* const* s_peer,
+                                            const int32_t* __restrict__ ci, int beg, int end,
+                                            int warp, int nwarps, int lane, int col, bool col_ok) {
+    constexpr int G = 32 / LPR;             // neighbor rows per load round
+    constexpr int U = LPR < 8 ? LPR : 8;    // rounds issued back to back (loads in flight = U*G rows)
+    const int g = lane / LPR;
+    const float* self_base = P.peer[P.pe];
+    const long long block_stride = (long long)P.chunk * nwarps;
+    for (long long b_beg = beg; b_beg < end; b_beg += block_stride) {
+        const long long w_beg = b_beg + (long long)warp * P.chunk;
+        if (w_beg >= end) break;
+        const int w_end = (int)min((long long)end, w_beg + P.chunk);
+        for (int base = (int)w_beg; base < w_end; base += 32) {
+            const int cnt = min(32, w_end - base);
+            // one coalesced read of up to 32 neighbor ids; streamed, they are used once
+            const int my = (lane < cnt) ? __ldcs(ci + base + lane) : -1;
+#pragma unroll 1
+            for (int r0 = 0; r0 < LPR; r0 += U) {
+                if (r0 * G >= cnt) break;
+                Vec<VEC> v[U];
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int nid = __shfl_sync(0xffffffffu, my, (r0 + u) * G + g);
+                    v[u].zero();
+                    if (nid >= 0 && col_ok) {
+                        const float* src;
+                        if (REMOTE) {
+                            const unsigned owner = (unsigned)(((unsigned long long)(unsigned)nid * P.div_magic) >> P.div_shift);
+                            const int row = nid - (int)owner * P.node_per_pe;
+                            src = s_peer[owner] + (long long)row * P.dim + col;
+                        } else {
+                            src = self_base + (long long)(nid - P.lb) * P.dim + col;
+                        }
+                        v[u].load(src);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; u++) acc.add(v[u]);
+            }
+        }
+    }
+}
+
+// One block per node.  Dynamic shared memory: nwarps * dim floats (the warps' partial rows).
+template <int LPR, int VEC>
+__global__ void __launch_bounds__(512) sag_np_div_kernel(const AggParams P) {
+    extern __shared__ __align__(16) float s_part[];
+    __shared__ const float* s_peer[MGGB_MAX_PES];
+
+    const int row = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nwarps = blockDim.x >> 5;
+    if (threadIdx.x < MGGB_MAX_PES) s_peer[threadIdx.x] = P.peer[threadIdx.x < P.num_pes ? threadIdx.x : 0];
+    __syncthreads();
+
+    const int lbeg = P.rp_l[row], lend = P.rp_l[row + 1];
+    const int rbeg = P.rp_r[row], rend = P.rp_r[row + 1];
+    const int l = lane % LPR;
+    constexpr int COLS = LPR * VEC;  // columns covered per pass
+
+    for (int cb = 0; cb < P.dim; cb += COLS) {
+        const int col = cb + l * VEC;
+        const bool col_ok = col < P.dim;
+        Vec<VEC> acc;
+        acc.zero();
+        gather_list<LPR, VEC, false>(acc, P, s_peer, P.ci_l, lbeg, lend, warp, nwarps, lane, col, col_ok);
+        if (rend > rbeg)
+            gather_list<LPR, VEC, true>(acc, P, s_peer, P.ci_r, rbeg, rend, warp, nwarps, lane, col, col_ok);
+        // fold the 32/LPR sub-warps together
+#pragma unroll
+        for (int off = LPR; off < 32; off <<= 1) acc.xor_reduce(off);
+        if (lane < LPR && col_ok) acc.store_smem(s_part + warp * P.dim + col);
+    }
+    __syncthreads();
+
+    // Single writer per output element: sum the warps' partials in warp order, then the epilogue.
+    const long long obase = (long long)row * P.dim;
+    for (int c = threadIdx.x; c < P.dim; c += blockDim.x) {
+        float s = 0.f;
+        for (int w = 0; w < nwarps; w++) s += s_part[w * P.dim + c];
+        if (P.row_scale) s *= P.row_scale[row];
+        if (P.mode == MODE_GIN) s += P.self_scale * P.peer[P.pe][obase + c];
+        else if (P.mode == MODE_ACCUMULATE) s += P.out[obase + c];
+        P.out[obase + c] = s;
+    }
+}
+
+// Exact unsigned division by a runtime constant d for every 32-bit numerator:
+// q = (n * magic) >> shift with shift = 32 + ceil(log2 d), magic = ceil(2^shift / d) < 2^33.
+void make_divider(uint32_t d, unsigned long long* magic, int* shift) {
+    int lg = 0;
+    while ((1ull << lg) < d) lg++;
+    *shift = 32 + lg;
+    const unsigned __int128 one = 1;
+    *magic = (unsigned long long)(((one << *shift) + d - 1) / d);
+}
+
+template <int LPR, int VEC>
+int launch(const AggParams& P, int wpb, cudaStream_t st) {
+    const size_t smem = (size_t)wpb * P.dim * sizeof(float);
+    if (smem > 48 * 1024)
+        MGGB_CUDA(cudaFuncSetAttribute(sag_np_div_kernel<LPR, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    sag_np_div_kernel<LPR, VEC><<<P.num_rows, wpb * 32, smem, st>>>(P);
+    MGGB_CUDA(cudaGetLastError());
+    return MGGB_OK;
+}
+
+int aggregate(float* output, const float* const* peer_input, int num_pes, const int32_t* rp_l,
+              const int32_t* ci_l, const int32_t* rp_r, const int32_t* ci_r, int32_t lb, int32_t ub,
+              int dim, int32_t node_per_pe, int pe, int ps, int wpb, int dist, const float* row_scale,
+              int mode, float self_scale, void* stream) {
+    MGGB_REQUIRE(output && peer_input && rp_l && rp_r, "aggregate: NULL argument");
+    MGGB_REQUIRE(num_pes >= 1 && num_pes <= MGGB_MAX_PES, "aggregate: num_pes must be in [1,%d] (got %d)", MGGB_MAX_PES, num_pes);
+    MGGB_REQUIRE(pe >= 0 && pe < num_pes, "aggregate: pe %d outside [0,%d)", pe, num_pes);
+    MGGB_REQUIRE(lb >= 0 && ub >= lb, "aggregate: need 0 <= lb <= ub (lb=%d ub=%d)", lb, ub);
+    MGGB_REQUIRE(dim >= 1, "aggregate: dim must be >= 1 (got %d)", dim);
+    MGGB_REQUIRE(node_per_pe >= 1 && ub - lb <= node_per_pe, "aggregate: shard [%d,%d) larger than node_per_pe=%d", lb, ub, node_per_pe);
+    MGGB_REQUIRE((long long)lb == (long long)pe * node_per_pe || ub == lb, "aggregate: lb=%d is not pe*node_per_pe (%d*%d)", lb, pe, node_per_pe);
+    MGGB_REQUIRE(ps >= 1 && dist >= 1 && wpb >= 1 && wpb <= 16, "aggregate: need part_size >= 1, interleaved_dist >= 1, 1 <= warp_per_block <= 16 (ps=%d wpb=%d dist=%d)", ps, wpb, dist);
+    MGGB_REQUIRE((long long)ps * dist <= (1 << 30), "aggregate: part_size*interleaved_dist too large");
+    for (int p = 0; p < num_pes; p++)
+        MGGB_REQUIRE(peer_input[p] != nullptr, "aggregate: peer_input[%d] is NULL", p);
+    MGGB_REQUIRE(mode != MODE_GIN || output != peer_input[pe], "gin_np_div: output must not alias this PE's input buffer");
+    if ((size_t)wpb * dim * sizeof(float) > 200 * 1024)
+        return mggb::fail(MGGB_ERR_UNSUPPORTED, "aggregate: warp_per_block*dim*4 = %zu bytes of shared memory exceeds 200 KiB", (size_t)wpb * dim * sizeof(float));
+    if (ub == lb) return MGGB_OK;
+
+    AggParams P{};
+    P.out = output;
+    for (int p = 0; p < MGGB_MAX_PES; p++) P.peer[p] = peer_input[p < num_pes ? p : 0];
+    P.rp_l = rp_l; P.ci_l = ci_l; P.rp_r = rp_r; P.ci_r = ci_r;
+    P.row_scale = row_scale;
+    P.lb = lb; P.num_rows = ub - lb; P.node_per_pe = node_per_pe;
+    P.dim = dim; P.pe = pe; P.num_pes = num_pes;
+    P.chunk = ps * dist;
+    make_divider((uint32_t)node_per_pe, &P.div_magic, &P.div_shift);
+    P.mode = mode; P.self_scale = self_scale;
+
+    cudaStream_t st = (cudaStream_t)stream;
+    bool vec4 = (dim % 4 == 0);
+    for (int p = 0; p < num_pes && vec4; p++) vec4 = ((uintptr_t)peer_input[p] % 16 == 0);
+    if (vec4) {
+        const int q = dim / 4;
+        if (q <= 1) return launch<1, 4>(P, wpb, st);
+        if (q <= 2) return launch<2, 4>(P, wpb, st);
+        if (q <= 4) return launch<4, 4>(P, wpb, st);
+        if (q <= 8) return launch<8, 4>(P, wpb, st);
+        if (q <= 16) return launch<16, 4>(P, wpb, st);
+        return launch<32, 4>(P, wpb, st);
+    }
+    if (dim <= 1) return launch<1, 1>(P, wpb, st);
+    if (dim <= 2) return launch<2, 1>(P, wpb, st);
+    if (dim <= 4) return launch<4, 1>(P, wpb, st);
+    if (dim <= 8) return launch<8, 1>(P, wpb, st);
+    if (dim <= 16) return launch<16, 1>(P, wpb, st);
+    return launch<32, 1>(P, wpb, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int mggb_sag_np_div(float* output, const float* const* peer_input, int num_pes,
+                    const int32_t* row_ptr_l, const int32_t* col_idx_l, const int32_t* row_ptr_r,
+                    const int32_t* col_idx_r, int32_t lb, int32_t ub, int dim, int32_t node_per_pe,
+                    int pe, int part_size, int warp_per_block, int interleaved_dist,
+                    const float* row_scale, int flags, void* stream) {
+    return aggregate(output, peer_input, num_pes, row_ptr_l, col_idx_l, row_ptr_r, col_idx_r, lb, ub, dim,
+                     node_per_pe, pe, part_size, warp_per_block, interleaved_dist, row_scale,
+                     (flags & MGGB_AGG_ACCUMULATE) ? MODE_ACCUMULATE : MODE_OVERWRITE, 0.f, stream);
+}
+
+int mggb_gin_np_div(float* output, const float* const* peer_input, int num_pes,
+                    const int32_t* row_ptr_l, const int32_t* col_idx_l, const int32_t* row_ptr_r,
+                    const int32_t* col_idx_r, int32_t lb, int32_t ub, int dim, int32_t node_per_pe,
+                    int pe, int part_size, int warp_per_block, int interleaved_dist, float eps,
+                    int flags, void* stream) {
+    (void)flags;
+    return aggregate(output, peer_input, num_pes, row_ptr_l, col_idx_l, row_ptr_r, col_idx_r, lb, ub, dim,
+                     node_per_pe, pe, part_size, warp_per_block, interleaved_dist, nullptr, MODE_GIN,
+                     1.0f + eps, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,31 @@
+// Shared helpers of the library's translation units: status codes, the per-thread error message
+// and the CUDA-call check.  Nothing here crosses the C ABI.
+#pragma once
+#include <cstdarg>
+#include <cstdio>
+#include <cstdint>
+#include "../../include/mggb200.h"
+
+namespace mggb {
+
+// Stores a printf-style message for mggb_last_error() and returns `code`.
+int fail(int code, const char* fmt, ...);
+void clear_error();
+
+}  // namespace mggb
+
+#define MGGB_REQUIRE(cond, ...)                                            \
+    do {                                                                   \
+        if (!(cond)) return mggb::fail(MGGB_ERR_INVALID_ARG, __VA_ARGS__); \
+    } while (0)
+
+#ifdef __CUDACC__
+#include <cuda_runtime.h>
+#define MGGB_CUDA(call)                                                                   \
+    do {                                                                                  \
+        cudaError_t e__ = (call);                                                         \
+        if (e__ != cudaSuccess)                                                           \
+            return mggb::fail(MGGB_ERR_CUDA, "%s failed: %s (%s:%d)", #call,              \
+                              cudaGetErrorString(e__), __FILE__, __LINE__);               \
+    } while (0)
+#endif

@@ -1,0 +1,122 @@
+// Dense node update out[n, dim2] = x[n, dim1] * w[dim1, dim2] (row-major, alpha 1, beta 0, no bias)
+// with an optional per-row scale and ReLU epilogue.
+//
+// Stands in for dense_beg_new_forward / dense_hidden_new_forward (include/gnn_layer.cuh:42-52), which
+// hand the product to cublasSgemm with m=dim2, n=numNodes, k=dim1 (include/layer_new.cuh:285-286).
+// The matrices are tall and skinny (n up to millions, dim2 16..172), so the product is bound by
+// streaming x once from HBM.
+//
+// This file holds the fp32 CUDA-core kernel: a block keeps a [BM x 32] slab of x and the matching
+// [32 x dim2] slab of w in shared memory and each thread owns a 4x4 output micro-tile.
+#include "common.h"
+
+namespace {
+
+constexpr int BK = 32;
+constexpr int TM = 4;
+constexpr int TN = 4;
+constexpr int THREADS = 256;
+
+__global__ void __launch_bounds__(THREADS)
+dense_simt_kernel(float* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
+                  long long n, int K, int M, const float* __restrict__ row_scale, int relu, int CT, int RT) {
+    extern __shared__ __align__(16) float smem[];
+    const int BM = RT * TM;
+    const int Mpad = CT * TN;
+    float* Xs = smem;                       // [BM][BK+1]
+    float* Ws = smem + (size_t)BM * (BK + 1);  // [BK][Mpad]
+    const int t = threadIdx.x;
+    const int ct = t % CT, rt = t / CT;
+    const bool active = rt < RT;
+    const long long tiles = (n + BM - 1) / BM;
+
+    for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const long long row0 = tile * BM;
+        float acc[TM][TN];
+#pragma unroll
+        for (int i = 0; i < TM; i++)
+#pragma unroll
+            for (int j = 0; j < TN; j++) acc[i][j] = 0.f;
+
+        for (int k0 = 0; k0 < K; k0 += BK) {
+            for (int idx = t; idx < BM * BK; idx += THREADS) {
+                const int r = idx / BK, k = idx % BK;
+                const long long gr = row0 + r;
+                Xs[r * (BK + 1) + k] = (gr < n && k0 + k < K) ? __ldcs(x + gr * K + k0 + k) : 0.f;
+            }
+            for (int idx = t; idx < BK * Mpad; idx += THREADS) {
+                const int k = idx / Mpad, c = idx % Mpad;
+                Ws[idx] = (k0 + k < K && c < M) ? __ldg(w + (long long)(k0 + k) * M + c) : 0.f;
+            }
+            __syncthreads();
+            if (active) {
+#pragma unroll 8
+                for (int k = 0; k < BK; k++) {
+                    const float4 b = *reinterpret_cast<const float4*>(Ws + k * Mpad + ct * TN);
+#pragma unroll
+                    for (int i = 0; i < TM; i++) {
+                        const float a = Xs[(rt * TM + i) * (BK + 1) + k];
+                        acc[i][0] = fmaf(a, b.x, acc[i][0]);
+                        acc[i][1] = fmaf(a, b.y, acc[i][1]);
+                        acc[i][2] = fmaf(a, b.z, acc[i][2]);
+                        acc[i][3] = fmaf(a, b.w, acc[i][3]);
+                    }
+                }
+            }
+            __syncthreads();
+        }
+        if (active) {
+#pragma unroll
+            for (int i = 0; i < TM; i++) {
+                const long long gr = row0 + rt * TM + i;
+                if (gr >= n) continue;
+                const float s = row_scale ? row_scale[gr] : 1.f;
+#pragma unroll
+                for (int j = 0; j < TN; j++) {
+                    const int c = ct * TN + j;
+                    if (c < M) {
+                        float v = acc[i][j] * s;
+                        if (relu) v = fmaxf(v, 0.f);
+                        out[gr * M + c] = v;
+                    }
+                }
+            }
+        }
+    }
+}
+
+}  // namespace
+
+namespace mggb {
+
+int dense_simt(float* out, const float* x, const float* w, int64_t n, int dim1, int dim2,
+               const float* row_scale, int flags, cudaStream_t st) {
+    const int CT = (dim2 + TN - 1) / TN;
+    if (CT > THREADS)
+        return fail(MGGB_ERR_UNSUPPORTED, "dense_forward: dim2=%d exceeds %d", dim2, THREADS * TN);
+    const int RT = THREADS / CT;
+    const int BM = RT * TM;
+    const size_t smem = ((size_t)BM * (BK + 1) + (size_t)BK * CT * TN) * sizeof(float);
+    if (smem > 48 * 1024)
+        MGGB_CUDA(cudaFuncSetAttribute(dense_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int dev = 0, sms = 148;
+    MGGB_CUDA(cudaGetDevice(&dev));
+    MGGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long tiles = (n + BM - 1) / BM;
+    const int grid = (int)(tiles < (long long)sms * 4 ? tiles : (long long)sms * 4);
+    dense_simt_kernel<<<grid, THREADS, smem, st>>>(out, x, w, n, dim1, dim2, row_scale,
+                                                   (flags & MGGB_DENSE_RELU) ? 1 : 0, CT, RT);
+    MGGB_CUDA(cudaGetLastError());
+    return MGGB_OK;
+}
+
+}  // namespace mggb
+
+extern "C" int mggb_dense_forward(float* out, const float* x, const float* w, int64_t n, int dim1,
+                                  int dim2, const float* row_scale, int flags, void* stream) {
+    MGGB_REQUIRE(out && x && w, "dense_forward: NULL argument");
+    MGGB_REQUIRE(n >= 0 && dim1 >= 1 && dim2 >= 1, "dense_forward: need n >= 0, dim1 >= 1, dim2 >= 1 (n=%lld dim1=%d dim2=%d)", (long long)n, dim1, dim2);
+    MGGB_REQUIRE(out != x, "dense_forward: out must not alias x");
+    if (n == 0) return MGGB_OK;
+    return mggb::dense_simt(out, x, w, n, dim1, dim2, row_scale, flags, (cudaStream_t)stream);
+}

@@ -1,0 +1,274 @@
+"""Forward-pass orchestration: the host side of the reference's ``main()`` functions.
+
+* :class:`GCN2Forward`   - ``src/mgg_np_div_mem.cu:211-227``  (2-layer GCN, the headline path)
+* :class:`GIN5Forward`   - ``src/mgg_np_div_gin_mem.cu:193-223`` (5-layer GIN)
+* :class:`SingleAggregation` - ``src/mgg_np_div_kernel.cu:183-188`` (one aggregation; the ps/wpb/dist sweeps)
+
+One object serves one PE (GPU).  A forward pass is a list of *stages*; peers must not start stage
+s+1 before every PE finished stage s, because stage s+1 reads what the peers published in stage s.
+:func:`run_stages` runs the stages with a barrier between them.  (The reference has no barrier
+between its layers, ``src/mgg_np_div_mem.cu:213-226``: a PE can read a peer's buffer while the owner
+overwrites it.)  With one process per GPU the barrier is a one-element NCCL all-reduce enqueued on
+the compute stream, so the host never blocks; several PEs emulated in one process on one stream
+need none.
+
+Differences from the reference's drivers that are deliberate:
+* the dense step computes ``X*W`` from its input (the reference multiplies its output buffer in place);
+* both GCN aggregations run at the hidden width, as in the reference (``:214-215, :221-222``), which is
+  legitimate because layer 2 is evaluated as ``(A*H)*W2``;
+* publishing alternates between two symmetric buffers so that no PE overwrites a buffer a slower
+  peer may still be reading.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import api
+from .symmem import SymmetricBuffer
+
+
+@dataclass
+class Knobs:
+    """The reference's command-line tuning knobs (``src/mgg_np_div_mem.cu:44-46``)."""
+    partSize: int = 16
+    warpPerBlock: int = 4
+    interleaved_dist: int = 1
+
+
+class Shard:
+    """What one PE holds of the graph: its node range and the split CSR on the device."""
+
+    def __init__(self, row_ptr, col_idx, pe: int, num_pes: int, device=None, num_nodes: Optional[int] = None):
+        row_ptr = np.ascontiguousarray(row_ptr)
+        n = len(row_ptr) - 1 if num_nodes is None else num_nodes
+        self.pe, self.num_pes, self.num_nodes = pe, num_pes, n
+        self.node_per_pe, self.lb, self.ub = api.shard_range(n, num_pes, pe)
+        self.rows = self.ub - self.lb
+        lp, rp, lc, rc = api.split_CSR(row_ptr, col_idx, self.lb, self.ub)
+        self.e_local, self.e_remote = int(lc.size), int(rc.size)
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.device = dev
+        self.rp_l = torch.from_numpy(lp).to(dev)
+        self.rp_r = torch.from_numpy(rp).to(dev)
+        # never hand the kernel a NULL column array, even for an empty half
+        self.ci_l = torch.from_numpy(lc if lc.size else np.zeros(1, np.int32)).to(dev)
+        self.ci_r = torch.from_numpy(rc if rc.size else np.zeros(1, np.int32)).to(dev)
+        self._dinv = None
+
+    @property
+    def edges(self) -> int:
+        return self.e_local + self.e_remote
+
+    def inv_sqrt_degree(self) -> torch.Tensor:
+        """1/sqrt(deg) of this shard's rows (deg = stored row length, local + remote)."""
+        if self._dinv is None:
+            self._dinv = torch.empty(max(self.rows, 1), dtype=torch.float32, device=self.device)[: self.rows]
+            if self.rows:
+                api.inv_sqrt_degree(self._dinv, self.rp_l, self.rp_r)
+        return self._dinv
+
+    def aggregate(self, out, sym, dim, knobs: Knobs, accumulate=False, row_scale_=None):
+        api.mgg_SAG_np_div(out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim,
+                           self.node_per_pe, self.pe, knobs.partSize, knobs.warpPerBlock,
+                           knobs.interleaved_dist, accumulate=accumulate, row_scale_=row_scale_)
+
+    def aggregate_gin(self, out, sym, dim, knobs: Knobs, eps: float):
+        api.mgg_GIN_np_div(out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim,
+                           self.node_per_pe, self.pe, knobs.partSize, knobs.warpPerBlock,
+                           knobs.interleaved_dist, eps)
+
+
+def nccl_stream_barrier(group=None) -> Callable[[], None]:
+    """Barrier for one-process-per-GPU runs: a one-element all-reduce on the current stream."""
+    import torch.distributed as dist
+    token = torch.zeros(1, dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+
+    def barrier():
+        dist.all_reduce(token, group=group)
+    return barrier
+
+
+def run_stages(models: Sequence, barrier: Optional[Callable[[], None]] = None):
+    """Runs every model's stage s (all PEs held by this process), then the barrier, for each s."""
+    n = len(models[0].stages)
+    for s in range(n):
+        for m in models:
+            m.stages[s]()
+        if barrier is not None and s + 1 < n:
+            barrier()
+
+
+class _Forward:
+    """Shared plumbing: symmetric buffers, sizes, the host-buffer entry point."""
+
+    def __init__(self, shard: Shard, sym_a, sym_b, knobs: Knobs):
+        self.shard, self.knobs = shard, knobs
+        self.sym_a, self.sym_b = sym_a, sym_b
+        self.stages: List[Callable[[], None]] = []
+        self._h_out = None
+
+    def _sym_view(self, sym, dim):
+        return sym.tensor[: self.shard.rows * dim].view(self.shard.rows, dim)
+
+    def forward(self, barrier=None):
+        run_stages([self], barrier)
+        return self.out
+
+    def forward_host(self, x_host: torch.Tensor, barrier=None) -> torch.Tensor:
+        """The call a user with HOST data makes: uploads this PE's feature rows (pinned ``x_host``
+        [rows, in_dim]), runs the forward pass and returns the class probabilities in pinned host
+        memory.  Synchronises the stream before returning."""
+        self.d_in.copy_(x_host, non_blocking=True)
+        self.forward(barrier)
+        if self._h_out is None:
+            self._h_out = torch.empty(self.out.shape, dtype=torch.float32, pin_memory=True)
+        self._h_out.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._h_out
+
+
+class GCN2Forward(_Forward):
+    """softmax((A * (A * (X*W1))) * W2) on one PE's rows; both aggregations at the hidden width.
+
+    norm: "none" (the reference: unnormalised sums) or "sym" (A scaled by 1/sqrt(deg_i*deg_j); the
+    row factors are folded into the epilogues of the dense and aggregation kernels).
+    Buffers per PE: d_in [rows, in], two symmetric [nodePerPE, hidden], d_agg [rows, hidden],
+    logits/out [rows, out]."""
+
+    def __init__(self, shard: Shard, in_dim: int, hidden: int, out_dim: int, sym_a, sym_b, knobs: Knobs,
+                 w1: Optional[torch.Tensor] = None, w2: Optional[torch.Tensor] = None, norm: str = "none",
+                 dense_flags: int = 0):
+        super().__init__(shard, sym_a, sym_b, knobs)
+        dev, rows = shard.device, max(shard.rows, 1)
+        self.in_dim, self.hidden, self.out_dim = in_dim, hidden, out_dim
+        self.d_in = torch.zeros(rows, in_dim, dtype=torch.float32, device=dev)[: shard.rows]
+        self.d_agg = torch.zeros(rows, hidden, dtype=torch.float32, device=dev)[: shard.rows]
+        self.logits = torch.zeros(rows, out_dim, dtype=torch.float32, device=dev)[: shard.rows]
+        self.out = torch.zeros(rows, out_dim, dtype=torch.float32, device=dev)[: shard.rows]
+        self.dp1 = api.dense_param_new_beg("d-1", self.d_in, self._sym_view(sym_a, hidden), shard.rows, in_dim, hidden)
+        self.dp2 = api.dense_param_new_hidden("d-2", self.d_agg, self.logits, shard.rows, hidden, out_dim)
+        self.smx = api.softmax_new_param("smx-2", self.logits, self.out, shard.rows, out_dim)
+        self.dp1.flags = self.dp2.flags = dense_flags
+        if w1 is not None:
+            self.dp1.set_weight(w1)
+        if w2 is not None:
+            self.dp2.set_weight(w2)
+        if norm not in ("none", "sym"):
+            raise ValueError("norm must be 'none' or 'sym'")
+        self.scale1 = self.scale2 = None
+        if norm == "sym":
+            dinv = shard.inv_sqrt_degree()
+            self.dp1.row_scale = dinv          # H1' = dinv * (X W1)
+            self.scale1 = dinv * dinv          # Z1' = dinv * (dinv * A H1')   (second factor pre-scales layer 2)
+            self.scale2 = dinv                 # Z2  = dinv * A Z1'
+        self.stages = [self._dense1, self._agg1, self._agg2_dense2_softmax]
+
+    def _dense1(self):
+        if self.shard.rows:
+            api.dense_beg_new_forward(self.dp1)
+
+    def _agg1(self):
+        if self.shard.rows:
+            self.shard.aggregate(self._sym_view(self.sym_b, self.hidden), self.sym_a, self.hidden, self.knobs,
+                                 row_scale_=self.scale1)
+
+    def _agg2_dense2_softmax(self):
+        if self.shard.rows:
+            self.shard.aggregate(self.d_agg, self.sym_b, self.hidden, self.knobs, row_scale_=self.scale2)
+            api.dense_hidden_new_forward(self.dp2)
+            api.softmax_new_forward(self.smx)
+
+    kernels_per_forward = 5   # dense, aggregate, aggregate, dense, softmax
+    aggregations_per_forward = 2
+
+
+class GIN5Forward(_Forward):
+    """dense(in->hidden), then five times [GIN aggregation, dense], the last dense hidden->out, softmax.
+    Each "MLP" is one bias-free linear layer, as in the reference (``src/mgg_np_div_gin_mem.cu:195-222``)."""
+
+    def __init__(self, shard: Shard, in_dim: int, hidden: int, out_dim: int, sym_a, sym_b, knobs: Knobs,
+                 eps: float = 0.5, weights: Optional[Sequence[torch.Tensor]] = None, num_layers: int = 5,
+                 dense_flags: int = 0):
+        super().__init__(shard, sym_a, sym_b, knobs)
+        dev, rows = shard.device, max(shard.rows, 1)
+        self.in_dim, self.hidden, self.out_dim, self.eps, self.num_layers = in_dim, hidden, out_dim, eps, num_layers
+        self.d_in = torch.zeros(rows, in_dim, dtype=torch.float32, device=dev)[: shard.rows]
+        self.d_agg = torch.zeros(rows, hidden, dtype=torch.float32, device=dev)[: shard.rows]
+        self.logits = torch.zeros(rows, out_dim, dtype=torch.float32, device=dev)[: shard.rows]
+        self.out = torch.zeros(rows, out_dim, dtype=torch.float32, device=dev)[: shard.rows]
+        syms = [sym_a, sym_b]
+        self.dense = [api.dense_param_new_beg("d-1", self.d_in, self._sym_view(sym_a, hidden), shard.rows, in_dim, hidden)]
+        for k in range(1, num_layers):
+            self.dense.append(api.dense_param_new_hidden(f"d-{k + 1}", self.d_agg, self._sym_view(syms[k % 2], hidden),
+                                                         shard.rows, hidden, hidden))
+        self.dense.append(api.dense_param_new_hidden(f"d-{num_layers + 1}", self.d_agg, self.logits, shard.rows, hidden, out_dim))
+        for dp in self.dense:
+            dp.flags = dense_flags
+        if weights is not None:
+            for dp, w in zip(self.dense, weights):
+                dp.set_weight(w)
+        self.smx = api.softmax_new_param("smx", self.logits, self.out, shard.rows, out_dim)
+        self._syms = syms
+        self.stages = [self._first] + [self._layer(k) for k in range(num_layers)]
+
+    def _first(self):
+        if self.shard.rows:
+            api.dense_beg_new_forward(self.dense[0])
+
+    def _layer(self, k: int):
+        def stage():
+            if not self.shard.rows:
+                return
+            self.shard.aggregate_gin(self.d_agg, self._syms[k % 2], self.hidden, self.knobs, self.eps)
+            api.dense_hidden_new_forward(self.dense[k + 1])
+            if k == self.num_layers - 1:
+                api.softmax_new_forward(self.smx)
+        return stage
+
+    @property
+    def kernels_per_forward(self):
+        return 2 * self.num_layers + 2
+
+    @property
+    def aggregations_per_forward(self):
+        return self.num_layers
+
+
+class SingleAggregation(_Forward):
+    """One ``mgg_SAG_np_div`` over the shard (``src/mgg_np_div_kernel.cu:183-188``): what the
+    ps / wpb / dist design-space sweeps time."""
+
+    def __init__(self, shard: Shard, dim: int, sym_a, knobs: Knobs, norm: str = "none"):
+        super().__init__(shard, sym_a, None, knobs)
+        self.dim = dim
+        rows = max(shard.rows, 1)
+        self.d_in = self._sym_view(sym_a, dim)
+        self.out = torch.zeros(rows, dim, dtype=torch.float32, device=shard.device)[: shard.rows]
+        self.scale = shard.inv_sqrt_degree() if norm == "sym" else None
+        self.stages = [self._agg]
+
+    def _agg(self):
+        if self.shard.rows:
+            self.shard.aggregate(self.out, self.sym_a, self.dim, self.knobs, row_scale_=self.scale)
+
+    kernels_per_forward = 1
+    aggregations_per_forward = 1
+
+
+class LocalSym:
+    """Symmetric buffers of several PEs emulated in ONE process: plain tensors plus the shared table."""
+
+    def __init__(self, tensors: Sequence[torch.Tensor], pe: int):
+        self.tensor = tensors[pe]
+        self.peer_ptrs = [t.data_ptr() for t in tensors]
+
+
+def local_symmetric(num_pes: int, numel: int, device=None) -> List[LocalSym]:
+    """One buffer per emulated PE, all on one device; returns the per-PE handles."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    tensors = [torch.zeros(max(numel, 4), dtype=torch.float32, device=dev) for _ in range(num_pes)]
+    return [LocalSym(tensors, pe) for pe in range(num_pes)]

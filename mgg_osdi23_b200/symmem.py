@@ -1,0 +1,71 @@
+"""Symmetric (peer-readable) embedding buffers for the Python host layer.
+
+Replaces ``nvshmem_malloc`` (``src/mgg_np_div_mem.cu:139``): every PE allocates a buffer of the same
+size and every PE ends up with the table of all PEs' base addresses, which the aggregation call
+takes.  Allocation and mapping go through the C ABI (CUDA IPC between processes); torch only wraps
+the local allocation as a tensor and carries the 64-byte handles between ranks.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ._lib import lib, check
+
+
+class _RawCudaBuffer:
+    """Exposes a raw device allocation through ``__cuda_array_interface__`` so torch can view it."""
+
+    def __init__(self, ptr: int, numel: int):
+        self.__cuda_array_interface__ = {
+            "shape": (numel,), "typestr": "<f4", "data": (ptr, False), "version": 3, "strides": None}
+
+
+class SymmetricBuffer:
+    """``numel`` fp32 elements on the current device, readable by every PE of ``group``.
+
+    ``tensor``     1-D torch view of the local allocation.
+    ``peer_ptrs``  base address of every PE's buffer as seen from this process (index = PE).
+    With ``group=None`` (or a group of one) there is a single PE and nothing is exchanged.
+    """
+
+    def __init__(self, numel: int, group=None, pe: int = 0, num_pes: int = 1):
+        self.numel = int(numel)
+        self.pe, self.num_pes = pe, num_pes
+        self._imported = []
+        p = C.c_void_p()
+        check(lib.mggb_sym_alloc(self.numel * 4, C.byref(p)))
+        self.ptr = p.value
+        self._raw = _RawCudaBuffer(self.ptr, self.numel)
+        self.tensor = torch.as_tensor(self._raw, device=torch.device("cuda", torch.cuda.current_device()))
+        self.peer_ptrs = [self.ptr]
+        if num_pes > 1:
+            import torch.distributed as dist
+            handle = C.create_string_buffer(64)
+            check(lib.mggb_sym_export(C.c_void_p(self.ptr), handle))
+            handles = [None] * num_pes
+            dist.all_gather_object(handles, handle.raw, group=group)
+            self.peer_ptrs = []
+            for r, h in enumerate(handles):
+                if r == pe:
+                    self.peer_ptrs.append(self.ptr)
+                else:
+                    q = C.c_void_p()
+                    check(lib.mggb_sym_import(h, C.byref(q)))
+                    self._imported.append(q.value)
+                    self.peer_ptrs.append(q.value)
+
+    def view(self, rows: int, dim: int) -> torch.Tensor:
+        return self.tensor[: rows * dim].view(rows, dim)
+
+    def close(self):
+        """Unmaps the peers' buffers and frees the local one.  Every PE must have stopped reading it."""
+        for q in self._imported:
+            lib.mggb_sym_close(C.c_void_p(q))
+        self._imported = []
+        if self.ptr:
+            self.tensor = None
+            self._raw = None
+            lib.mggb_sym_free(C.c_void_p(self.ptr))
+            self.ptr = 0

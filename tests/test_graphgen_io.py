@@ -1,0 +1,68 @@
+"""Synthetic graph generators and the reference's binary CSR file format."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from mgg_osdi23_b200 import graphgen as gg, graphio
+
+
+def _check_csr(g, symmetric):
+    rp, col = g.row_ptr.numpy(), g.col_idx.numpy()
+    assert rp[0] == 0 and rp[-1] == col.size and np.all(np.diff(rp) >= 0)
+    assert col.min() >= 0 and col.max() < g.num_nodes
+    rows = np.repeat(np.arange(g.num_nodes), np.diff(rp))
+    keys = rows.astype(np.int64) * g.num_nodes + col
+    assert np.all(np.diff(keys) > 0)                 # sorted, no duplicates
+    if symmetric:
+        rev = np.sort(col.astype(np.int64) * g.num_nodes + rows)
+        assert np.array_equal(rev, keys)
+
+
+def test_config1_graph():
+    g = gg.config1_graph()
+    assert g.num_nodes == 16384 and 262144 < g.num_edges <= 2 * 262144 + 16384
+    _check_csr(g, True)
+    assert np.all(np.diff(g.row_ptr.numpy()) >= 1)   # self-loops
+    g2 = gg.config1_graph()
+    assert torch.equal(g.col_idx, g2.col_idx)        # seeded
+
+
+def test_chung_lu_communities():
+    g = gg.chung_lu_graph(4096, 200_000, 2.1, seed=1, communities=8, p_intra=0.7)
+    _check_csr(g, True)
+    assert abs(g.num_edges - 200_000) / 200_000 < 0.05
+    rows = np.repeat(np.arange(g.num_nodes), np.diff(g.row_ptr.numpy()))
+    same = (rows // 512) == (g.col_idx.numpy() // 512)
+    assert 0.6 < same.mean() < 0.85
+    deg = np.diff(g.row_ptr.numpy())
+    assert deg.max() > 5 * deg.mean()                # heavy tail
+
+
+def test_directed_rmat_subset():
+    g = gg.config4_graph(scale_shift=8)
+    _check_csr(g, False)
+    assert g.num_nodes == 4_206_785 >> 8
+
+
+def test_features_are_shard_independent():
+    full = gg.features(100, 16, seed=5)
+    part = gg.features(30, 16, seed=5, first_row=40)
+    assert torch.equal(full[40:70], part)
+    assert full.min() >= -1 and full.max() < 1
+    w = gg.glorot_uniform(602, 16, seed=1)
+    assert w.abs().max() <= (6 / 618) ** 0.5
+
+
+def test_binary_csr_roundtrip(tmp_path):
+    g = gg.rmat_graph(8, 1000, seed=2)
+    beg, csr, wt = graphio.write_graph(str(tmp_path / "g"), g.row_ptr.numpy(), g.col_idx.numpy())
+    assert os.path.getsize(beg) == 8 * (g.num_nodes + 1)
+    assert os.path.getsize(csr) == 8 * g.num_edges and os.path.getsize(wt) == 4 * g.num_edges
+    assert np.array_equal(np.fromfile(csr, np.int64), g.col_idx.numpy().astype(np.int64))
+    rp, col = graphio.load_graph(beg, csr)
+    assert np.array_equal(rp, g.row_ptr.numpy()) and np.array_equal(col, g.col_idx.numpy())
+    import mgg_osdi23_b200 as mgg
+    with pytest.raises(mgg.MggbError):
+        graphio.load_graph(str(tmp_path / "missing_beg_pos.bin"), csr)
