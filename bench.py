@@ -1,0 +1,425 @@
+#!/usr/bin/env python
+"""Benchmark of the MGG hot path on B200: 2-layer GCN forward on the Reddit-shaped synthetic graph.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config cfg2|cfg1|cfg3|cfg4]
+
+One "step" is one forward pass (dense 602->16, two neighbor aggregations at width 16, dense 16->41,
+softmax) over the whole graph, sharded by node range over N GPUs (one process per GPU; torchrun for
+N > 1).  The metric is aggregated edges per second: (aggregations per pass x stored edges) / pass time.
+Prints ONE JSON line on rank 0.
+
+--impl reference times the reference's own CPU implementation of the aggregation (SAG_ref compiled
+from the reference's sources when that binary is present, else the plain-C port), with the dense /
+softmax steps done by the CPU oracle, on the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+NVLINK_GBS = 900.0          # per direction per GPU (nominal); 770 GB/s measured peer copy on this pool
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4"])
+    ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (quick checks only; not a bench value)")
+    ap.add_argument("--ps", type=int, default=None)
+    ap.add_argument("--wpb", type=int, default=None)
+    ap.add_argument("--dist", type=int, default=None)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+CONFIGS = {
+    # name: (model, in_dim, hidden, out_dim, default knobs (ps, wpb, dist), description)
+    "cfg1": ("agg", 16, 16, 16, (32, 2, 1), "R-MAT 16,384 nodes, one sym-normalised aggregation, dim 16"),
+    "cfg2": ("gcn2", 602, 16, 41, (32, 4, 1), "Reddit-shaped power-law graph 232,965 nodes ~114.6M edges, GCN-2 602-16-41"),
+    "cfg3": ("gin5", 100, 64, 47, (16, 1, 2), "products-shaped power-law graph 2,449,029 nodes ~123.7M edges, GIN-5 hidden 64"),
+    "cfg4": ("agg", 16, 16, 16, (32, 4, 1), "skewed directed R-MAT 4,206,785 nodes ~101.3M edges, one aggregation dim 16"),
+}
+
+
+def make_graph(cfg: str, device, scale: float):
+    from mgg_osdi23_b200 import graphgen as gg
+    if cfg == "cfg1":
+        return gg.config1_graph(device=device)
+    if cfg == "cfg2":
+        return gg.config2_graph(device=device, scale=scale)
+    if cfg == "cfg3":
+        return gg.config3_graph(device=device, scale=scale)
+    shift = 0
+    while scale < 1.0 and (1 << shift) * scale < 1.0:
+        shift += 1
+    return gg.config4_graph(device=device, scale_shift=shift)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._pump, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# -------------------------------------------------------------------------------------------------
+# CPU arm: the reference's host aggregation (or the port) + oracle dense/softmax
+# -------------------------------------------------------------------------------------------------
+
+def cpu_forward_factory(cfg_name, g_cpu, x_np, weights_np, norm):
+    """Returns (step_fn, description dict).  step_fn() runs one forward pass on the host."""
+    import numpy as np
+    from oracle.oracle import Oracle, Ref
+    orc = Oracle()
+    use_ref = Ref.available()
+    ref = Ref() if use_ref else None
+    rp = g_cpu.row_ptr.numpy().astype(np.int32)
+    col = g_cpu.col_idx.numpy()
+    model = CONFIGS[cfg_name][0]
+    dinv = orc.inv_sqrt_degree(rp) if norm == "sym" else None
+
+    def sag(t):
+        return ref.sag_ref(t, rp, col) if use_ref else orc.sag_f32(t, rp, col)
+
+    def agg(t):
+        if dinv is None:
+            return sag(t)
+        return orc.row_scale(sag(orc.row_scale(t, dinv)), dinv)
+
+    def step():
+        if model == "agg":
+            return agg(x_np)
+        if model == "gcn2":
+            h = orc.dense(x_np, weights_np[0])
+            z = agg(agg(h))
+            return orc.softmax(orc.dense(z, weights_np[1]))
+        h = orc.dense(x_np, weights_np[0])
+        for k in range(5):
+            h = orc.dense(sag(h) + h, weights_np[k + 1])
+        return orc.softmax(h)
+
+    desc = {"kind": "reference" if use_ref else "port", "cores": 1,
+            "sample": ("whole workload, full forward pass per step: aggregations by "
+                       + ("SAG_ref compiled from the reference's include/utils.cuh (single thread, as written)" if use_ref
+                          else "the plain-C port of SAG_ref (single thread)")
+                       + "; dense/softmax by the CPU oracle (OpenMP, not reference code)")}
+    return step, desc
+
+
+def run_reference(args, rank, world):
+    import numpy as np
+    import torch
+    if rank != 0:
+        return
+    from mgg_osdi23_b200 import graphgen as gg
+    model, din, hid, dout, _, desc = CONFIGS[args.config]
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    g = make_graph(args.config, dev, args.scale).cpu()
+    x = gg.features(g.num_nodes, din, seed=1).numpy()
+    weights = build_weights(args.config, "cpu")
+    norm = "sym" if model in ("gcn2",) or args.config == "cfg1" else "none"
+    step, d = cpu_forward_factory(args.config, g, x, [w.numpy() for w in weights], norm)
+    naggs = {"agg": 1, "gcn2": 2, "gin5": 5}[model]
+    # bound the run: the driver's K and W are honoured up to ~150 s of CPU work
+    t0 = time.perf_counter(); step(); one = time.perf_counter() - t0
+    steps = max(1, min(args.steps, int(120.0 / max(one, 1e-3))))
+    warm = max(0, min(args.warmup, int(30.0 / max(one, 1e-3))) - 1)
+    for _ in range(warm):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    value = naggs * g.num_edges / dt
+    d["value"] = value
+    d["unit"] = "edges/s"
+    line = {
+        "impl": "reference", "metric": metric_name(model), "value": value, "unit": "edges/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warm + 1, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, g, model, din, hid, dout, None, 1),
+        "cpu_baseline": d,
+        "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def metric_name(model):
+    return {"gcn2": "gcn2_fwd_aggregated_edges_per_s", "gin5": "gin5_fwd_aggregated_edges_per_s",
+            "agg": "aggregation_edges_per_s"}[model]
+
+
+def workload_config(args, g, model, din, hid, dout, knobs, world):
+    c = {"workload": f"{args.config}: {CONFIGS[args.config][5]}", "nodes": g.num_nodes, "edges": g.num_edges,
+         "in_dim": din, "aggregated_width": hid, "classes": dout, "graph": g.meta,
+         "partition": f"node-range x{world}", "l2_policy": "inputs larger than L2 (features 561 MB, neighbor ids 458 MB per aggregation)"
+         if args.config == "cfg2" else "inputs larger than L2 where the graph is (see edges x 4 B of neighbor ids per aggregation)"}
+    if knobs is not None:
+        c.update({"ps": knobs.partSize, "wpb": knobs.warpPerBlock, "dist": knobs.interleaved_dist})
+    if args.scale != 1.0:
+        c["scale"] = args.scale
+    return c
+
+
+def build_weights(cfg, device):
+    from mgg_osdi23_b200 import graphgen as gg
+    model, din, hid, dout, _, _ = CONFIGS[cfg]
+    if model == "gcn2":
+        return [gg.glorot_uniform(din, hid, 1, device), gg.glorot_uniform(hid, dout, 2, device)]
+    if model == "gin5":
+        # scaled down so that five unnormalised sum-aggregations stay finite in fp32
+        return ([gg.glorot_uniform(din, hid, 10, device) * 0.05] + [gg.glorot_uniform(hid, hid, 11 + k, device) * 0.05 for k in range(4)]
+                + [gg.glorot_uniform(hid, dout, 20, device) * 0.05])
+    return []
+
+
+# -------------------------------------------------------------------------------------------------
+# GPU arm
+# -------------------------------------------------------------------------------------------------
+
+def run_ours(args, rank, world, local_rank):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from mgg_osdi23_b200 import drivers, graphgen as gg
+    from mgg_osdi23_b200.symmem import SymmetricBuffer
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --impl ours needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    model_kind, din, hid, dout, dknobs, desc = CONFIGS[args.config]
+    knobs = drivers.Knobs(args.ps or dknobs[0], args.wpb or dknobs[1], args.dist or dknobs[2])
+
+    g = make_graph(args.config, dev, args.scale)
+    n = g.num_nodes
+    rp_host, col_host = g.row_ptr.cpu().numpy(), g.col_idx.cpu().numpy()
+    t0 = time.perf_counter()
+    shard = drivers.Shard(rp_host, col_host, rank, world, device=dev)
+    preproc_ms = (time.perf_counter() - t0) * 1e3
+    g_meta, g_edges = g.meta, g.num_edges
+    del g
+    torch.cuda.empty_cache()
+
+    npp = shard.node_per_pe
+    sym_a = SymmetricBuffer(npp * hid, group, rank, world)
+    sym_b = SymmetricBuffer(npp * hid, group, rank, world)
+    weights = build_weights(args.config, dev)
+    norm = "sym" if model_kind == "gcn2" or args.config == "cfg1" else "none"
+    if model_kind == "gcn2":
+        model = drivers.GCN2Forward(shard, din, hid, dout, sym_a, sym_b, knobs, w1=weights[0], w2=weights[1], norm=norm)
+    elif model_kind == "gin5":
+        model = drivers.GIN5Forward(shard, din, hid, dout, sym_a, sym_b, knobs, eps=0.0, weights=weights)
+    else:
+        model = drivers.SingleAggregation(shard, hid, sym_a, knobs, norm=norm)
+    x_dev = gg.features(shard.rows, din, seed=1, device=dev, first_row=shard.lb)
+    if model_kind == "agg" and norm == "sym":
+        x_dev = x_dev * shard.inv_sqrt_degree()[:, None]
+    x_host = torch.empty(x_dev.shape, dtype=torch.float32, pin_memory=True)
+    x_host.copy_(x_dev)
+    model.d_in.copy_(x_dev)
+    del x_dev
+    barrier = drivers.nccl_stream_barrier(group) if world > 1 else None
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing ---------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        model.forward(barrier)
+    sync_all()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    agg_events = []
+    shard.event_sink = agg_events
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for _ in range(args.steps):
+        model.forward(barrier)
+    e1.record()
+    sync_all()
+    shard.event_sink = None
+    step_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    agg_ms_local = sum(a.elapsed_time(b) for a, b in agg_events) / max(1, len(agg_events))
+    agg_ms = max_over_ranks(agg_ms_local)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the host-buffer entry point ---------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        for _ in range(2):
+            model.forward_host(x_host, barrier)
+        sync_all()
+        e_steps = max(3, min(args.steps, 10))
+        e0.record()
+        for _ in range(e_steps):
+            model.forward_host(x_host, barrier)
+        e1.record()
+        sync_all()
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e_steps)
+    naggs = model.aggregations_per_forward
+    total_edges = g_edges
+    value = naggs * total_edges / (step_ms * 1e-3)
+
+    # per-rank edge split, gathered for the roofline
+    stats = torch.tensor([shard.e_local, shard.e_remote, shard.rows], dtype=torch.int64, device=dev)
+    if world > 1:
+        allstats = [torch.zeros_like(stats) for _ in range(world)]
+        dist.all_gather(allstats, stats)
+    else:
+        allstats = [stats]
+    allstats = [s.tolist() for s in allstats]
+
+    if rank == 0:
+        hbm, hbm_src = measured_peaks()
+        D = hid
+        t_roof = max(max(4.0 * D * el / (hbm * 1e9), 4.0 * D * er / (NVLINK_GBS * 1e9)) for el, er, _ in allstats)
+        alg_bytes = max(4.0 * D * (el + er) for el, er, _ in allstats)       # per launch, busiest GPU
+        achieved = alg_bytes / (agg_ms * 1e-3) / 1e9
+        line = {
+            "metric": metric_name(model_kind), "value": value, "unit": "edges/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, type("G", (), {"num_nodes": n, "num_edges": total_edges, "meta": g_meta})(),
+                                      model_kind, din, hid, dout, knobs, world),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                         "traffic": None, "peak_source": f"of {hbm_src}", "kernel": "sag_np_div_kernel",
+                         "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": agg_ms,
+                         "aggregation_roofline_ms": t_roof * 1e3, "aggregation_roofline_frac": t_roof * 1e3 / agg_ms,
+                         "nvlink_gbs_assumed": NVLINK_GBS},
+            "per_gpu_edges": [{"local": el, "remote": er, "rows": r} for el, er, r in allstats],
+            "remote_fraction": sum(er for _, er, _ in allstats) / max(1, total_edges),
+            "gpu_launches": args.steps * model.kernels_per_forward * world,
+            "preproc_ms": preproc_ms, "clocks": clocks,
+        }
+        if not args.no_e2e:
+            h2d = int(n * din * 4)
+            d2h = int(n * (dout if model_kind != "agg" else hid) * 4)
+            line["e2e"] = {"value": naggs * total_edges / (e2e_ms * 1e-3), "unit": "edges/s", "ms_per_step": e2e_ms,
+                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                           "note": "pinned host features -> device, forward, probabilities -> pinned host; graph structure resident"}
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(args, rp_host, col_host, n, din, weights, norm, naggs, total_edges, g_meta)
+        print(json.dumps(line), flush=True)
+
+    sync_all()
+    sym_a.close(); sym_b.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(args, rp_host, col_host, n, din, weights, norm, naggs, total_edges, meta):
+    """Times the CPU arm on the host cores for a bounded number of passes (about 10-30 s)."""
+    import torch
+    from mgg_osdi23_b200 import graphgen as gg
+    g_cpu = gg.Graph(n, torch.from_numpy(rp_host), torch.from_numpy(col_host), meta)
+    x = gg.features(n, din, seed=1).numpy()
+    step, d = cpu_forward_factory(args.config, g_cpu, x, [w.cpu().numpy() for w in weights], norm)
+    t0 = time.perf_counter(); step(); one = time.perf_counter() - t0
+    reps = max(1, min(5, int(15.0 / max(one, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        step()
+    dt = (time.perf_counter() - t0) / reps
+    d["value"] = naggs * total_edges / dt
+    d["unit"] = "edges/s"
+    d["ms_per_step"] = dt * 1e3
+    d["sample"] += f"; {reps} timed passes after 1 warm-up"
+    return d
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun: python -m torch.distributed.run --nproc-per-node {args.gpus} bench.py ...")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

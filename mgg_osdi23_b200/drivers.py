@@ -58,6 +58,16 @@ class Shard:
         self.ci_l = torch.from_numpy(lc if lc.size else np.zeros(1, np.int32)).to(dev)
         self.ci_r = torch.from_numpy(rc if rc.size else np.zeros(1, np.int32)).to(dev)
         self._dinv = None
+        self.event_sink = None   # when a list: (start, end) CUDA events of every aggregation launch are appended
+
+    def _timed(self, launch):
+        if self.event_sink is None:
+            return launch()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        launch()
+        b.record()
+        self.event_sink.append((a, b))
 
     @property
     def edges(self) -> int:
@@ -72,14 +82,14 @@ class Shard:
         return self._dinv
 
     def aggregate(self, out, sym, dim, knobs: Knobs, accumulate=False, row_scale_=None):
-        api.mgg_SAG_np_div(out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim,
-                           self.node_per_pe, self.pe, knobs.partSize, knobs.warpPerBlock,
-                           knobs.interleaved_dist, accumulate=accumulate, row_scale_=row_scale_)
+        self._timed(lambda: api.mgg_SAG_np_div(
+            out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim, self.node_per_pe, self.pe,
+            knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, accumulate=accumulate, row_scale_=row_scale_))
 
     def aggregate_gin(self, out, sym, dim, knobs: Knobs, eps: float):
-        api.mgg_GIN_np_div(out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim,
-                           self.node_per_pe, self.pe, knobs.partSize, knobs.warpPerBlock,
-                           knobs.interleaved_dist, eps)
+        self._timed(lambda: api.mgg_GIN_np_div(
+            out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim, self.node_per_pe, self.pe,
+            knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, eps))
 
 
 def nccl_stream_barrier(group=None) -> Callable[[], None]:

@@ -22,6 +22,18 @@ class _RawCudaBuffer:
             "shape": (numel,), "typestr": "<f4", "data": (ptr, False), "version": 3, "strides": None}
 
 
+def exchange_handles(handle: bytes, group, num_pes: int):
+    """All-gathers one 64-byte export handle per PE (index = PE).  Works on any backend."""
+    import torch.distributed as dist
+    if len(handle) != 64:
+        raise ValueError("an export handle is 64 bytes")
+    handles = [None] * num_pes
+    dist.all_gather_object(handles, handle, group=group)
+    if any(h is None or len(h) != 64 for h in handles):
+        raise RuntimeError("handle exchange returned a malformed handle")
+    return handles
+
+
 class SymmetricBuffer:
     """``numel`` fp32 elements on the current device, readable by every PE of ``group``.
 
@@ -41,11 +53,9 @@ class SymmetricBuffer:
         self.tensor = torch.as_tensor(self._raw, device=torch.device("cuda", torch.cuda.current_device()))
         self.peer_ptrs = [self.ptr]
         if num_pes > 1:
-            import torch.distributed as dist
             handle = C.create_string_buffer(64)
             check(lib.mggb_sym_export(C.c_void_p(self.ptr), handle))
-            handles = [None] * num_pes
-            dist.all_gather_object(handles, handle.raw, group=group)
+            handles = exchange_handles(handle.raw, group, num_pes)
             self.peer_ptrs = []
             for r, h in enumerate(handles):
                 if r == pe:

@@ -1,0 +1,156 @@
+"""Parity of the CUDA aggregation (through the C ABI) with the CPU oracle and the golden vectors."""
+import numpy as np
+import pytest
+import torch
+
+import mgg_osdi23_b200 as mgg
+from mgg_osdi23_b200 import drivers, graphgen as gg
+from gpu_util import RTOL, ATOL, emulated_aggregate, random_graph
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("G", [1, 2, 3, 8])
+@pytest.mark.parametrize("dim", [16, 5])
+def test_golden_vectors(golden, G, dim):
+    rp, col, x = golden["g_row_ptr"], golden["g_col"], golden[f"g_x{dim}"]
+    got = emulated_aggregate(rp, col, x, G)
+    np.testing.assert_allclose(got, golden[f"g_sag{dim}"], rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("G", [1, 2, 4])
+def test_all_ones_is_exact_degree(golden, G):
+    """The reference's only known-answer property: all-ones input gives the degree, exactly."""
+    rp, col = golden["g_row_ptr"], golden["g_col"]
+    ones = np.ones((len(rp) - 1, 16), np.float32)
+    got = emulated_aggregate(rp, col, ones, G)
+    assert np.array_equal(got, np.repeat(np.diff(rp)[:, None], 16, 1).astype(np.float32))
+    assert np.array_equal(got[:, :4], golden["g_sag_ones"])
+
+
+@pytest.mark.parametrize("dim", [1, 2, 4, 8, 12, 16, 32, 64, 100, 128, 200, 7, 33])
+@pytest.mark.parametrize("G", [1, 4])
+def test_widths(oracle, dim, G):
+    rp, col = random_graph(300, 20, seed=dim, hubs=[(5, 700), (17, 0), (299, 0)])
+    x = np.random.default_rng(dim).uniform(-1, 1, (300, dim)).astype(np.float32)
+    got = emulated_aggregate(rp, col, x, G)
+    np.testing.assert_allclose(got, oracle.sag_f64(x, rp, col), rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(got, oracle.sag_f32(x, rp, col), rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("ps", [1, 2, 4, 8, 16, 32])
+@pytest.mark.parametrize("wpb,dist", [(1, 1), (2, 16), (4, 2), (8, 4), (16, 1), (3, 3)])
+def test_knob_sweep(oracle, ps, wpb, dist):
+    """Every ps x (wpb, dist) point of the design-space sweep gives the same sums."""
+    rp, col = random_graph(200, 35, seed=1, hubs=[(0, 3000), (1, 1), (2, 0)])
+    x = np.random.default_rng(2).uniform(-1, 1, (200, 16)).astype(np.float32)
+    want = oracle.sag_f64(x, rp, col)
+    for G in (1, 2):
+        got = emulated_aggregate(rp, col, x, G, knobs=(ps, wpb, dist))
+        np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
+
+
+def test_accumulate_matches_reference_semantics(oracle, golden):
+    """The reference adds on top of the output buffer; two calls double the sum."""
+    rp, col, x = golden["g_row_ptr"], golden["g_col"], golden["g_x16"]
+    first = emulated_aggregate(rp, col, x, 2, accumulate=True)
+    second = emulated_aggregate(rp, col, x, 2, accumulate=True, init=first)
+    np.testing.assert_allclose(second, golden["g_sag_accum"], rtol=RTOL, atol=ATOL)
+    # overwrite mode ignores what was there
+    again = emulated_aggregate(rp, col, x, 2, accumulate=False, init=np.full_like(first, 7.0))
+    assert np.array_equal(again, first)
+
+
+@pytest.mark.parametrize("G", [1, 3])
+@pytest.mark.parametrize("eps", [0.0, 0.5])
+def test_gin_combine(oracle, G, eps):
+    rp, col = random_graph(257, 12, seed=4)
+    x = np.random.default_rng(5).uniform(-1, 1, (257, 64)).astype(np.float32)
+    got = emulated_aggregate(rp, col, x, G, gin_eps=eps)
+    want = oracle.sag_f64(x, rp, col).astype(np.float64) + (1.0 + eps) * x
+    np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
+
+
+def test_row_scale_and_symmetric_norm_config1(oracle):
+    """Config 1: one GCN aggregation with 1/sqrt(deg_i*deg_j) on the 16,384-node R-MAT graph, dim 16."""
+    g = gg.config1_graph()
+    rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
+    x = gg.features(g.num_nodes, 16, seed=0).numpy()
+    dinv = oracle.inv_sqrt_degree(rp)
+    want = oracle.row_scale(oracle.sag_f64(oracle.row_scale(x, dinv), rp, col), dinv)
+    for G in (1, 2):
+        got = emulated_aggregate(rp, col, oracle.row_scale(x, dinv), G, row_scale=dinv)
+        np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
+    # the device-side helpers produce the same factors
+    dev = torch.device("cuda")
+    sh = drivers.Shard(rp, col, 0, 1, device=dev)
+    np.testing.assert_allclose(sh.inv_sqrt_degree().cpu().numpy(), dinv, rtol=1e-6)
+    xs = torch.empty(g.num_nodes, 16, device=dev)
+    mgg.row_scale(xs, torch.from_numpy(x).to(dev), sh.inv_sqrt_degree())
+    np.testing.assert_allclose(xs.cpu().numpy(), oracle.row_scale(x, dinv), rtol=1e-6)
+
+
+def test_bit_reproducible_for_fixed_knobs():
+    rp, col = random_graph(500, 60, seed=9, hubs=[(3, 5000)])
+    x = np.random.default_rng(1).uniform(-1, 1, (500, 16)).astype(np.float32)
+    a = emulated_aggregate(rp, col, x, 2, knobs=(16, 4, 2))
+    b = emulated_aggregate(rp, col, x, 2, knobs=(16, 4, 2))
+    assert np.array_equal(a, b)
+
+
+def test_empty_graph_and_empty_shards():
+    rp = np.zeros(5, np.int32)
+    col = np.zeros(0, np.int32)
+    x = np.ones((4, 16), np.float32)
+    assert np.array_equal(emulated_aggregate(rp, col, x, 1), np.zeros((4, 16), np.float32))
+    # more PEs than nodes: trailing PEs own nothing
+    rp, col = random_graph(3, 2, seed=0)
+    x = np.random.default_rng(0).uniform(-1, 1, (3, 16)).astype(np.float32)
+    got = emulated_aggregate(rp, col, x, 8)
+    want = np.zeros_like(x)
+    for i in range(3):
+        for e in range(rp[i], rp[i + 1]):
+            want[i] += x[col[e]]
+    np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
+
+
+def test_errors_reported_not_fatal():
+    dev = torch.device("cuda")
+    rp, col = random_graph(8, 2, seed=0)
+    sh = drivers.Shard(rp, col, 0, 1, device=dev)
+    x = torch.zeros(8, 16, device=dev)
+    o = torch.zeros(8, 16, device=dev)
+    with pytest.raises(mgg.MggbError):
+        sh.aggregate(o, x, 16, drivers.Knobs(16, 64, 1))
+    with pytest.raises(mgg.MggbError):
+        sh.aggregate_gin(x, x, 16, drivers.Knobs(), 0.0)      # output aliases the input
+    with pytest.raises(ValueError):
+        sh.aggregate(o.cpu(), x, 16, drivers.Knobs())
+    sh.aggregate(o, x, 16, drivers.Knobs())                    # the context is still usable
+    torch.cuda.synchronize()
+
+
+def test_full_size_config2_properties():
+    """At the benchmark's full size (232,965 nodes, ~114.6 M edges, dim 16): all-ones input gives the
+    exact degree in every column, and the aggregation is linear (A(2x) = 2 A(x) bit for bit)."""
+    dev = torch.device("cuda")
+    g = gg.config2_graph(device=dev)
+    assert g.num_nodes == 232_965 and abs(g.num_edges - 114.6e6) / 114.6e6 < 0.02
+    sh = drivers.Shard(g.row_ptr.cpu().numpy(), g.col_idx.cpu().numpy(), 0, 1, device=dev)
+    deg = (g.row_ptr[1:] - g.row_ptr[:-1]).to(torch.float32)
+    ones = torch.ones(g.num_nodes, 16, device=dev)
+    out = torch.empty_like(ones)
+    sh.aggregate(out, ones, 16, drivers.Knobs(32, 4, 1))
+    assert torch.equal(out, deg[:, None].expand(-1, 16))
+    assert int(out[:, 0].double().sum().item()) == g.num_edges
+    x = gg.features(g.num_nodes, 16, seed=1, device=dev)
+    a, b = torch.empty_like(x), torch.empty_like(x)
+    sh.aggregate(a, x, 16, drivers.Knobs(32, 4, 1))
+    sh.aggregate(b, x * 2, 16, drivers.Knobs(32, 4, 1))
+    assert torch.equal(b, a * 2)
+    # spot rows against a float64 gather done with torch indexing (hub, median and tail rows)
+    order = torch.argsort(deg)
+    for r in [int(order[-1]), int(order[len(order) // 2]), int(order[0])]:
+        nb = g.col_idx[g.row_ptr[r]:g.row_ptr[r + 1]].long()
+        want = x[nb].double().sum(0)
+        torch.testing.assert_close(a[r].double(), want, rtol=RTOL, atol=ATOL)

@@ -1,0 +1,128 @@
+"""2-layer GCN / 5-layer GIN forward passes (several PEs emulated on one device) against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import mgg_osdi23_b200 as mgg
+from mgg_osdi23_b200 import drivers, graphgen as gg
+from gpu_util import RTOL, ATOL
+
+pytestmark = pytest.mark.gpu
+
+
+def _oracle_gcn2(oracle, rp, col, x, w1, w2, norm):
+    h = oracle.dense(x, w1)
+    if norm == "sym":
+        dinv = oracle.inv_sqrt_degree(rp)
+        agg = lambda t: oracle.row_scale(oracle.sag_f64(oracle.row_scale(t, dinv), rp, col), dinv)
+    else:
+        agg = lambda t: oracle.sag_f64(t, rp, col)
+    z = agg(agg(h))
+    logits = oracle.dense(z, w2)
+    return logits, oracle.softmax(logits)
+
+
+def _run_cluster(make_model, G, n, x):
+    models = [make_model(pe) for pe in range(G)]
+    for m in models:
+        m.d_in.copy_(torch.from_numpy(x[m.shard.lb:m.shard.ub]).to(m.d_in.device))
+    drivers.run_stages(models)
+    torch.cuda.synchronize()
+    out = np.zeros((n, models[0].out.shape[1]), np.float32)
+    logits = np.zeros_like(out)
+    for m in models:
+        out[m.shard.lb:m.shard.ub] = m.out.cpu().numpy()
+        logits[m.shard.lb:m.shard.ub] = m.logits.cpu().numpy()
+    return logits, out
+
+
+@pytest.mark.parametrize("G", [1, 2, 4])
+@pytest.mark.parametrize("norm", ["sym", "none"])
+def test_gcn2_forward(oracle, G, norm):
+    g = gg.chung_lu_graph(1500, 40_000, 2.1, seed=2, communities=4, p_intra=0.7)
+    rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
+    n, din, hid, dout = g.num_nodes, 602, 16, 41
+    x = gg.features(n, din, seed=3).numpy()
+    w1, w2 = gg.glorot_uniform(din, hid, 1), gg.glorot_uniform(hid, dout, 2)
+    if norm == "none":
+        w1 = w1 * 0.01          # keeps unnormalised sums of ~27^2 neighbors in a softmax-friendly range
+    dev = torch.device("cuda")
+    npp = (n + G - 1) // G
+    sa, sb = drivers.local_symmetric(G, npp * hid, dev), drivers.local_symmetric(G, npp * hid, dev)
+
+    def make(pe):
+        sh = drivers.Shard(rp, col, pe, G, device=dev)
+        return drivers.GCN2Forward(sh, din, hid, dout, sa[pe], sb[pe], drivers.Knobs(16, 4, 2),
+                                   w1=w1.to(dev), w2=w2.to(dev), norm=norm)
+
+    logits, probs = _run_cluster(make, G, n, x)
+    want_logits, want_probs = _oracle_gcn2(oracle, rp, col, x, w1.numpy(), w2.numpy(), norm)
+    np.testing.assert_allclose(logits, want_logits, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(probs, want_probs, rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("G", [1, 3])
+def test_gin5_forward(oracle, G):
+    g = gg.chung_lu_graph(1200, 12_000, 2.3, seed=5)
+    rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
+    n, din, hid, dout, eps = g.num_nodes, 100, 64, 47, 0.0
+    x = gg.features(n, din, seed=4).numpy()
+    # scaled so that five unnormalised aggregations stay O(1)
+    ws = [gg.glorot_uniform(din, hid, 10) * 0.1] + [gg.glorot_uniform(hid, hid, 11 + k) * 0.1 for k in range(4)] \
+        + [gg.glorot_uniform(hid, dout, 20) * 0.1]
+    dev = torch.device("cuda")
+    npp = (n + G - 1) // G
+    sa, sb = drivers.local_symmetric(G, npp * hid, dev), drivers.local_symmetric(G, npp * hid, dev)
+
+    def make(pe):
+        sh = drivers.Shard(rp, col, pe, G, device=dev)
+        return drivers.GIN5Forward(sh, din, hid, dout, sa[pe], sb[pe], drivers.Knobs(8, 2, 2), eps=eps,
+                                   weights=[w.to(dev) for w in ws])
+
+    logits, probs = _run_cluster(make, G, n, x)
+    h = oracle.dense(x, ws[0].numpy())
+    for k in range(5):
+        a = (oracle.sag_f64(h, rp, col).astype(np.float64) + (1 + eps) * h).astype(np.float32)
+        h = oracle.dense(a, ws[k + 1].numpy())
+    scale = max(1.0, float(np.abs(h).max()))
+    np.testing.assert_allclose(logits / scale, h / scale, rtol=1e-4, atol=ATOL)   # 11 chained fp32 kernels
+    np.testing.assert_allclose(probs, oracle.softmax(h), rtol=1e-3, atol=ATOL)
+
+
+def test_forward_host_entry_point(oracle):
+    """The host-buffer call: pinned features in, pinned probabilities out."""
+    g = gg.rmat_graph(9, 4000, seed=7)
+    rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
+    n = g.num_nodes
+    dev = torch.device("cuda")
+    sa, sb = drivers.local_symmetric(1, n * 16, dev), drivers.local_symmetric(1, n * 16, dev)
+    sh = drivers.Shard(rp, col, 0, 1, device=dev)
+    w1, w2 = gg.glorot_uniform(32, 16, 1), gg.glorot_uniform(16, 8, 2)
+    m = drivers.GCN2Forward(sh, 32, 16, 8, sa[0], sb[0], drivers.Knobs(), w1=w1.to(dev), w2=w2.to(dev), norm="sym")
+    x = gg.features(n, 32, seed=1).pin_memory()
+    probs = m.forward_host(x)
+    assert probs.is_pinned() and not probs.is_cuda
+    _, want = _oracle_gcn2(oracle, rp, col, x.numpy(), w1.numpy(), w2.numpy(), "sym")
+    np.testing.assert_allclose(probs.numpy(), want, rtol=RTOL, atol=ATOL)
+
+
+def test_single_aggregation_driver(oracle):
+    g = gg.config4_graph(scale_shift=9)
+    rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
+    n = g.num_nodes
+    dev = torch.device("cuda")
+    x = gg.features(n, 16, seed=2).numpy()
+    want = oracle.sag_f64(x, rp, col)
+    for G in (1, 4):
+        npp = (n + G - 1) // G
+        syms = drivers.local_symmetric(G, npp * 16, dev)
+        models = []
+        for pe in range(G):
+            sh = drivers.Shard(rp, col, pe, G, device=dev)
+            m = drivers.SingleAggregation(sh, 16, syms[pe], drivers.Knobs(4, 8, 4))
+            m.d_in.copy_(torch.from_numpy(x[sh.lb:sh.ub]).to(dev))
+            models.append(m)
+        drivers.run_stages(models)
+        torch.cuda.synchronize()
+        for m in models:
+            np.testing.assert_allclose(m.out.cpu().numpy(), want[m.shard.lb:m.shard.ub], rtol=RTOL, atol=ATOL)
