@@ -18,7 +18,26 @@
 //   * the warps' partial sums meet in shared memory and ONE thread group stores the output row.
 //     No atomics (:1456-1458 uses a spin on atomicExch), so the result is reproducible for fixed
 //     knobs, and the epilogue (accumulate / GIN combine / row scale) is applied exactly once.
+#include <algorithm>
 #include "common.h"
+
+// Compile-time tuning, per row width (LPR = lanes that read one row).  Chosen by measurement on
+// B200: narrow rows (dim <= 16) are served mostly from L2 and want many resident warps, so registers
+// are capped (3 blocks of 512 threads -> 40 registers); wide rows stream from HBM, run one batch
+// per node on typical graphs, and do better without the cap.  Prefetching the next batch of ids
+// paid off only below that occupancy, so it is off by default.
+//   MGGB_AGG_MIN_BLOCKS_NARROW  second argument of __launch_bounds__(512, .) for LPR <= 4
+//   MGGB_AGG_MAX_ROUNDS         load rounds issued back to back (rows in flight = rounds * 32/LPR)
+//   MGGB_AGG_PREFETCH_NARROW    1: request the next batch of neighbor ids before gathering the rows
+#ifndef MGGB_AGG_MIN_BLOCKS_NARROW
+#define MGGB_AGG_MIN_BLOCKS_NARROW 3
+#endif
+#ifndef MGGB_AGG_MAX_ROUNDS
+#define MGGB_AGG_MAX_ROUNDS 4
+#endif
+#ifndef MGGB_AGG_PREFETCH_NARROW
+#define MGGB_AGG_PREFETCH_NARROW 0
+#endif
 
 namespace {
 
@@ -68,55 +87,83 @@ template <> struct Vec<1> {
     __device__ __forceinline__ void store_smem(float* p) const { *p = v; }
 };
 
+// Adds the rows of up to 32 neighbors (ids held one per lane in `my`, -1 = none) into acc.
+// FULL: all 32 ids are valid, so no per-row predicate is needed.
+template <int LPR, int VEC, bool REMOTE, bool FULL>
+__device__ __forceinline__ void gather_batch(Vec<VEC>& acc, const AggParams& P, const float* const* s_peer,
+                                             const char* lbase, unsigned row_bytes, int my, int cnt,
+                                             int g, int col, bool col_ok) {
+    constexpr int G = 32 / LPR;             // neighbor rows per load round
+    constexpr int U = LPR < MGGB_AGG_MAX_ROUNDS ? LPR : MGGB_AGG_MAX_ROUNDS;  // rounds issued back to back
+#pragma unroll 1
+    for (int r0 = 0; r0 < LPR; r0 += U) {
+        if (!FULL && r0 * G >= cnt) break;
+        Vec<VEC> v[U];
+        bool ok[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int got = __shfl_sync(0xffffffffu, my, (r0 + u) * G + g);
+            ok[u] = col_ok && (FULL || got >= 0);
+            const int nid = FULL ? got : max(got, 0);   // absent lanes hold -1: keep every address and the owner index in range
+            const float* src;
+            if (REMOTE) {
+                const unsigned owner = (unsigned)(((unsigned long long)(unsigned)nid * P.div_magic) >> P.div_shift);
+                const int row = nid - (int)owner * P.node_per_pe;
+                src = s_peer[owner] + (long long)row * P.dim + col;
+            } else {
+                src = reinterpret_cast<const float*>(lbase + (long long)nid * row_bytes);
+            }
+            if (ok[u]) v[u].load(src);
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (ok[u]) acc.add(v[u]);
+    }
+}
+
 // Gathers the edges [beg, end) of one neighbor list that belong to this warp and adds their rows
 // (columns [col, col+VEC) of each) into acc.  REMOTE selects the owner lookup.
+// The warp's share is walked as a sequence of batches of up to 32 ids: chunk q of the warp starts
+// at beg + (q*nwarps + warp)*chunk.  The ids of batch t+1 are requested before the rows of batch t
+// are gathered, so the id fetch (from HBM) overlaps the row fetch (mostly from L2).
 template <int LPR, int VEC, bool REMOTE>
 __device__ __forceinline__ void gather_list(Vec<VEC>& acc, const AggParams& P, const float* const* s_peer,
                                             const int32_t* __restrict__ ci, int beg, int end,
                                             int warp, int nwarps, int lane, int col, bool col_ok) {
-    constexpr int G = 32 / LPR;             // neighbor rows per load round
-    constexpr int U = LPR < 8 ? LPR : 8;    // rounds issued back to back (loads in flight = U*G rows)
+    constexpr bool PREFETCH = (LPR <= 4) && MGGB_AGG_PREFETCH_NARROW;
     const int g = lane / LPR;
-    const float* self_base = P.peer[P.pe];
-    const long long block_stride = (long long)P.chunk * nwarps;
-    for (long long b_beg = beg; b_beg < end; b_beg += block_stride) {
-        const long long w_beg = b_beg + (long long)warp * P.chunk;
-        if (w_beg >= end) break;
-        const int w_end = (int)min((long long)end, w_beg + P.chunk);
-        for (int base = (int)w_beg; base < w_end; base += 32) {
-            const int cnt = min(32, w_end - base);
-            // one coalesced read of up to 32 neighbor ids; streamed, they are used once
-            const int my = (lane < cnt) ? __ldcs(ci + base + lane) : -1;
-#pragma unroll 1
-            for (int r0 = 0; r0 < LPR; r0 += U) {
-                if (r0 * G >= cnt) break;
-                Vec<VEC> v[U];
-#pragma unroll
-                for (int u = 0; u < U; u++) {
-                    const int nid = __shfl_sync(0xffffffffu, my, (r0 + u) * G + g);
-                    v[u].zero();
-                    if (nid >= 0 && col_ok) {
-                        const float* src;
-                        if (REMOTE) {
-                            const unsigned owner = (unsigned)(((unsigned long long)(unsigned)nid * P.div_magic) >> P.div_shift);
-                            const int row = nid - (int)owner * P.node_per_pe;
-                            src = s_peer[owner] + (long long)row * P.dim + col;
-                        } else {
-                            src = self_base + (long long)(nid - P.lb) * P.dim + col;
-                        }
-                        v[u].load(src);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < U; u++) acc.add(v[u]);
-            }
+    const unsigned row_bytes = (unsigned)P.dim * 4u;
+    // local rows: address = lbase + id * row_bytes (the shard's first id, lb, is folded into lbase)
+    const char* lbase = reinterpret_cast<const char*>(P.peer[P.pe] + col) - (long long)P.lb * row_bytes;
+    // Edge positions fit 32 bits (a shard half has < 2^31 edges and the chunk is clamped to 2^24),
+    // so the walk uses unsigned arithmetic.
+    const unsigned uend = (unsigned)end, chunk = (unsigned)P.chunk;
+    const unsigned block_stride = chunk * (unsigned)nwarps;
+    unsigned cstart = (unsigned)beg + (unsigned)warp * chunk;         // start of the current chunk
+    if (cstart >= uend) return;
+    unsigned r = 0;                                                   // offset of the batch in its chunk
+    int cnt = (int)min(32u, min(chunk, uend - cstart));
+    int my = (lane < cnt) ? __ldcs(ci + cstart + lane) : -1;
+    while (true) {
+        unsigned ncs = cstart, nr = r + 32;
+        if (nr >= chunk || ncs + nr >= uend) { ncs += block_stride; nr = 0; }
+        const bool more = ncs < uend;
+        int ncnt = 0, nxt = -1;
+        if (more) {
+            ncnt = (int)min(32u, min(chunk - nr, uend - (ncs + nr)));
+            if (PREFETCH && lane < ncnt) nxt = __ldcs(ci + ncs + nr + lane);
         }
+        if (cnt == 32) gather_batch<LPR, VEC, REMOTE, true>(acc, P, s_peer, lbase, row_bytes, my, cnt, g, col, col_ok);
+        else           gather_batch<LPR, VEC, REMOTE, false>(acc, P, s_peer, lbase, row_bytes, my, cnt, g, col, col_ok);
+        if (!more) break;
+        if (!PREFETCH && lane < ncnt) nxt = __ldcs(ci + ncs + nr + lane);
+        cstart = ncs; r = nr; cnt = ncnt; my = nxt;
     }
 }
 
 // One block per node.  Dynamic shared memory: nwarps * dim floats (the warps' partial rows).
-template <int LPR, int VEC>
-__global__ void __launch_bounds__(512) sag_np_div_kernel(const AggParams P) {
+template <int LPR, int VEC, bool EXACT, bool HAS_REMOTE>
+__global__ void __launch_bounds__(512, (LPR <= 4 ? MGGB_AGG_MIN_BLOCKS_NARROW : 1)) sag_np_div_kernel(const AggParams P) {
     extern __shared__ __align__(16) float s_part[];
     __shared__ const float* s_peer[MGGB_MAX_PES];
 
@@ -131,13 +178,13 @@ __global__ void __launch_bounds__(512) sag_np_div_kernel(const AggParams P) {
     const int l = lane % LPR;
     constexpr int COLS = LPR * VEC;  // columns covered per pass
 
-    for (int cb = 0; cb < P.dim; cb += COLS) {
+    for (int cb = 0; cb < (EXACT ? 1 : P.dim); cb += COLS) {
         const int col = cb + l * VEC;
-        const bool col_ok = col < P.dim;
+        const bool col_ok = EXACT || col < P.dim;
         Vec<VEC> acc;
         acc.zero();
         gather_list<LPR, VEC, false>(acc, P, s_peer, P.ci_l, lbeg, lend, warp, nwarps, lane, col, col_ok);
-        if (rend > rbeg)
+        if (HAS_REMOTE && rend > rbeg)
             gather_list<LPR, VEC, true>(acc, P, s_peer, P.ci_r, rbeg, rend, warp, nwarps, lane, col, col_ok);
         // fold the 32/LPR sub-warps together
 #pragma unroll
@@ -168,12 +215,30 @@ void make_divider(uint32_t d, unsigned long long* magic, int* shift) {
     *magic = (unsigned long long)(((one << *shift) + d - 1) / d);
 }
 
+template <int LPR, int VEC, bool EXACT>
+int launch_exact(const AggParams& P, int wpb, cudaStream_t st);
+template <int LPR, int VEC, bool EXACT, bool HAS_REMOTE>
+int launch_kernel(const AggParams& P, int wpb, cudaStream_t st);
+
 template <int LPR, int VEC>
 int launch(const AggParams& P, int wpb, cudaStream_t st) {
+    if (P.dim == LPR * VEC) return launch_exact<LPR, VEC, true>(P, wpb, st);
+    return launch_exact<LPR, VEC, false>(P, wpb, st);
+}
+
+// A single PE has no remote half: that instantiation drops the owner lookup altogether.
+template <int LPR, int VEC, bool EXACT>
+int launch_exact(const AggParams& P, int wpb, cudaStream_t st) {
+    if (P.num_pes > 1) return launch_kernel<LPR, VEC, EXACT, true>(P, wpb, st);
+    return launch_kernel<LPR, VEC, EXACT, false>(P, wpb, st);
+}
+
+template <int LPR, int VEC, bool EXACT, bool HAS_REMOTE>
+int launch_kernel(const AggParams& P, int wpb, cudaStream_t st) {
     const size_t smem = (size_t)wpb * P.dim * sizeof(float);
     if (smem > 48 * 1024)
-        MGGB_CUDA(cudaFuncSetAttribute(sag_np_div_kernel<LPR, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    sag_np_div_kernel<LPR, VEC><<<P.num_rows, wpb * 32, smem, st>>>(P);
+        MGGB_CUDA(cudaFuncSetAttribute(sag_np_div_kernel<LPR, VEC, EXACT, HAS_REMOTE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    sag_np_div_kernel<LPR, VEC, EXACT, HAS_REMOTE><<<P.num_rows, wpb * 32, smem, st>>>(P);
     MGGB_CUDA(cudaGetLastError());
     return MGGB_OK;
 }
@@ -205,7 +270,7 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
     P.row_scale = row_scale;
     P.lb = lb; P.num_rows = ub - lb; P.node_per_pe = node_per_pe;
     P.dim = dim; P.pe = pe; P.num_pes = num_pes;
-    P.chunk = ps * dist;
+    P.chunk = (int)std::min<long long>((long long)ps * dist, 1 << 24);  // larger than any useful chunk: same walk
     make_divider((uint32_t)node_per_pe, &P.div_magic, &P.div_shift);
     P.mode = mode; P.self_scale = self_scale;
 

@@ -1,0 +1,51 @@
+// MGG_np_div_gin_mem: 5-layer GIN forward, 100 timed passes.
+// Same command line and stdout lines as the reference's src/mgg_np_div_gin_mem.cu; eps = 0.5 as
+// hard-coded there (:49).  Pass = dense(dim->hidden) | 5 x [GIN aggregate(hidden), dense] | softmax,
+// the last dense mapping hidden->outdim.  Publishing alternates between two symmetric buffers.
+#include "cli_common.hpp"
+
+int main(int argc, char* argv[]) {
+    if (argc >= 2) std::cout << "Graph File: " << argv[1] << '\n';
+    cli::Args a = cli::parse(argc, argv);
+    const float eps = 0.5f;
+    const int layers = 5;
+    cli::Graph g = cli::load_graph(a);
+    cli::Cluster c = cli::make_cluster(a, g);
+    const int G = a.num_GPUs;
+    cli::Symmetric sym[2] = {cli::alloc_symmetric(c, (size_t)c.pes[0].nodesPerPE * a.hiddenSize),
+                             cli::alloc_symmetric(c, (size_t)c.pes[0].nodesPerPE * a.hiddenSize)};
+    std::vector<const float*> table[2] = {sym[0].table(), sym[1].table()};
+    std::vector<float*> d_in(G), d_agg(G), d_logit(G);
+    std::vector<dense_param_new_beg*> dp1(G);
+    std::vector<std::vector<dense_param_new_hidden*>> dph(G);
+    std::vector<softmax_new_param*> smx(G);
+    for (auto& p : c.pes) {
+        d_in[p.pe] = cli::alloc_filled(c, p, (size_t)p.nodesPerPE * a.dim, 1.0f);
+        d_agg[p.pe] = cli::alloc_filled(c, p, (size_t)p.nodesPerPE * a.hiddenSize, 0.0f);
+        d_logit[p.pe] = cli::alloc_filled(c, p, (size_t)p.nodesPerPE * a.outdim, 0.0f);
+        dp1[p.pe] = new dense_param_new_beg("d-1", d_in[p.pe], sym[0].ptr[p.pe], p.rows(), a.dim, a.hiddenSize);
+        for (int k = 1; k < layers; k++)
+            dph[p.pe].push_back(new dense_param_new_hidden("d-h", d_agg[p.pe], sym[k % 2].ptr[p.pe], p.rows(), a.hiddenSize, a.hiddenSize));
+        dph[p.pe].push_back(new dense_param_new_hidden("d-o", d_agg[p.pe], d_logit[p.pe], p.rows(), a.hiddenSize, a.outdim));
+        smx[p.pe] = new softmax_new_param("smx", d_logit[p.pe], d_logit[p.pe], p.rows(), a.outdim);
+    }
+    auto pass = [&]() {
+        for (auto& p : c.pes) { c.use(p); if (p.rows()) dense_beg_new_forward(dp1[p.pe], p.stream); }
+        for (int k = 0; k < layers; k++) {
+            c.barrier();
+            for (auto& p : c.pes) {
+                c.use(p);
+                if (!p.rows()) continue;
+                MGG_COMPAT_CHECK(mggb_gin_np_div(d_agg[p.pe], table[k % 2].data(), G, p.rp_l, p.ci_l, p.rp_r, p.ci_r,
+                                                 (int32_t)p.lb, (int32_t)p.ub, a.hiddenSize, (int32_t)p.nodesPerPE, p.pe,
+                                                 a.partSize, a.warpPerBlock, a.interleaved_dist, eps, 0, p.stream));
+                dense_hidden_new_forward(dph[p.pe][k], p.stream);
+                if (k == layers - 1) softmax_new_forward(smx[p.pe], p.stream);
+            }
+        }
+        c.barrier();
+    };
+    double ms = cli::time_loop(c, 100, 10, pass);
+    cli::report(c, a, g, ms, layers, a.hiddenSize);
+    return 0;
+}

@@ -1,0 +1,52 @@
+// MGG_np_div_kernel: ONE neighbor aggregation at width `hidden`, 100 timed launches: what the
+// reference's partition-size / warps-per-block / interleave-distance sweeps run
+// (src/mgg_np_div_kernel.cu:183-188; bench_MGG_DSE_dist_ps.py:28).  Same command line.
+// Its input is a symmetric buffer filled with 1.0 (the reference leaves it zero-filled); with
+// MGG_VALIDATE=1 in the environment the result is checked against the node degrees, exactly.
+#include "cli_common.hpp"
+
+int main(int argc, char* argv[]) {
+    if (argc >= 2) std::cout << "Graph File: " << argv[1] << '\n';
+    cli::Args a = cli::parse(argc, argv);
+    cli::Graph g = cli::load_graph(a);
+    cli::Cluster c = cli::make_cluster(a, g);
+    const int G = a.num_GPUs;
+    const size_t floats = (size_t)c.pes[0].nodesPerPE * a.hiddenSize;
+    cli::Symmetric sym = cli::alloc_symmetric(c, floats);
+    auto table = sym.table();
+    std::vector<float*> d_out(G);
+    for (auto& p : c.pes) {
+        c.use(p);
+        std::vector<float> ones(std::max<size_t>(floats, 4), 1.0f);
+        CLI_CUDA(cudaMemcpy(sym.ptr[p.pe], ones.data(), ones.size() * sizeof(float), cudaMemcpyHostToDevice));
+        d_out[p.pe] = cli::alloc_filled(c, p, floats, 0.0f);
+    }
+    auto pass = [&]() {
+        for (auto& p : c.pes) {
+            c.use(p);
+            if (!p.rows()) continue;
+            MGG_COMPAT_CHECK(mggb_sag_np_div(d_out[p.pe], table.data(), G, p.rp_l, p.ci_l, p.rp_r, p.ci_r, (int32_t)p.lb,
+                                             (int32_t)p.ub, a.hiddenSize, (int32_t)p.nodesPerPE, p.pe, a.partSize,
+                                             a.warpPerBlock, a.interleaved_dist, nullptr, 0, p.stream));
+        }
+        c.barrier();
+    };
+    double ms = cli::time_loop(c, 100, 10, pass);
+    const char* v = getenv("MGG_VALIDATE");
+    if (v && atoi(v)) {
+        bool ok = true;
+        for (auto& p : c.pes) {
+            c.use(p);
+            std::vector<float> h((size_t)p.rows() * a.hiddenSize);
+            CLI_CUDA(cudaMemcpy(h.data(), d_out[p.pe], h.size() * sizeof(float), cudaMemcpyDeviceToHost));
+            for (int r = 0; r < p.rows() && ok; r++) {
+                const float deg = (float)(g.row_ptr[p.lb + r + 1] - g.row_ptr[p.lb + r]);
+                for (int d = 0; d < a.hiddenSize; d++)
+                    if (h[(size_t)r * a.hiddenSize + d] != deg) { printf("[%d] ref: %.3f -- out: %.3f\n", r, deg, h[(size_t)r * a.hiddenSize + d]); ok = false; break; }
+            }
+        }
+        printf("Validation status: %s\n", ok ? "True" : "False");
+    }
+    cli::report(c, a, g, ms, 1, a.hiddenSize);
+    return 0;
+}

@@ -1,0 +1,52 @@
+// MGG_np_div_mem: 2-layer GCN forward, 100 timed passes.
+// Same command line and stdout lines as the reference's src/mgg_np_div_mem.cu:
+//   MGG_np_div_mem beg_file csr_file weight_file num_GPUs partSize warpPerBlock interleaved_dist dim hidden outdim
+// Pass = dense(dim->hidden) | aggregate(hidden) | aggregate(hidden), dense(hidden->outdim), softmax;
+// "|" marks where every PE waits for its peers.  Inputs and weights are all 1.0 as in the reference
+// (:128, include/layer_new.cuh:307).
+#include "cli_common.hpp"
+
+int main(int argc, char* argv[]) {
+    if (argc >= 2) std::cout << "Graph File: " << argv[1] << '\n';
+    cli::Args a = cli::parse(argc, argv);
+    cli::Graph g = cli::load_graph(a);
+    cli::Cluster c = cli::make_cluster(a, g);
+    const int G = a.num_GPUs;
+    cli::Symmetric sym_a = cli::alloc_symmetric(c, (size_t)c.pes[0].nodesPerPE * a.hiddenSize);
+    cli::Symmetric sym_b = cli::alloc_symmetric(c, (size_t)c.pes[0].nodesPerPE * a.hiddenSize);
+    std::vector<float*> d_in(G), d_agg(G), d_logit(G);
+    std::vector<dense_param_new_beg*> dp1(G);
+    std::vector<dense_param_new_hidden*> dp2(G);
+    std::vector<softmax_new_param*> smx(G);
+    auto ta = sym_a.table(), tb = sym_b.table();
+    for (auto& p : c.pes) {
+        d_in[p.pe] = cli::alloc_filled(c, p, (size_t)p.nodesPerPE * a.dim, 1.0f);
+        d_agg[p.pe] = cli::alloc_filled(c, p, (size_t)p.nodesPerPE * a.hiddenSize, 0.0f);
+        d_logit[p.pe] = cli::alloc_filled(c, p, (size_t)p.nodesPerPE * a.outdim, 0.0f);
+        dp1[p.pe] = new dense_param_new_beg("d-1", d_in[p.pe], sym_a.ptr[p.pe], p.rows(), a.dim, a.hiddenSize);
+        dp2[p.pe] = new dense_param_new_hidden("d-2", d_agg[p.pe], d_logit[p.pe], p.rows(), a.hiddenSize, a.outdim);
+        smx[p.pe] = new softmax_new_param("smx-2", d_logit[p.pe], d_logit[p.pe], p.rows(), a.outdim);
+    }
+    auto agg = [&](cli::PE& p, float* out, const std::vector<const float*>& table) {
+        MGG_COMPAT_CHECK(mggb_sag_np_div(out, table.data(), G, p.rp_l, p.ci_l, p.rp_r, p.ci_r, (int32_t)p.lb, (int32_t)p.ub,
+                                         a.hiddenSize, (int32_t)p.nodesPerPE, p.pe, a.partSize, a.warpPerBlock,
+                                         a.interleaved_dist, nullptr, 0, p.stream));
+    };
+    auto pass = [&]() {
+        for (auto& p : c.pes) { c.use(p); if (p.rows()) dense_beg_new_forward(dp1[p.pe], p.stream); }
+        c.barrier();
+        for (auto& p : c.pes) { c.use(p); if (p.rows()) agg(p, sym_b.ptr[p.pe], ta); }
+        c.barrier();
+        for (auto& p : c.pes) {
+            c.use(p);
+            if (!p.rows()) continue;
+            agg(p, d_agg[p.pe], tb);
+            dense_hidden_new_forward(dp2[p.pe], p.stream);
+            softmax_new_forward(smx[p.pe], p.stream);
+        }
+        c.barrier();
+    };
+    double ms = cli::time_loop(c, 100, 10, pass);
+    cli::report(c, a, g, ms, 2, a.hiddenSize);
+    return 0;
+}

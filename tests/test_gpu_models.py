@@ -126,3 +126,21 @@ def test_single_aggregation_driver(oracle):
         torch.cuda.synchronize()
         for m in models:
             np.testing.assert_allclose(m.out.cpu().numpy(), want[m.shard.lb:m.shard.ub], rtol=RTOL, atol=ATOL)
+
+
+def test_symmetric_buffer_single_pe():
+    """The library-allocated symmetric buffer viewed as a torch tensor, used as aggregation input."""
+    from mgg_osdi23_b200.symmem import SymmetricBuffer
+    dev = torch.device("cuda")
+    s = SymmetricBuffer(64 * 16)
+    assert s.tensor.is_cuda and s.tensor.numel() == 64 * 16 and s.tensor.data_ptr() == s.ptr
+    assert float(s.tensor.abs().sum()) == 0.0            # zero-filled like the reference's buffers
+    s.view(64, 16).fill_(1.0)
+    rp = np.arange(0, 65 * 3, 3, dtype=np.int32)
+    col = (np.arange(64 * 3) % 64).astype(np.int32)
+    sh = drivers.Shard(rp, col, 0, 1, device=dev)
+    out = torch.zeros(64, 16, device=dev)
+    sh.aggregate(out, s, 16, drivers.Knobs())
+    torch.cuda.synchronize()
+    assert torch.equal(out, torch.full_like(out, 3.0))
+    s.close()
