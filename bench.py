@@ -40,6 +40,10 @@ def parse_args():
     ap.add_argument("--ps", type=int, default=None)
     ap.add_argument("--wpb", type=int, default=None)
     ap.add_argument("--dist", type=int, default=None)
+    ap.add_argument("--fetch", default="auto", choices=["auto", "peer", "replica"],
+                    help="how peers see a layer's output: 'peer' = rows pulled from the owner inside the aggregation "
+                         "kernel; 'replica' = rows pushed into every PE's copy by the producing kernel; 'auto' = replica "
+                         "when there are peers and the copy fits")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -243,11 +247,12 @@ def build_weights(cfg, device):
 # -------------------------------------------------------------------------------------------------
 
 def run_ours(args, rank, world, local_rank):
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # only a one-element all-reduce goes through NCCL
     import numpy as np
     import torch
     import torch.distributed as dist
     from mgg_osdi23_b200 import drivers, graphgen as gg
-    from mgg_osdi23_b200.symmem import SymmetricBuffer
+    from mgg_osdi23_b200.symmem import SymmetricBuffer, ReplicaBuffer
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py --impl ours needs a CUDA device (there is no CPU path)")
@@ -270,8 +275,17 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.empty_cache()
 
     npp = shard.node_per_pe
-    sym_a = SymmetricBuffer(npp * hid, group, rank, world)
-    sym_b = SymmetricBuffer(npp * hid, group, rank, world)
+    fetch = args.fetch
+    if fetch == "auto":
+        fetch = "replica" if world > 1 and model_kind != "agg" and world * npp * hid * 4 < (8 << 30) else "peer"
+    if fetch == "replica" and model_kind == "agg":
+        raise SystemExit("--fetch replica needs a producing layer in front of the aggregation; the single-aggregation configs pull from peers")
+    if fetch == "replica":
+        sym_a = ReplicaBuffer(npp, hid, group, rank, world)
+        sym_b = ReplicaBuffer(npp, hid, group, rank, world)
+    else:
+        sym_a = SymmetricBuffer(npp * hid, group, rank, world)
+        sym_b = SymmetricBuffer(npp * hid, group, rank, world)
     weights = build_weights(args.config, dev)
     norm = "sym" if model_kind == "gcn2" or args.config == "cfg1" else "none"
     if model_kind == "gcn2":
@@ -322,6 +336,9 @@ def run_ours(args, rank, world, local_rank):
     step_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     agg_ms_local = sum(a.elapsed_time(b) for a, b in agg_events) / max(1, len(agg_events))
     agg_ms = max_over_ranks(agg_ms_local)
+    nsite = model.aggregations_per_forward
+    agg_ms_by_site = [max_over_ranks(sum(a.elapsed_time(b) for a, b in agg_events[s::nsite]) / max(1, len(agg_events[s::nsite])))
+                      for s in range(nsite)]
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end through the host-buffer entry point ---------------------------------------
@@ -364,9 +381,10 @@ def run_ours(args, rank, world, local_rank):
                                       model_kind, din, hid, dout, knobs, world),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
                          "traffic": None, "peak_source": f"of {hbm_src}", "kernel": "sag_np_div_kernel",
-                         "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": agg_ms,
+                         "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": agg_ms, "kernel_ms_by_call_site": agg_ms_by_site,
                          "aggregation_roofline_ms": t_roof * 1e3, "aggregation_roofline_frac": t_roof * 1e3 / agg_ms,
                          "nvlink_gbs_assumed": NVLINK_GBS},
+            "fetch": fetch,
             "per_gpu_edges": [{"local": el, "remote": er, "rows": r} for el, er, r in allstats],
             "remote_fraction": sum(er for _, er, _ in allstats) / max(1, total_edges),
             "gpu_launches": args.steps * model.kernels_per_forward * world,

@@ -120,7 +120,7 @@ inline void mgg_SAG_np_div(float* output, const float* input, const nidType* row
     if (!mgg_compat::lookup(input, table)) { table = {input}; pe = 0; }
     int st = mggb_sag_np_div(output, table.data(), (int)table.size(), row_pointers_l, column_index_l, row_pointers_r,
                              column_index_r, lb, ub, dim, nodePerPE, pe, np_size, warpPerBlock, interleaved_dist,
-                             nullptr, MGGB_AGG_ACCUMULATE, nullptr);
+                             nullptr, MGGB_AGG_ACCUMULATE, nullptr, 0, nullptr);
     cudaError_t error = (st == MGGB_OK) ? cudaDeviceSynchronize() : cudaSuccess;
     if (st != MGGB_OK || error != cudaSuccess) {
         printf("CUDA error @mgg_SAG_np_div_cuda: %s\n", st != MGGB_OK ? mggb_last_error() : cudaGetErrorString(error));
@@ -201,10 +201,10 @@ public:
 };
 
 inline void dense_beg_new_forward(dense_param_new_beg* dp, cudaStream_t stream = nullptr) {
-    MGG_COMPAT_CHECK(mggb_dense_forward(dp->d_out, dp->d_in, dp->d_W, dp->numNodes, dp->dim1, dp->dim2, nullptr, 0, stream));
+    MGG_COMPAT_CHECK(mggb_dense_forward(dp->d_out, dp->d_in, dp->d_W, dp->numNodes, dp->dim1, dp->dim2, nullptr, 0, nullptr, 0, stream));
 }
 inline void dense_hidden_new_forward(dense_param_new_hidden* dp, cudaStream_t stream = nullptr) {
-    MGG_COMPAT_CHECK(mggb_dense_forward(dp->d_out, dp->d_in, dp->d_W, dp->numNodes, dp->dim1, dp->dim2, nullptr, 0, stream));
+    MGG_COMPAT_CHECK(mggb_dense_forward(dp->d_out, dp->d_in, dp->d_W, dp->numNodes, dp->dim1, dp->dim2, nullptr, 0, nullptr, 0, stream));
 }
 inline void softmax_new_forward(softmax_new_param* smx, cudaStream_t stream = nullptr) {
     MGG_COMPAT_CHECK(mggb_softmax_forward(smx->d_out, smx->d_in, smx->numNodes, smx->dim, stream));

@@ -35,8 +35,12 @@ enum {
 
 /* Flags of the aggregation entry points. */
 enum {
-    MGGB_AGG_ACCUMULATE = 1 /* out += sum (what the reference does, include/neighbor_utils.cuh:1456-1458);
-                               without it out = sum, which needs no zero-fill between passes */
+    MGGB_AGG_ACCUMULATE = 1, /* out += sum (what the reference does, include/neighbor_utils.cuh:1456-1458);
+                                without it out = sum, which needs no zero-fill between passes */
+    MGGB_AGG_NO_HUB_SPLIT = 2 /* keep every node on its own warp_per_block-warp block, as the reference does.
+                                 By default a node with more than max(16384, 64*ps*dist*wpb) neighbors is passed,
+                                 through a work list in library-owned device memory (allocated once per device
+                                 and stream, on first use), to a second kernel that gives it a 16-warp block */
 };
 
 /* Flags of mggb_dense_forward. */
@@ -119,6 +123,13 @@ int mggb_enable_peer_access(int device, int peer_device);    /* MGGB_ERR_PEER if
  *   row_scale   NULL, or [ub-lb] factors applied to each output row before it is stored (used for
  *               symmetric normalisation; not in the reference)
  *   flags       MGGB_AGG_*
+ *   publish_out HOST array of num_publish device pointers (NULL / 0 for none): every output row is
+ *               ALSO stored at publish_out[k] + row*dim for each k, whichever device that memory is
+ *               on.  This is how a layer's result is pushed into the peers' replicas of the embedding
+ *               matrix from the kernel's epilogue, with no separate all-gather pass (the reference
+ *               has no counterpart: its peers pull rows one neighbor at a time).  Peers may read
+ *               them in kernels launched after this kernel has finished (i.e. after a barrier that
+ *               follows it in stream order).
  * Results do not depend on ps/wpb/dist except through fp32 summation order; for fixed knobs they
  * are bit-reproducible (one writer per output row, no atomics). */
 int mggb_sag_np_div(float* output, const float* const* peer_input, int num_pes,
@@ -126,7 +137,8 @@ int mggb_sag_np_div(float* output, const float* const* peer_input, int num_pes,
                     const int32_t* row_ptr_r, const int32_t* col_idx_r,
                     int32_t lb, int32_t ub, int dim, int32_t node_per_pe, int pe,
                     int part_size, int warp_per_block, int interleaved_dist,
-                    const float* row_scale, int flags, void* stream);
+                    const float* row_scale, int flags,
+                    float* const* publish_out, int num_publish, void* stream);
 
 /* Replaces mgg_GIN_np_div (launcher include/neighbor_utils.cuh:902-958, kernel :1554-1667):
  * output[b,:] = (1+eps) * x_self[b,:] + sum, where x_self is this PE's own symmetric buffer
@@ -143,11 +155,12 @@ int mggb_gin_np_div(float* output, const float* const* peer_input, int num_pes,
  * parameter structs of include/layer_new.cuh:272-393: row-major out[n, dim2] = x[n, dim1] * w[dim1, dim2],
  * alpha = 1, beta = 0, no bias.  The reference's call passes d_out as the B operand and never reads
  * d_in; this function computes the intended product from x.  row_scale (NULL or [n]) multiplies
- * output row i.  Precision: fp32-equivalent by default (3-pass split on the tensor cores, or the
+ * output row i; publish_out / num_publish as for mggb_sag_np_div.  Precision: fp32-equivalent by default (3-pass split on the tensor cores, or the
  * CUDA-core kernel); MGGB_DENSE_TF32 selects one TF32 pass. */
 int mggb_dense_forward(float* out, const float* x, const float* w,
                        int64_t n, int dim1, int dim2,
-                       const float* row_scale, int flags, void* stream);
+                       const float* row_scale, int flags,
+                       float* const* publish_out, int num_publish, void* stream);
 
 /* Replaces softmax_new_forward (include/gnn_layer.cuh:36-40; descriptors include/layer_new.cuh:80-85):
  * max-subtracted softmax over the dim classes of each row; in and out may alias. */

@@ -54,10 +54,10 @@ SIGNATURES = {
     "mggb_sym_close": [_vp],
     "mggb_enable_peer_access": [_int, _int],
     "mggb_sag_np_div": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
-                        _int, _int, _int, _vp, _int, _vp],
+                        _int, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp],
     "mggb_gin_np_div": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
                         _int, _int, _int, _f, _int, _vp],
-    "mggb_dense_forward": [_vp, _vp, _vp, _i64, _int, _int, _vp, _int, _vp],
+    "mggb_dense_forward": [_vp, _vp, _vp, _i64, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp],
     "mggb_softmax_forward": [_vp, _vp, _i64, _int, _vp],
     "mggb_row_scale": [_vp, _vp, _vp, _i64, _int, _vp],
     "mggb_inv_sqrt_degree": [_vp, _vp, _vp, _i64, _vp],

@@ -71,6 +71,14 @@ def _peer_table(input_) -> tuple:
     return (C.c_void_p * len(ptrs))(*ptrs), len(ptrs)
 
 
+def _publish_table(publish):
+    """None, or a sequence of tensors / raw device addresses that also receive every output row."""
+    if not publish:
+        return None, 0
+    ptrs = [p.data_ptr() if isinstance(p, torch.Tensor) else int(p) for p in publish]
+    return (C.c_void_p * len(ptrs))(*ptrs), len(ptrs)
+
+
 # ---- partitioner --------------------------------------------------------------------------------
 
 def shard_range(num_nodes: int, num_gpus: int, pe: int):
@@ -125,19 +133,21 @@ def build_part(name: str, indptr, num_nodes: int, partSize: int, exact_sentinel:
 
 def mgg_SAG_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r, column_index_r,
                    lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist,
-                   *, accumulate: bool = True, row_scale_: torch.Tensor | None = None):
+                   *, accumulate: bool = True, row_scale_: torch.Tensor | None = None, publish=None):
     """``output[b,:] (+)= sum of the local and remote neighbors' rows`` for the shard ``[lb, ub)``.
 
     ``input`` is this PE's symmetric embedding buffer: a tensor when there is one PE, otherwise the
     table of all PEs' buffers (see ``_peer_table``).  ``accumulate=True`` is the reference's
-    behaviour (it adds on top of ``output``'s contents)."""
+    behaviour (it adds on top of ``output``'s contents).  ``publish``: buffers (local or peer-mapped)
+    that also receive every output row, see ``mggb_sag_np_div``."""
     table, num_pes = _peer_table(input)
+    pub, npub = _publish_table(publish)
     check(lib.mggb_sag_np_div(
         _dev_ptr(output, torch.float32, "output"), table, num_pes,
         _dev_ptr(row_pointers_l, torch.int32, "row_pointers_l"), _dev_ptr(column_index_l, torch.int32, "column_index_l"),
         _dev_ptr(row_pointers_r, torch.int32, "row_pointers_r"), _dev_ptr(column_index_r, torch.int32, "column_index_r"),
         lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist,
-        _dev_ptr(row_scale_, torch.float32, "row_scale"), _lib.AGG_ACCUMULATE if accumulate else 0, _stream()))
+        _dev_ptr(row_scale_, torch.float32, "row_scale"), _lib.AGG_ACCUMULATE if accumulate else 0, pub, npub, _stream()))
 
 
 def mgg_GIN_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r, column_index_r,
@@ -153,7 +163,7 @@ def mgg_GIN_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r
 
 # ---- dense update and softmax ---------------------------------------------------------------------
 
-def dense_forward(out, x, w, row_scale_=None, relu=False, flags=0):
+def dense_forward(out, x, w, row_scale_=None, relu=False, flags=0, publish=None):
     n, dim1 = x.shape
     dim2 = w.shape[1]
     if w.shape[0] != dim1 or tuple(out.shape) != (n, dim2):
@@ -161,7 +171,7 @@ def dense_forward(out, x, w, row_scale_=None, relu=False, flags=0):
     check(lib.mggb_dense_forward(_dev_ptr(out, torch.float32, "out"), _dev_ptr(x, torch.float32, "x"),
                                  _dev_ptr(w, torch.float32, "w"), n, dim1, dim2,
                                  _dev_ptr(row_scale_, torch.float32, "row_scale"),
-                                 flags | (_lib.DENSE_RELU if relu else 0), _stream()))
+                                 flags | (_lib.DENSE_RELU if relu else 0), *_publish_table(publish), _stream()))
 
 
 def softmax_forward(out, inp):
@@ -202,6 +212,7 @@ class _dense_param:
         self.row_scale = None
         self.relu = False
         self.flags = 0
+        self.publish = None      # extra destinations of the output rows (peers' replicas)
 
     def set_weight(self, w: torch.Tensor):
         if tuple(w.shape) != (self.dim1, self.dim2):
@@ -211,7 +222,7 @@ class _dense_param:
     def _forward(self):
         x = self.d_in.reshape(-1)[: self.numNodes * self.dim1].view(self.numNodes, self.dim1)
         o = self.d_out.reshape(-1)[: self.numNodes * self.dim2].view(self.numNodes, self.dim2)
-        dense_forward(o, x, self.d_W, self.row_scale, self.relu, self.flags)
+        dense_forward(o, x, self.d_W, self.row_scale, self.relu, self.flags, self.publish)
 
 
 class dense_param_new_beg(_dense_param):

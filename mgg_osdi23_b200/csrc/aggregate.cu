@@ -19,6 +19,9 @@
 //     No atomics (:1456-1458 uses a spin on atomicExch), so the result is reproducible for fixed
 //     knobs, and the epilogue (accumulate / GIN combine / row scale) is applied exactly once.
 #include <algorithm>
+#include <map>
+#include <mutex>
+#include <utility>
 #include "common.h"
 
 // Compile-time tuning, per row width (LPR = lanes that read one row).  Chosen by measurement on
@@ -41,6 +44,11 @@
 
 namespace {
 
+constexpr int HUB_WARPS = 16;        // warps of a hub row's block
+constexpr int HUB_GRID = 148 * 2;    // blocks walking the hub list (two per SM)
+constexpr int HUB_MIN_EDGES = 16384; // smallest neighbor count treated as a hub (a 4-warp block needs > 100 us for it)
+constexpr int HUB_CAP = 1 << 18;     // list entries: enough for every row above 16384 edges of a 2^32-edge shard
+
 struct AggParams {
     float* out;
     const float* peer[MGGB_MAX_PES];
@@ -49,6 +57,8 @@ struct AggParams {
     const int32_t* rp_r;
     const int32_t* ci_r;
     const float* row_scale;
+    float* publish[MGGB_MAX_PES];   // extra destinations of every output row (peers' replicas)
+    int num_publish;
     int32_t lb;
     int32_t num_rows;
     int32_t node_per_pe;
@@ -60,6 +70,12 @@ struct AggParams {
     int div_shift;
     int mode;              // 0 overwrite, 1 accumulate, 2 GIN combine
     float self_scale;      // 1 + eps (GIN)
+    // Hub rows (more than hub_min_edges neighbors) are not aggregated by their one-node block: that
+    // block appends the row to hub_list and a second kernel gives each listed row a 16-warp block.
+    int* hub_count;        // number of rows appended (may exceed hub_cap); NULL = no hub handling
+    int* hub_list;
+    int hub_cap;
+    int hub_min_edges;
 };
 
 enum { MODE_OVERWRITE = 0, MODE_ACCUMULATE = 1, MODE_GIN = 2 };
@@ -126,15 +142,13 @@ __device__ __forceinline__ void gather_batch(Vec<VEC>& acc, const AggParams& P, 
 // The warp's share is walked as a sequence of batches of up to 32 ids: chunk q of the warp starts
 // at beg + (q*nwarps + warp)*chunk.  The ids of batch t+1 are requested before the rows of batch t
 // are gathered, so the id fetch (from HBM) overlaps the row fetch (mostly from L2).
-template <int LPR, int VEC, bool REMOTE>
+template <int LPR, int VEC, bool REMOTE, bool PREFETCH>
 __device__ __forceinline__ void gather_list(Vec<VEC>& acc, const AggParams& P, const float* const* s_peer,
-                                            const int32_t* __restrict__ ci, int beg, int end,
+                                            const int32_t* __restrict__ ci, int beg, int end, const char* lbase,
                                             int warp, int nwarps, int lane, int col, bool col_ok) {
-    constexpr bool PREFETCH = (LPR <= 4) && MGGB_AGG_PREFETCH_NARROW;
     const int g = lane / LPR;
     const unsigned row_bytes = (unsigned)P.dim * 4u;
-    // local rows: address = lbase + id * row_bytes (the shard's first id, lb, is folded into lbase)
-    const char* lbase = reinterpret_cast<const char*>(P.peer[P.pe] + col) - (long long)P.lb * row_bytes;
+    // directly addressed rows (REMOTE == false): address = lbase + id * row_bytes
     // Edge positions fit 32 bits (a shard half has < 2^31 edges and the chunk is clamped to 2^24),
     // so the walk uses unsigned arithmetic.
     const unsigned uend = (unsigned)end, chunk = (unsigned)P.chunk;
@@ -162,17 +176,18 @@ __device__ __forceinline__ void gather_list(Vec<VEC>& acc, const AggParams& P, c
 }
 
 // One block per node.  Dynamic shared memory: nwarps * dim floats (the warps' partial rows).
-template <int LPR, int VEC, bool EXACT, bool HAS_REMOTE>
-__global__ void __launch_bounds__(512, (LPR <= 4 ? MGGB_AGG_MIN_BLOCKS_NARROW : 1)) sag_np_div_kernel(const AggParams P) {
-    extern __shared__ __align__(16) float s_part[];
-    __shared__ const float* s_peer[MGGB_MAX_PES];
-
-    const int row = blockIdx.x;
+// REMOTE_MODE: 0 = one PE, no remote half; 1 = remote rows found through the owner lookup (peers'
+// buffers anywhere); 2 = the PEs' buffers are the consecutive slots of ONE matrix indexed by global id
+// (a local replica), so remote rows are addressed like local ones.
+//
+// Aggregates one node with all warps of the block and stores its output row.  s_part: nwarps * dim
+// floats of shared memory.  Ends with the block's threads past a __syncthreads() only on entry, so a
+// caller that loops over rows must synchronise before reusing s_part.
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE, bool PREFETCH>
+__device__ __forceinline__ void aggregate_row(const AggParams& P, const int row, float* s_part,
+                                              const float* const* s_peer) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
-    if (threadIdx.x < MGGB_MAX_PES) s_peer[threadIdx.x] = P.peer[threadIdx.x < P.num_pes ? threadIdx.x : 0];
-    __syncthreads();
-
     const int lbeg = P.rp_l[row], lend = P.rp_l[row + 1];
     const int rbeg = P.rp_r[row], rend = P.rp_r[row + 1];
     const int l = lane % LPR;
@@ -183,9 +198,28 @@ __global__ void __launch_bounds__(512, (LPR <= 4 ? MGGB_AGG_MIN_BLOCKS_NARROW : 
         const bool col_ok = EXACT || col < P.dim;
         Vec<VEC> acc;
         acc.zero();
-        gather_list<LPR, VEC, false>(acc, P, s_peer, P.ci_l, lbeg, lend, warp, nwarps, lane, col, col_ok);
-        if (HAS_REMOTE && rend > rbeg)
-            gather_list<LPR, VEC, true>(acc, P, s_peer, P.ci_r, rbeg, rend, warp, nwarps, lane, col, col_ok);
+        const unsigned row_bytes = (unsigned)P.dim * 4u;
+        // the shard's first id, lb, is folded into the base of the local rows
+        const char* lbase = reinterpret_cast<const char*>(P.peer[P.pe] + col) - (long long)P.lb * row_bytes;
+        // The remote list's chunks are dealt to the warps starting where the local list's chunks
+        // stopped, so a short remote list does not always land on warp 0 (the reference restarts at
+        // warp 0, include/neighbor_utils.cuh:1432-1437; only the fp32 summation order differs).
+        const int rwarp = (warp + nwarps - (int)(((unsigned)(lend - lbeg) + P.chunk - 1) / P.chunk % nwarps)) % nwarps;
+        if (REMOTE_MODE == 1) {
+            gather_list<LPR, VEC, false, PREFETCH>(acc, P, s_peer, P.ci_l, lbeg, lend, lbase, warp, nwarps, lane, col, col_ok);
+            if (rend > rbeg)
+                gather_list<LPR, VEC, true, PREFETCH>(acc, P, s_peer, P.ci_r, rbeg, rend, nullptr, rwarp, nwarps, lane, col, col_ok);
+        } else {
+            // both halves are directly addressed: one copy of the gather code walks them in turn
+#pragma unroll 1
+            for (int half = 0; half < (REMOTE_MODE == 2 ? 2 : 1); half++) {
+                const int32_t* ci = half ? P.ci_r : P.ci_l;
+                const int beg = half ? rbeg : lbeg, end = half ? rend : lend;
+                const char* base = half ? reinterpret_cast<const char*>(P.peer[0] + col) : lbase;
+                if (end > beg)
+                    gather_list<LPR, VEC, false, PREFETCH>(acc, P, s_peer, ci, beg, end, base, half ? rwarp : warp, nwarps, lane, col, col_ok);
+            }
+        }
         // fold the 32/LPR sub-warps together
 #pragma unroll
         for (int off = LPR; off < 32; off <<= 1) acc.xor_reduce(off);
@@ -202,6 +236,53 @@ __global__ void __launch_bounds__(512, (LPR <= 4 ? MGGB_AGG_MIN_BLOCKS_NARROW : 
         if (P.mode == MODE_GIN) s += P.self_scale * P.peer[P.pe][obase + c];
         else if (P.mode == MODE_ACCUMULATE) s += P.out[obase + c];
         P.out[obase + c] = s;
+        for (int k = 0; k < P.num_publish; k++) P.publish[k][obase + c] = s;
+    }
+    // No fence here: the pushed rows only have to be visible to kernels that peers launch after the
+    // next barrier, and a kernel's stores are complete, system-wide, when the kernel has finished.
+}
+
+// One block per node.  Dynamic shared memory: nwarps * dim floats (the warps' partial rows).
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE>
+__global__ void __launch_bounds__(512, (LPR <= 4 ? MGGB_AGG_MIN_BLOCKS_NARROW : 1)) sag_np_div_kernel(const AggParams P) {
+    extern __shared__ __align__(16) float s_part[];
+    __shared__ const float* s_peer[MGGB_MAX_PES];
+    __shared__ int s_deferred;
+
+    const int row = blockIdx.x;
+    if (threadIdx.x < MGGB_MAX_PES) s_peer[threadIdx.x] = P.peer[threadIdx.x < P.num_pes ? threadIdx.x : 0];
+    if (threadIdx.x == 0) {
+        // A hub row is handed to the wide-block kernel if the list still has room; otherwise this
+        // block aggregates it after all (slower, same result).
+        int deferred = 0;
+        if (P.hub_count != nullptr) {
+            const int edges = (P.rp_l[row + 1] - P.rp_l[row]) + (P.rp_r[row + 1] - P.rp_r[row]);
+            if (edges > P.hub_min_edges) {
+                const int slot = atomicAdd(P.hub_count, 1);
+                if (slot < P.hub_cap) { P.hub_list[slot] = row; deferred = 1; }
+            }
+        }
+        s_deferred = deferred;
+    }
+    __syncthreads();
+    if (s_deferred) return;
+    aggregate_row<LPR, VEC, EXACT, REMOTE_MODE, (LPR <= 4) && MGGB_AGG_PREFETCH_NARROW>(P, row, s_part, s_peer);
+}
+
+// Hub rows: a fixed grid of 16-warp blocks walks the list the kernel above filled.  Each listed row
+// is aggregated by ONE block with the same warp/chunk mapping (just more warps), so its result does
+// not depend on the order in which rows were appended.  The next batch of neighbor ids is
+// prefetched here: a hub's warps run hundreds of batches back to back.
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE>
+__global__ void __launch_bounds__(512, 2) sag_hub_rows_kernel(const AggParams P) {
+    extern __shared__ __align__(16) float s_part[];
+    __shared__ const float* s_peer[MGGB_MAX_PES];
+    if (threadIdx.x < MGGB_MAX_PES) s_peer[threadIdx.x] = P.peer[threadIdx.x < P.num_pes ? threadIdx.x : 0];
+    __syncthreads();
+    const int count = min(*P.hub_count, P.hub_cap);
+    for (int i = blockIdx.x; i < count; i += gridDim.x) {
+        aggregate_row<LPR, VEC, EXACT, REMOTE_MODE, true>(P, P.hub_list[i], s_part, s_peer);
+        __syncthreads();   // s_part is reused by the next row
     }
 }
 
@@ -217,7 +298,7 @@ void make_divider(uint32_t d, unsigned long long* magic, int* shift) {
 
 template <int LPR, int VEC, bool EXACT>
 int launch_exact(const AggParams& P, int wpb, cudaStream_t st);
-template <int LPR, int VEC, bool EXACT, bool HAS_REMOTE>
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE>
 int launch_kernel(const AggParams& P, int wpb, cudaStream_t st);
 
 template <int LPR, int VEC>
@@ -229,24 +310,61 @@ int launch(const AggParams& P, int wpb, cudaStream_t st) {
 // A single PE has no remote half: that instantiation drops the owner lookup altogether.
 template <int LPR, int VEC, bool EXACT>
 int launch_exact(const AggParams& P, int wpb, cudaStream_t st) {
-    if (P.num_pes > 1) return launch_kernel<LPR, VEC, EXACT, true>(P, wpb, st);
-    return launch_kernel<LPR, VEC, EXACT, false>(P, wpb, st);
+    if (P.num_pes == 1) return launch_kernel<LPR, VEC, EXACT, 0>(P, wpb, st);
+    bool one_matrix = true;   // peer[p] == peer[0] + p * node_per_pe * dim for every p
+    for (int p = 1; p < P.num_pes; p++)
+        one_matrix = one_matrix && (P.peer[p] == P.peer[0] + (long long)p * P.node_per_pe * P.dim);
+    if (one_matrix) return launch_kernel<LPR, VEC, EXACT, 2>(P, wpb, st);
+    return launch_kernel<LPR, VEC, EXACT, 1>(P, wpb, st);
 }
 
-template <int LPR, int VEC, bool EXACT, bool HAS_REMOTE>
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE>
 int launch_kernel(const AggParams& P, int wpb, cudaStream_t st) {
     const size_t smem = (size_t)wpb * P.dim * sizeof(float);
     if (smem > 48 * 1024)
-        MGGB_CUDA(cudaFuncSetAttribute(sag_np_div_kernel<LPR, VEC, EXACT, HAS_REMOTE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    sag_np_div_kernel<LPR, VEC, EXACT, HAS_REMOTE><<<P.num_rows, wpb * 32, smem, st>>>(P);
+        MGGB_CUDA(cudaFuncSetAttribute(sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, sizeof(int), st));
+    sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE><<<P.num_rows, wpb * 32, smem, st>>>(P);
     MGGB_CUDA(cudaGetLastError());
+    if (P.hub_count != nullptr) {
+        const size_t hub_smem = (size_t)HUB_WARPS * P.dim * sizeof(float);
+        if (hub_smem > 48 * 1024)
+            MGGB_CUDA(cudaFuncSetAttribute(sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem));
+        sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
+        MGGB_CUDA(cudaGetLastError());
+    }
+    return MGGB_OK;
+}
+
+// Hub work list: per (device, stream) so that calls ordered on one stream reuse it safely and calls
+// on different streams never share one.  Allocated on first use, kept until the process exits.
+struct HubScratch { int* count; int* list; };
+
+int hub_scratch(cudaStream_t st, HubScratch* out) {
+    static std::mutex mu;
+    static std::map<std::pair<int, cudaStream_t>, HubScratch> table;
+    int dev = 0;
+    MGGB_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> g(mu);
+    auto key = std::make_pair(dev, st);
+    auto it = table.find(key);
+    if (it == table.end()) {
+        int* base = nullptr;
+        MGGB_CUDA(cudaMalloc((void**)&base, sizeof(int) * (size_t)(HUB_CAP + 64)));
+        it = table.emplace(key, HubScratch{base, base + 64}).first;
+    }
+    *out = it->second;
     return MGGB_OK;
 }
 
 int aggregate(float* output, const float* const* peer_input, int num_pes, const int32_t* rp_l,
               const int32_t* ci_l, const int32_t* rp_r, const int32_t* ci_r, int32_t lb, int32_t ub,
               int dim, int32_t node_per_pe, int pe, int ps, int wpb, int dist, const float* row_scale,
-              int mode, float self_scale, void* stream) {
+              int mode, float self_scale, float* const* publish_out, int num_publish, int flags, void* stream) {
+    MGGB_REQUIRE(num_publish >= 0 && num_publish <= MGGB_MAX_PES && (num_publish == 0 || publish_out),
+                 "aggregate: num_publish must be in [0,%d] with a non-NULL table (got %d)", MGGB_MAX_PES, num_publish);
+    for (int k = 0; k < num_publish; k++)
+        MGGB_REQUIRE(publish_out[k] != nullptr, "aggregate: publish_out[%d] is NULL", k);
     MGGB_REQUIRE(output && peer_input && rp_l && rp_r, "aggregate: NULL argument");
     MGGB_REQUIRE(num_pes >= 1 && num_pes <= MGGB_MAX_PES, "aggregate: num_pes must be in [1,%d] (got %d)", MGGB_MAX_PES, num_pes);
     MGGB_REQUIRE(pe >= 0 && pe < num_pes, "aggregate: pe %d outside [0,%d)", pe, num_pes);
@@ -268,11 +386,22 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
     for (int p = 0; p < MGGB_MAX_PES; p++) P.peer[p] = peer_input[p < num_pes ? p : 0];
     P.rp_l = rp_l; P.ci_l = ci_l; P.rp_r = rp_r; P.ci_r = ci_r;
     P.row_scale = row_scale;
+    P.num_publish = num_publish;
+    for (int k = 0; k < num_publish; k++) P.publish[k] = publish_out[k];
     P.lb = lb; P.num_rows = ub - lb; P.node_per_pe = node_per_pe;
     P.dim = dim; P.pe = pe; P.num_pes = num_pes;
     P.chunk = (int)std::min<long long>((long long)ps * dist, 1 << 24);  // larger than any useful chunk: same walk
     make_divider((uint32_t)node_per_pe, &P.div_magic, &P.div_shift);
     P.mode = mode; P.self_scale = self_scale;
+    // Hub rows get wide blocks unless the caller asked for none or already runs wide blocks.
+    P.hub_count = nullptr; P.hub_list = nullptr; P.hub_cap = 0;
+    P.hub_min_edges = std::max(HUB_MIN_EDGES, 64 * P.chunk * wpb);
+    if (!(flags & MGGB_AGG_NO_HUB_SPLIT) && wpb <= HUB_WARPS / 2 && (size_t)HUB_WARPS * dim * sizeof(float) <= 200 * 1024) {
+        HubScratch hs;
+        int st_ = hub_scratch((cudaStream_t)stream, &hs);
+        if (st_ != MGGB_OK) return st_;
+        P.hub_count = hs.count; P.hub_list = hs.list; P.hub_cap = HUB_CAP;
+    }
 
     cudaStream_t st = (cudaStream_t)stream;
     bool vec4 = (dim % 4 == 0);
@@ -302,10 +431,12 @@ int mggb_sag_np_div(float* output, const float* const* peer_input, int num_pes,
                     const int32_t* row_ptr_l, const int32_t* col_idx_l, const int32_t* row_ptr_r,
                     const int32_t* col_idx_r, int32_t lb, int32_t ub, int dim, int32_t node_per_pe,
                     int pe, int part_size, int warp_per_block, int interleaved_dist,
-                    const float* row_scale, int flags, void* stream) {
+                    const float* row_scale, int flags, float* const* publish_out, int num_publish,
+                    void* stream) {
     return aggregate(output, peer_input, num_pes, row_ptr_l, col_idx_l, row_ptr_r, col_idx_r, lb, ub, dim,
                      node_per_pe, pe, part_size, warp_per_block, interleaved_dist, row_scale,
-                     (flags & MGGB_AGG_ACCUMULATE) ? MODE_ACCUMULATE : MODE_OVERWRITE, 0.f, stream);
+                     (flags & MGGB_AGG_ACCUMULATE) ? MODE_ACCUMULATE : MODE_OVERWRITE, 0.f, publish_out,
+                     num_publish, flags, stream);
 }
 
 int mggb_gin_np_div(float* output, const float* const* peer_input, int num_pes,
@@ -313,10 +444,9 @@ int mggb_gin_np_div(float* output, const float* const* peer_input, int num_pes,
                     const int32_t* col_idx_r, int32_t lb, int32_t ub, int dim, int32_t node_per_pe,
                     int pe, int part_size, int warp_per_block, int interleaved_dist, float eps,
                     int flags, void* stream) {
-    (void)flags;
     return aggregate(output, peer_input, num_pes, row_ptr_l, col_idx_l, row_ptr_r, col_idx_r, lb, ub, dim,
                      node_per_pe, pe, part_size, warp_per_block, interleaved_dist, nullptr, MODE_GIN,
-                     1.0f + eps, stream);
+                     1.0f + eps, nullptr, 0, flags, stream);
 }
 
 }  // extern "C"

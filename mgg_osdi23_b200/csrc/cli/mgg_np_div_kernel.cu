@@ -27,7 +27,7 @@ int main(int argc, char* argv[]) {
             if (!p.rows()) continue;
             MGG_COMPAT_CHECK(mggb_sag_np_div(d_out[p.pe], table.data(), G, p.rp_l, p.ci_l, p.rp_r, p.ci_r, (int32_t)p.lb,
                                              (int32_t)p.ub, a.hiddenSize, (int32_t)p.nodesPerPE, p.pe, a.partSize,
-                                             a.warpPerBlock, a.interleaved_dist, nullptr, 0, p.stream));
+                                             a.warpPerBlock, a.interleaved_dist, nullptr, 0, nullptr, 0, p.stream));
         }
         c.barrier();
     };

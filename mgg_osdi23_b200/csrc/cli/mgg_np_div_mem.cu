@@ -30,7 +30,7 @@ int main(int argc, char* argv[]) {
     auto agg = [&](cli::PE& p, float* out, const std::vector<const float*>& table) {
         MGG_COMPAT_CHECK(mggb_sag_np_div(out, table.data(), G, p.rp_l, p.ci_l, p.rp_r, p.ci_r, (int32_t)p.lb, (int32_t)p.ub,
                                          a.hiddenSize, (int32_t)p.nodesPerPE, p.pe, a.partSize, a.warpPerBlock,
-                                         a.interleaved_dist, nullptr, 0, p.stream));
+                                         a.interleaved_dist, nullptr, 0, nullptr, 0, p.stream));
     };
     auto pass = [&]() {
         for (auto& p : c.pes) { c.use(p); if (p.rows()) dense_beg_new_forward(dp1[p.pe], p.stream); }

@@ -12,6 +12,12 @@
 
 namespace {
 
+// Extra destinations of every output row (the peers' replicas of the embedding matrix).
+struct Publish {
+    float* dst[MGGB_MAX_PES];
+    int n;
+};
+
 constexpr int BK = 32;
 constexpr int TM = 4;
 constexpr int TN = 4;
@@ -19,7 +25,8 @@ constexpr int THREADS = 256;
 
 __global__ void __launch_bounds__(THREADS)
 dense_simt_kernel(float* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
-                  long long n, int K, int M, const float* __restrict__ row_scale, int relu, int CT, int RT) {
+                  long long n, int K, int M, const float* __restrict__ row_scale, int relu, int CT, int RT,
+                  const Publish pub) {
     extern __shared__ __align__(16) float smem[];
     const int BM = RT * TM;
     const int Mpad = CT * TN;
@@ -78,6 +85,7 @@ dense_simt_kernel(float* __restrict__ out, const float* __restrict__ x, const fl
                         float v = acc[i][j] * s;
                         if (relu) v = fmaxf(v, 0.f);
                         out[gr * M + c] = v;
+                        for (int q = 0; q < pub.n; q++) pub.dst[q][gr * M + c] = v;
                     }
                 }
             }
@@ -90,7 +98,10 @@ dense_simt_kernel(float* __restrict__ out, const float* __restrict__ x, const fl
 namespace mggb {
 
 int dense_simt(float* out, const float* x, const float* w, int64_t n, int dim1, int dim2,
-               const float* row_scale, int flags, cudaStream_t st) {
+               const float* row_scale, int flags, float* const* publish_out, int num_publish, cudaStream_t st) {
+    Publish pub{};
+    pub.n = num_publish;
+    for (int q = 0; q < num_publish; q++) pub.dst[q] = publish_out[q];
     const int CT = (dim2 + TN - 1) / TN;
     if (CT > THREADS)
         return fail(MGGB_ERR_UNSUPPORTED, "dense_forward: dim2=%d exceeds %d", dim2, THREADS * TN);
@@ -105,7 +116,7 @@ int dense_simt(float* out, const float* x, const float* w, int64_t n, int dim1, 
     const long long tiles = (n + BM - 1) / BM;
     const int grid = (int)(tiles < (long long)sms * 4 ? tiles : (long long)sms * 4);
     dense_simt_kernel<<<grid, THREADS, smem, st>>>(out, x, w, n, dim1, dim2, row_scale,
-                                                   (flags & MGGB_DENSE_RELU) ? 1 : 0, CT, RT);
+                                                   (flags & MGGB_DENSE_RELU) ? 1 : 0, CT, RT, pub);
     MGGB_CUDA(cudaGetLastError());
     return MGGB_OK;
 }
@@ -113,10 +124,14 @@ int dense_simt(float* out, const float* x, const float* w, int64_t n, int dim1, 
 }  // namespace mggb
 
 extern "C" int mggb_dense_forward(float* out, const float* x, const float* w, int64_t n, int dim1,
-                                  int dim2, const float* row_scale, int flags, void* stream) {
+                                  int dim2, const float* row_scale, int flags, float* const* publish_out,
+                                  int num_publish, void* stream) {
+    MGGB_REQUIRE(num_publish >= 0 && num_publish <= MGGB_MAX_PES && (num_publish == 0 || publish_out),
+                 "dense_forward: num_publish must be in [0,%d] with a non-NULL table (got %d)", MGGB_MAX_PES, num_publish);
+    for (int q = 0; q < num_publish; q++) MGGB_REQUIRE(publish_out[q] != nullptr, "dense_forward: publish_out[%d] is NULL", q);
     MGGB_REQUIRE(out && x && w, "dense_forward: NULL argument");
     MGGB_REQUIRE(n >= 0 && dim1 >= 1 && dim2 >= 1, "dense_forward: need n >= 0, dim1 >= 1, dim2 >= 1 (n=%lld dim1=%d dim2=%d)", (long long)n, dim1, dim2);
     MGGB_REQUIRE(out != x, "dense_forward: out must not alias x");
     if (n == 0) return MGGB_OK;
-    return mggb::dense_simt(out, x, w, n, dim1, dim2, row_scale, flags, (cudaStream_t)stream);
+    return mggb::dense_simt(out, x, w, n, dim1, dim2, row_scale, flags, publish_out, num_publish, (cudaStream_t)stream);
 }

@@ -18,6 +18,13 @@ Differences from the reference's drivers that are deliberate:
   legitimate because layer 2 is evaluated as ``(A*H)*W2``;
 * publishing alternates between two symmetric buffers so that no PE overwrites a buffer a slower
   peer may still be reading.
+
+How peers see a layer's output is chosen by what is passed as ``sym_a`` / ``sym_b``:
+* a :class:`symmem.SymmetricBuffer` (or :class:`LocalSym`): each PE keeps only its own rows and the
+  aggregation kernel PULLS every remote neighbor's row from the owner's memory (the reference's scheme);
+* a :class:`symmem.ReplicaBuffer` (or :class:`LocalReplica`): the producing kernel's epilogue PUSHES
+  each output row into every peer's copy of the matrix, and the aggregation then reads local memory
+  only.  One pushed row per node and peer instead of one pulled row per remote edge.
 """
 from __future__ import annotations
 
@@ -81,10 +88,11 @@ class Shard:
                 api.inv_sqrt_degree(self._dinv, self.rp_l, self.rp_r)
         return self._dinv
 
-    def aggregate(self, out, sym, dim, knobs: Knobs, accumulate=False, row_scale_=None):
+    def aggregate(self, out, sym, dim, knobs: Knobs, accumulate=False, row_scale_=None, publish=None):
         self._timed(lambda: api.mgg_SAG_np_div(
             out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim, self.node_per_pe, self.pe,
-            knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, accumulate=accumulate, row_scale_=row_scale_))
+            knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, accumulate=accumulate, row_scale_=row_scale_,
+            publish=publish))
 
     def aggregate_gin(self, out, sym, dim, knobs: Knobs, eps: float):
         self._timed(lambda: api.mgg_GIN_np_div(
@@ -122,7 +130,8 @@ class _Forward:
         self._h_out = None
 
     def _sym_view(self, sym, dim):
-        return sym.tensor[: self.shard.rows * dim].view(self.shard.rows, dim)
+        """Where this PE writes its rows of the published matrix (its own buffer, or its slot of a replica)."""
+        return sym.own(self.shard.rows, dim)
 
     def forward(self, barrier=None):
         run_stages([self], barrier)
@@ -163,6 +172,7 @@ class GCN2Forward(_Forward):
         self.dp2 = api.dense_param_new_hidden("d-2", self.d_agg, self.logits, shard.rows, hidden, out_dim)
         self.smx = api.softmax_new_param("smx-2", self.logits, self.out, shard.rows, out_dim)
         self.dp1.flags = self.dp2.flags = dense_flags
+        self.dp1.publish = sym_a.publish
         if w1 is not None:
             self.dp1.set_weight(w1)
         if w2 is not None:
@@ -184,7 +194,7 @@ class GCN2Forward(_Forward):
     def _agg1(self):
         if self.shard.rows:
             self.shard.aggregate(self._sym_view(self.sym_b, self.hidden), self.sym_a, self.hidden, self.knobs,
-                                 row_scale_=self.scale1)
+                                 row_scale_=self.scale1, publish=self.sym_b.publish)
 
     def _agg2_dense2_softmax(self):
         if self.shard.rows:
@@ -216,8 +226,10 @@ class GIN5Forward(_Forward):
             self.dense.append(api.dense_param_new_hidden(f"d-{k + 1}", self.d_agg, self._sym_view(syms[k % 2], hidden),
                                                          shard.rows, hidden, hidden))
         self.dense.append(api.dense_param_new_hidden(f"d-{num_layers + 1}", self.d_agg, self.logits, shard.rows, hidden, out_dim))
-        for dp in self.dense:
+        for k, dp in enumerate(self.dense):
             dp.flags = dense_flags
+            if k < num_layers:
+                dp.publish = syms[k % 2].publish
         if weights is not None:
             for dp, w in zip(self.dense, weights):
                 dp.set_weight(w)
@@ -256,7 +268,7 @@ class SingleAggregation(_Forward):
         super().__init__(shard, sym_a, None, knobs)
         self.dim = dim
         rows = max(shard.rows, 1)
-        self.d_in = self._sym_view(sym_a, dim)
+        self.d_in = self._sym_view(sym_a, dim)   # in replica mode the caller also fills the peers' slots
         self.out = torch.zeros(rows, dim, dtype=torch.float32, device=shard.device)[: shard.rows]
         self.scale = shard.inv_sqrt_degree() if norm == "sym" else None
         self.stages = [self._agg]
@@ -271,10 +283,34 @@ class SingleAggregation(_Forward):
 
 class LocalSym:
     """Symmetric buffers of several PEs emulated in ONE process: plain tensors plus the shared table."""
+    publish = None
 
     def __init__(self, tensors: Sequence[torch.Tensor], pe: int):
         self.tensor = tensors[pe]
         self.peer_ptrs = [t.data_ptr() for t in tensors]
+
+    def own(self, rows: int, dim: int) -> torch.Tensor:
+        return self.tensor[: rows * dim].view(rows, dim)
+
+
+class LocalReplica:
+    """Replicated embedding matrices of several PEs emulated in ONE process (see symmem.ReplicaBuffer)."""
+
+    def __init__(self, tensors: Sequence[torch.Tensor], pe: int, slot_elems: int):
+        self.tensor, self.pe, self.slot_elems = tensors[pe], pe, slot_elems
+        self.peer_ptrs = [tensors[pe].data_ptr() + p * slot_elems * 4 for p in range(len(tensors))]
+        self.publish = [t.data_ptr() + pe * slot_elems * 4 for q, t in enumerate(tensors) if q != pe] or None
+
+    def own(self, rows: int, dim: int) -> torch.Tensor:
+        off = self.pe * self.slot_elems
+        return self.tensor[off: off + rows * dim].view(rows, dim)
+
+
+def local_replicas(num_pes: int, node_per_pe: int, dim: int, device=None) -> List[LocalReplica]:
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    slot = node_per_pe * dim
+    tensors = [torch.zeros(max(num_pes * slot, 4), dtype=torch.float32, device=dev) for _ in range(num_pes)]
+    return [LocalReplica(tensors, pe, slot) for pe in range(num_pes)]
 
 
 def local_symmetric(num_pes: int, numel: int, device=None) -> List[LocalSym]:

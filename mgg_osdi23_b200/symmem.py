@@ -66,8 +66,14 @@ class SymmetricBuffer:
                     self._imported.append(q.value)
                     self.peer_ptrs.append(q.value)
 
+    publish = None   # a directly shared buffer is written locally only; peers pull from it
+
     def view(self, rows: int, dim: int) -> torch.Tensor:
         return self.tensor[: rows * dim].view(rows, dim)
+
+    def own(self, rows: int, dim: int) -> torch.Tensor:
+        """Where this PE writes its rows."""
+        return self.view(rows, dim)
 
     def close(self):
         """Unmaps the peers' buffers and frees the local one.  Every PE must have stopped reading it."""
@@ -79,3 +85,33 @@ class SymmetricBuffer:
             self._raw = None
             lib.mggb_sym_free(C.c_void_p(self.ptr))
             self.ptr = 0
+
+
+class ReplicaBuffer:
+    """A full copy of the [num_pes * node_per_pe, dim] embedding matrix on every PE.
+
+    Slot p (rows p*node_per_pe ...) holds PE p's rows.  A PE's kernels write their output rows into
+    their own slot of the local copy AND, through ``publish``, into the same slot of every peer's
+    copy, so after the next barrier every aggregation reads local memory only.  It costs
+    num_pes * node_per_pe * dim * 4 bytes per PE and one pushed row per (node, peer), instead of one
+    pulled row per remote EDGE: cheaper whenever a node is referenced by more than one remote edge.
+    Presents the same ``peer_ptrs`` / ``own`` / ``publish`` interface as :class:`SymmetricBuffer`.
+    """
+
+    def __init__(self, node_per_pe: int, dim: int, group=None, pe: int = 0, num_pes: int = 1):
+        self.node_per_pe, self.dim, self.pe, self.num_pes = node_per_pe, dim, pe, num_pes
+        self.slot_elems = node_per_pe * dim
+        self.sym = SymmetricBuffer(num_pes * self.slot_elems, group, pe, num_pes)
+        self.tensor = self.sym.tensor
+        # reading: every slot of the LOCAL copy
+        self.peer_ptrs = [self.sym.ptr + p * self.slot_elems * 4 for p in range(num_pes)]
+        # writing: this PE's slot in every PEER's copy
+        self.publish = [self.sym.peer_ptrs[q] + pe * self.slot_elems * 4 for q in range(num_pes) if q != pe] or None
+
+    def own(self, rows: int, dim: int) -> torch.Tensor:
+        off = self.pe * self.slot_elems
+        return self.tensor[off: off + rows * dim].view(rows, dim)
+
+    def close(self):
+        self.tensor = None
+        self.sym.close()

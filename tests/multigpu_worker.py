@@ -19,7 +19,7 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     from mgg_osdi23_b200 import drivers, graphgen as gg
-    from mgg_osdi23_b200.symmem import SymmetricBuffer
+    from mgg_osdi23_b200.symmem import SymmetricBuffer, ReplicaBuffer
     from oracle.oracle import Oracle
     orc = Oracle()
 
@@ -30,17 +30,22 @@ def main():
     w1, w2 = gg.glorot_uniform(din, hid, 1), gg.glorot_uniform(hid, dout, 2)
     sh = drivers.Shard(rp, col, rank, world, device=dev)
     assert world == 1 or sh.e_remote > 0
-    sa = SymmetricBuffer(sh.node_per_pe * hid, None, rank, world)
-    sb = SymmetricBuffer(sh.node_per_pe * hid, None, rank, world)
     barrier = drivers.nccl_stream_barrier()
-    m = drivers.GCN2Forward(sh, din, hid, dout, sa, sb, drivers.Knobs(16, 4, 2), w1=w1.to(dev), w2=w2.to(dev), norm="sym")
     xh = torch.from_numpy(x[sh.lb:sh.ub].copy()).pin_memory()
-    for _ in range(3):                       # repeated passes exercise the buffer alternation
-        probs = m.forward_host(xh, barrier)
     dinv = orc.inv_sqrt_degree(rp)
     agg = lambda t: orc.row_scale(orc.sag_f64(orc.row_scale(t, dinv), rp, col), dinv)
     want = orc.softmax(orc.dense(agg(agg(orc.dense(x, w1.numpy()))), w2.numpy()))
-    np.testing.assert_allclose(probs.numpy(), want[sh.lb:sh.ub], rtol=1e-5, atol=1e-4)
+    # pull mode (rows fetched from the owners inside the kernel), then push mode (replicas)
+    sa = SymmetricBuffer(sh.node_per_pe * hid, None, rank, world)
+    sb = SymmetricBuffer(sh.node_per_pe * hid, None, rank, world)
+    ra = ReplicaBuffer(sh.node_per_pe, hid, None, rank, world)
+    rb = ReplicaBuffer(sh.node_per_pe, hid, None, rank, world)
+    for a, b in ((sa, sb), (ra, rb)):
+        m = drivers.GCN2Forward(sh, din, hid, dout, a, b, drivers.Knobs(16, 4, 2), w1=w1.to(dev), w2=w2.to(dev), norm="sym")
+        for _ in range(3):                   # repeated passes exercise the buffer alternation
+            probs = m.forward_host(xh, barrier)
+        np.testing.assert_allclose(probs.numpy(), want[sh.lb:sh.ub], rtol=1e-5, atol=1e-4)
+        barrier()
 
     # single aggregation, dim 64, GIN combine
     sc = SymmetricBuffer(sh.node_per_pe * 64, None, rank, world)
@@ -54,7 +59,7 @@ def main():
 
     dist.barrier()
     torch.cuda.synchronize()
-    for s in (sa, sb, sc):
+    for s in (sa, sb, sc, ra, rb):
         s.close()
     dist.destroy_process_group()
     print(f"rank {rank}/{world} ok: local {sh.e_local} remote {sh.e_remote} edges")

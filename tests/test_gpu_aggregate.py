@@ -154,3 +154,34 @@ def test_full_size_config2_properties():
         nb = g.col_idx[g.row_ptr[r]:g.row_ptr[r + 1]].long()
         want = x[nb].double().sum(0)
         torch.testing.assert_close(a[r].double(), want, rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("G", [1, 2])
+def test_hub_rows_every_epilogue(oracle, G):
+    """Rows above the hub threshold take the wide-block path; every epilogue must agree with the
+    one-block-per-node path (flag MGGB_AGG_NO_HUB_SPLIT) and with the oracle."""
+    from mgg_osdi23_b200 import _lib
+    n, dim = 400, 16
+    rp, col = random_graph(n, 10, seed=11, hubs=[(0, 40000), (7, 16385), (150, 16384), (399, 20000), (398, 1025)])
+    x = np.random.default_rng(3).uniform(-1, 1, (n, dim)).astype(np.float32)
+    want = oracle.sag_f64(x, rp, col)
+    scale = np.random.default_rng(4).uniform(0.5, 1.5, n).astype(np.float32)
+    np.testing.assert_allclose(emulated_aggregate(rp, col, x, G, knobs=(16, 2, 1)), want, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(emulated_aggregate(rp, col, x, G, knobs=(16, 2, 1), row_scale=scale), want * scale[:, None], rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(emulated_aggregate(rp, col, x, G, knobs=(16, 2, 1), gin_eps=0.25), want + 1.25 * x, rtol=RTOL, atol=ATOL)
+    init = np.random.default_rng(5).uniform(-1, 1, (n, dim)).astype(np.float32)
+    np.testing.assert_allclose(emulated_aggregate(rp, col, x, G, knobs=(16, 2, 1), accumulate=True, init=init), want + init, rtol=RTOL, atol=ATOL)
+    # the flag that keeps every node on its own block gives the same sums, and publish reaches hub rows too
+    dev = torch.device("cuda")
+    sh = drivers.Shard(rp, col, 0, 1, device=dev)
+    xd = torch.from_numpy(x).to(dev)
+    a, b, pub = (torch.zeros(n, dim, device=dev) for _ in range(3))
+    mgg.mgg_SAG_np_div(a, xd, sh.rp_l, sh.ci_l, sh.rp_r, sh.ci_r, 0, n, dim, n, 0, 16, 2, 1, accumulate=False, publish=[pub])
+    import ctypes as C
+    table = (C.c_void_p * 1)(xd.data_ptr())
+    _lib.check(_lib.lib.mggb_sag_np_div(b.data_ptr(), table, 1, sh.rp_l.data_ptr(), sh.ci_l.data_ptr(), sh.rp_r.data_ptr(),
+                                        sh.ci_r.data_ptr(), 0, n, dim, n, 0, 16, 2, 1, None, 2, None, 0, None))
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(a.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(b.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+    assert torch.equal(a, pub)

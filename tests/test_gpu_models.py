@@ -36,9 +36,17 @@ def _run_cluster(make_model, G, n, x):
     return logits, out
 
 
+def _published(G, npp, dim, dev, fetch):
+    """Two publication buffers per PE: pulled-from symmetric shards, or pushed-into replicas."""
+    if fetch == "replica":
+        return drivers.local_replicas(G, npp, dim, dev), drivers.local_replicas(G, npp, dim, dev)
+    return drivers.local_symmetric(G, npp * dim, dev), drivers.local_symmetric(G, npp * dim, dev)
+
+
+@pytest.mark.parametrize("fetch", ["peer", "replica"])
 @pytest.mark.parametrize("G", [1, 2, 4])
 @pytest.mark.parametrize("norm", ["sym", "none"])
-def test_gcn2_forward(oracle, G, norm):
+def test_gcn2_forward(oracle, G, norm, fetch):
     g = gg.chung_lu_graph(1500, 40_000, 2.1, seed=2, communities=4, p_intra=0.7)
     rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
     n, din, hid, dout = g.num_nodes, 602, 16, 41
@@ -48,7 +56,7 @@ def test_gcn2_forward(oracle, G, norm):
         w1 = w1 * 0.01          # keeps unnormalised sums of ~27^2 neighbors in a softmax-friendly range
     dev = torch.device("cuda")
     npp = (n + G - 1) // G
-    sa, sb = drivers.local_symmetric(G, npp * hid, dev), drivers.local_symmetric(G, npp * hid, dev)
+    sa, sb = _published(G, npp, hid, dev, fetch)
 
     def make(pe):
         sh = drivers.Shard(rp, col, pe, G, device=dev)
@@ -61,8 +69,9 @@ def test_gcn2_forward(oracle, G, norm):
     np.testing.assert_allclose(probs, want_probs, rtol=RTOL, atol=ATOL)
 
 
+@pytest.mark.parametrize("fetch", ["peer", "replica"])
 @pytest.mark.parametrize("G", [1, 3])
-def test_gin5_forward(oracle, G):
+def test_gin5_forward(oracle, G, fetch):
     g = gg.chung_lu_graph(1200, 12_000, 2.3, seed=5)
     rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
     n, din, hid, dout, eps = g.num_nodes, 100, 64, 47, 0.0
@@ -72,7 +81,7 @@ def test_gin5_forward(oracle, G):
         + [gg.glorot_uniform(hid, dout, 20) * 0.1]
     dev = torch.device("cuda")
     npp = (n + G - 1) // G
-    sa, sb = drivers.local_symmetric(G, npp * hid, dev), drivers.local_symmetric(G, npp * hid, dev)
+    sa, sb = _published(G, npp, hid, dev, fetch)
 
     def make(pe):
         sh = drivers.Shard(rp, col, pe, G, device=dev)
