@@ -1,7 +1,8 @@
 """Builds ``libmggb200.so`` (the C-ABI library) in-tree with nvcc for sm_100a.
 
-Run as ``python -m mgg_osdi23_b200.build`` or call :func:`build_library`.  The command-line
-drivers are built by :func:`build_cli`.
+Run as ``python mgg_osdi23_b200/build.py`` (by path: importing the package itself needs the library
+to exist already) or load this file by path and call :func:`build_library`.  The command-line drivers
+are built by :func:`build_cli`.
 """
 from __future__ import annotations
 

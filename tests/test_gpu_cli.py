@@ -18,8 +18,8 @@ BIN = os.path.join(ROOT, "mgg_osdi23_b200", "bin")
 def _exe(name):
     path = os.path.join(BIN, name)
     if not os.path.exists(path):
-        from mgg_osdi23_b200 import build
-        build.build_cli()
+        import __graft_entry__
+        __graft_entry__.build()
     assert os.path.exists(path), f"{path} not built"
     return path
 
