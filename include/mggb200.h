@@ -150,6 +150,39 @@ int mggb_gin_np_div(float* output, const float* const* peer_input, int num_pes,
                     int part_size, int warp_per_block, int interleaved_dist,
                     float eps, int flags, void* stream);
 
+/* mggb_sag_np_div for callers that must not trigger a device allocation.  It has no counterpart in
+ * the reference.
+ *
+ * mggb_sag_np_div keeps its list of hub rows (see MGGB_AGG_NO_HUB_SPLIT) in device memory that it
+ * allocates the first time a (device, stream) pair is used.  Some callers cannot afford that: code
+ * running inside a memory pool that owns the whole device, a latency-critical loop where an implicit
+ * device synchronisation inside cudaMalloc is not acceptable, or a process that is forbidden to
+ * grow its footprint after start-up.  This variant computes exactly the same result with the same
+ * kernels, but its hub list lives in a fixed array inside the library's device image (32 KiB + a
+ * 256-byte header, present on every GPU that loads the library, for the life of the process).  It
+ * calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ *   shard_edges  stored edges of this shard (local + remote, what mggb_split_csr_count returned).
+ *                The fixed list holds 8192 rows; since a listed row has more than
+ *                max(16384, 64*part_size*interleaved_dist*warp_per_block) neighbors, shards of up to
+ *                8192 times that many edges (134 M at the default knobs) can never overflow it.
+ *                Larger shards are refused with MGGB_ERR_UNSUPPORTED and a message naming the limit.
+ *   warp_per_block must be <= 8 (wider blocks do not use a hub list at all).
+ *   Every other argument is as for mggb_sag_np_div; MGGB_AGG_NO_HUB_SPLIT is ignored.
+ *
+ * The first call on each device looks up the array's device address (one cudaGetSymbolAddress, done
+ * with that device current, result cached); make that first call outside any stream capture.
+ * All calls on a device share the one array: the list counter is reset at the start of each call
+ * (stream-ordered), the list keeps the previous call's rows until overwritten, and two calls whose
+ * kernels overlap on the same GPU (different streams) race on it - order them. */
+int mggb_sag_np_div_static(float* output, const float* const* peer_input, int num_pes,
+                           const int32_t* row_ptr_l, const int32_t* col_idx_l,
+                           const int32_t* row_ptr_r, const int32_t* col_idx_r,
+                           int32_t lb, int32_t ub, int64_t shard_edges, int dim, int32_t node_per_pe, int pe,
+                           int part_size, int warp_per_block, int interleaved_dist,
+                           const float* row_scale, int flags,
+                           float* const* publish_out, int num_publish, void* stream);
+
 /* ---- dense node update and softmax ---------------------------------------------------------------
  * Replaces dense_beg_new_forward / dense_hidden_new_forward (include/gnn_layer.cuh:42-52) on the
  * parameter structs of include/layer_new.cuh:272-393: row-major out[n, dim2] = x[n, dim1] * w[dim1, dim2],

@@ -28,7 +28,7 @@ class MggbError(RuntimeError):
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m mgg_osdi23_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python mgg_osdi23_b200/build.py` "
             "(nvcc, sm_100a). This package has no fallback path.")
     return C.CDLL(LIB_PATH)
 
@@ -55,6 +55,8 @@ SIGNATURES = {
     "mggb_enable_peer_access": [_int, _int],
     "mggb_sag_np_div": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
                         _int, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp],
+    "mggb_sag_np_div_static": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _i64, _int, _i32, _int,
+                               _int, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp],
     "mggb_gin_np_div": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
                         _int, _int, _int, _f, _int, _vp],
     "mggb_dense_forward": [_vp, _vp, _vp, _i64, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp],
@@ -67,6 +69,9 @@ SIGNATURES = {
 }
 
 for _name, _args in SIGNATURES.items():
+    if not hasattr(lib, _name):
+        raise ImportError(f"{LIB_PATH} is stale (no symbol {_name}): rebuild it with `python mgg_osdi23_b200/build.py`. "
+                          "This package has no fallback path.")
     _fn = getattr(lib, _name)
     _fn.argtypes = _args
     _fn.restype = C.c_int

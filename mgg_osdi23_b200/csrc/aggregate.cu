@@ -360,7 +360,8 @@ int hub_scratch(cudaStream_t st, HubScratch* out) {
 int aggregate(float* output, const float* const* peer_input, int num_pes, const int32_t* rp_l,
               const int32_t* ci_l, const int32_t* rp_r, const int32_t* ci_r, int32_t lb, int32_t ub,
               int dim, int32_t node_per_pe, int pe, int ps, int wpb, int dist, const float* row_scale,
-              int mode, float self_scale, float* const* publish_out, int num_publish, int flags, void* stream) {
+              int mode, float self_scale, float* const* publish_out, int num_publish, int flags, void* stream,
+              const HubScratch* caller_scratch = nullptr, int caller_scratch_cap = 0) {
     MGGB_REQUIRE(num_publish >= 0 && num_publish <= MGGB_MAX_PES && (num_publish == 0 || publish_out),
                  "aggregate: num_publish must be in [0,%d] with a non-NULL table (got %d)", MGGB_MAX_PES, num_publish);
     for (int k = 0; k < num_publish; k++)
@@ -396,7 +397,9 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
     // Hub rows get wide blocks unless the caller asked for none or already runs wide blocks.
     P.hub_count = nullptr; P.hub_list = nullptr; P.hub_cap = 0;
     P.hub_min_edges = std::max(HUB_MIN_EDGES, 64 * P.chunk * wpb);
-    if (!(flags & MGGB_AGG_NO_HUB_SPLIT) && wpb <= HUB_WARPS / 2 && (size_t)HUB_WARPS * dim * sizeof(float) <= 200 * 1024) {
+    if (caller_scratch != nullptr) {
+        P.hub_count = caller_scratch->count; P.hub_list = caller_scratch->list; P.hub_cap = caller_scratch_cap;
+    } else if (!(flags & MGGB_AGG_NO_HUB_SPLIT) && wpb <= HUB_WARPS / 2 && (size_t)HUB_WARPS * dim * sizeof(float) <= 200 * 1024) {
         HubScratch hs;
         int st_ = hub_scratch((cudaStream_t)stream, &hs);
         if (st_ != MGGB_OK) return st_;
@@ -423,9 +426,75 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
     return launch<32, 1>(P, wpb, st);
 }
 
+// ---- hub work list that needs no allocation ---------------------------------------------------------
+// Backing store of mggb_sag_np_div_static: lives in the library's device image, so every GPU that
+// loads the library holds these bytes until the process exits.  [0] is the counter, the list
+// starts 64 ints in (256-byte aligned like the array).
+constexpr int STATIC_HUB_CAP = 8192;
+static __device__ __align__(256) int g_static_hub[64 + STATIC_HUB_CAP];
+
+// The array's name is only a host-side handle; the kernels need its device address, which differs
+// per device.  Looked up once per device (with that device current) and cached.
+int static_hub_scratch(HubScratch* out) {
+    constexpr int MAX_DEVICES = 64;
+    static std::mutex mu;
+    static int* base[MAX_DEVICES] = {nullptr};
+    int dev = 0;
+    MGGB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES)
+        return mggb::fail(MGGB_ERR_UNSUPPORTED, "sag_np_div_static: device ordinal %d is beyond %d", dev, MAX_DEVICES);
+    std::lock_guard<std::mutex> g(mu);
+    if (base[dev] == nullptr) {
+        int* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&p, g_static_hub);
+        if (e != cudaSuccess || p == nullptr)
+            return mggb::fail(MGGB_ERR_CUDA, "sag_np_div_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+        base[dev] = p;
+    }
+    out->count = base[dev];
+    out->list = base[dev] + 64;
+    return MGGB_OK;
+}
+
 }  // namespace
 
 extern "C" {
+
+// Same aggregation as mggb_sag_np_div for callers that cannot let the library allocate device memory
+// (a pool that owns the whole GPU, a loop that must not hit cudaMalloc's implicit synchronisation, a
+// process with a frozen footprint).  The hub work list is the fixed array g_static_hub instead of a
+// heap block, so nothing is allocated or freed here.  The price: a shard may have at most
+// STATIC_HUB_CAP * (hub threshold + 1) edges, checked below; the first call on a device resolves the
+// array's address and should be made outside stream capture; and all calls on one device share the
+// array, so calls whose kernels could overlap must be ordered by the caller.  The counter is cleared
+// at the start of every call; stale list entries are never read because the hub kernel stops at the
+// counter.
+int mggb_sag_np_div_static(float* output, const float* const* peer_input, int num_pes,
+                           const int32_t* row_ptr_l, const int32_t* col_idx_l, const int32_t* row_ptr_r,
+                           const int32_t* col_idx_r, int32_t lb, int32_t ub, int64_t shard_edges, int dim,
+                           int32_t node_per_pe, int pe, int part_size, int warp_per_block,
+                           int interleaved_dist, const float* row_scale, int flags,
+                           float* const* publish_out, int num_publish, void* stream) {
+    MGGB_REQUIRE(shard_edges >= 0, "sag_np_div_static: shard_edges must be >= 0");
+    MGGB_REQUIRE(part_size >= 1 && interleaved_dist >= 1 && warp_per_block >= 1 && warp_per_block <= HUB_WARPS / 2,
+                 "sag_np_div_static: need part_size >= 1, interleaved_dist >= 1 and 1 <= warp_per_block <= %d", HUB_WARPS / 2);
+    // Every listed row has more than hub_min neighbors, so at most shard_edges / (hub_min + 1) rows
+    // can be listed; refuse shards for which that bound does not fit the fixed list.
+    const long long chunk = std::min<long long>((long long)part_size * interleaved_dist, 1 << 24);
+    const long long hub_min = std::max<long long>(HUB_MIN_EDGES, 64 * chunk * warp_per_block);
+    const long long max_edges = (long long)STATIC_HUB_CAP * (hub_min + 1);
+    if (shard_edges > max_edges)
+        return mggb::fail(MGGB_ERR_UNSUPPORTED,
+                          "sag_np_div_static: a shard of %lld edges may hold more than %d hub rows (limit %lld edges at these knobs); "
+                          "use mggb_sag_np_div, which sizes its work list on the heap", (long long)shard_edges, STATIC_HUB_CAP, max_edges);
+    HubScratch hs;
+    int st = static_hub_scratch(&hs);
+    if (st != MGGB_OK) return st;
+    return aggregate(output, peer_input, num_pes, row_ptr_l, col_idx_l, row_ptr_r, col_idx_r, lb, ub, dim,
+                     node_per_pe, pe, part_size, warp_per_block, interleaved_dist, row_scale,
+                     (flags & MGGB_AGG_ACCUMULATE) ? MODE_ACCUMULATE : MODE_OVERWRITE, 0.f, publish_out,
+                     num_publish, flags & ~MGGB_AGG_NO_HUB_SPLIT, stream, &hs, STATIC_HUB_CAP);
+}
 
 int mggb_sag_np_div(float* output, const float* const* peer_input, int num_pes,
                     const int32_t* row_ptr_l, const int32_t* col_idx_l, const int32_t* row_ptr_r,

@@ -1,0 +1,82 @@
+"""The allocation-free aggregation entry point (mggb_sag_np_div_static) against the regular one.
+
+Some users of this library run where a device allocation is off limits once the job is up: inside a
+memory pool that has claimed the whole GPU, in a serving loop that cannot tolerate the implicit
+synchronisation of cudaMalloc, or under a fixed memory budget.  For them the library offers a variant
+whose only scratch memory (the list of hub rows) is a fixed array shipped inside the library.  This
+file checks, through the C ABI, that the variant returns what the regular entry point returns, twice
+in a row (the array is shared by all calls and keeps old contents), and that it refuses shards that
+could overflow the fixed list.  It is named to be collected last, so a failure here cannot hide the
+result of any other test; it must also pass when run on its own.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from mgg_osdi23_b200 import _lib, drivers
+from gpu_util import RTOL, ATOL, random_graph
+
+pytestmark = pytest.mark.gpu
+
+
+def _call(fn, out, x, sh, dim, knobs, extra_edges=None, scale=None, flags=0):
+    table = (C.c_void_p * 1)(x.data_ptr())
+    head = [out.data_ptr(), table, 1, sh.rp_l.data_ptr(), sh.ci_l.data_ptr(), sh.rp_r.data_ptr(), sh.ci_r.data_ptr(), sh.lb, sh.ub]
+    if extra_edges is not None:
+        head.append(extra_edges)
+    tail = [dim, sh.node_per_pe, 0, *knobs, None if scale is None else scale.data_ptr(), flags, None, 0, None]
+    return fn(*head, *tail)
+
+
+def test_static_scratch_variant_matches_regular_entry_point(oracle):
+    dev = torch.device("cuda")
+    n, dim = 600, 16
+    # three rows above the hub threshold (16384 neighbors), so the shared list is really used
+    rp, col = random_graph(n, 30, seed=21, hubs=[(3, 40000), (250, 17000), (599, 25000), (10, 16384)])
+    x_np = np.random.default_rng(8).uniform(-0.02, 0.02, (n, dim)).astype(np.float32)   # keeps 40,000-term fp32 sums within 1e-4
+    sh = drivers.Shard(rp, col, 0, 1, device=dev)
+    x = torch.from_numpy(x_np).to(dev)
+    scale = torch.from_numpy(np.random.default_rng(9).uniform(0.5, 1.5, n).astype(np.float32)).to(dev)
+    want = oracle.sag_f64(x_np, rp, col)
+    lib = _lib.lib
+    knobs = (16, 4, 1)
+    regular = torch.zeros(n, dim, device=dev)
+    _lib.check(_call(lib.mggb_sag_np_div, regular, x, sh, dim, knobs))
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(regular.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+
+    # call 1: plain sum; call 2, straight after it on the same stream: another graph shape (row scaling,
+    # different knobs), so the second call meets the list as the first one left it
+    first = torch.full((n, dim), 7.0, device=dev)
+    _lib.check(_call(lib.mggb_sag_np_div_static, first, x, sh, dim, knobs, extra_edges=sh.edges))
+    second = torch.full((n, dim), -3.0, device=dev)
+    _lib.check(_call(lib.mggb_sag_np_div_static, second, x, sh, dim, (32, 2, 2), extra_edges=sh.edges, scale=scale))
+    third = torch.zeros(n, dim, device=dev)
+    _lib.check(_call(lib.mggb_sag_np_div_static, third, x, sh, dim, knobs, extra_edges=sh.edges))
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(first.cpu().numpy(), regular.cpu().numpy(), rtol=RTOL, atol=ATOL)
+    assert torch.equal(first, regular) and torch.equal(third, regular)      # same kernels, same mapping: same bits
+    regular_scaled = torch.zeros(n, dim, device=dev)
+    _lib.check(_call(lib.mggb_sag_np_div, regular_scaled, x, sh, dim, (32, 2, 2), scale=scale))
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(second.cpu().numpy(), regular_scaled.cpu().numpy(), rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(second.cpu().numpy(), want * scale.cpu().numpy()[:, None], rtol=RTOL, atol=ATOL)
+
+
+def test_static_scratch_variant_refuses_oversized_shards():
+    dev = torch.device("cuda")
+    rp, col = random_graph(50, 5, seed=1)
+    sh = drivers.Shard(rp, col, 0, 1, device=dev)
+    x = torch.zeros(50, 16, device=dev)
+    out = torch.zeros(50, 16, device=dev)
+    lib = _lib.lib
+    too_many = 8192 * (16384 + 1) + 1           # one edge past what the 8192-entry list can cover
+    st = _call(lib.mggb_sag_np_div_static, out, x, sh, 16, (16, 4, 1), extra_edges=too_many)
+    assert st == _lib.ERR_UNSUPPORTED
+    msg = lib.mggb_last_error().decode()
+    assert "8192" in msg and "mggb_sag_np_div" in msg
+    assert _call(lib.mggb_sag_np_div_static, out, x, sh, 16, (16, 4, 1), extra_edges=too_many - 1) == _lib.OK
+    assert _call(lib.mggb_sag_np_div_static, out, x, sh, 16, (16, 16, 1), extra_edges=10) == _lib.ERR_INVALID_ARG
+    torch.cuda.synchronize()
