@@ -25,6 +25,9 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# DRAM bytes (read + write) of one aggregation launch from the ncu capture summarised in
+# profiles/cfg2_gcn2_1gpu_aggregation_and_dense.txt; only that case has been captured.
+NCU_TRAFFIC_BYTES = {("cfg2", 1, 1.0): 494.4e6}
 NVLINK_GBS = 900.0          # per direction per GPU (nominal); 770 GB/s measured peer copy on this pool
 FALLBACK_HBM_GBS = 6650.0
 
@@ -380,7 +383,7 @@ def run_ours(args, rank, world, local_rank):
             "config": workload_config(args, type("G", (), {"num_nodes": n, "num_edges": total_edges, "meta": g_meta})(),
                                       model_kind, din, hid, dout, knobs, world),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                         "traffic": None, "peak_source": f"of {hbm_src}", "kernel": "sag_np_div_kernel",
+                         "traffic": NCU_TRAFFIC_BYTES.get((args.config, world, args.scale)), "peak_source": f"of {hbm_src}", "kernel": "sag_np_div_kernel",
                          "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": agg_ms, "kernel_ms_by_call_site": agg_ms_by_site,
                          "aggregation_roofline_ms": t_roof * 1e3, "aggregation_roofline_frac": t_roof * 1e3 / agg_ms,
                          "nvlink_gbs_assumed": NVLINK_GBS},
