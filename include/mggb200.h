@@ -195,6 +195,13 @@ int mggb_dense_forward(float* out, const float* x, const float* w,
                        const float* row_scale, int flags,
                        float* const* publish_out, int num_publish, void* stream);
 
+/* Reads (and with reset != 0 clears) the status word of the tensor-core dense kernel on the current
+ * device; synchronises the device.  0 = every launch so far ran to completion; 1..4 = a bounded wait
+ * inside the kernel expired (1 input slab, 2 free slab, 3 accumulator ready, 4 accumulator free) and
+ * that launch returned early with an incomplete output.  The reference has no counterpart (cuBLAS
+ * reports nothing from the device). */
+int mggb_dense_device_status(int* status, int reset);
+
 /* Replaces softmax_new_forward (include/gnn_layer.cuh:36-40; descriptors include/layer_new.cuh:80-85):
  * max-subtracted softmax over the dim classes of each row; in and out may alias. */
 int mggb_softmax_forward(float* out, const float* in, int64_t n, int dim, void* stream);

@@ -55,3 +55,26 @@ def test_softmax_matches_oracle(oracle, n, c):
     got = d_in.cpu().numpy()
     np.testing.assert_allclose(got, oracle.softmax(z), rtol=1e-5, atol=1e-7)
     np.testing.assert_allclose(got.sum(1), 1.0, rtol=1e-5)
+
+
+def test_tensor_core_kernel_reports_clean_status_and_matches_cuda_core_kernel(oracle):
+    """The default path (tcgen05 kernel where the shape fits) against the forced CUDA-core kernel,
+    including rows that do not fill a 128-row tile and a K tail that does not fill a 32-float slab."""
+    import ctypes as C
+    from mgg_osdi23_b200 import _lib
+    dev = torch.device("cuda")
+    for n, k, m in [(128, 32, 16), (129, 602, 16), (1000, 100, 64), (5000, 64, 47), (77, 16, 41), (40000, 602, 16)]:
+        x = gg.features(n, k, seed=n).numpy()
+        w = gg.glorot_uniform(k, m, seed=k).numpy()
+        xd, wd = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
+        a, b = torch.full((n, m), 9.0, device=dev), torch.full((n, m), 9.0, device=dev)
+        mgg.dense_forward(a, xd, wd)
+        mgg.dense_forward(b, xd, wd, flags=_lib.DENSE_SIMT)
+        torch.cuda.synchronize()
+        status = C.c_int(-1)
+        _lib.check(_lib.lib.mggb_dense_device_status(C.byref(status), 1))
+        assert status.value == 0, f"a bounded wait expired in the tensor-core kernel (code {status.value}) for {(n, k, m)}"
+        want = oracle.dense(x, w)
+        np.testing.assert_allclose(a.cpu().numpy(), want, rtol=RTOL, atol=ATOL, err_msg=str((n, k, m)))
+        np.testing.assert_allclose(b.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(a.cpu().numpy(), b.cpu().numpy(), rtol=RTOL, atol=2e-5)
