@@ -11,14 +11,14 @@
 // dropped is below 2^-21 of the value) and all four partial products hi*hi, hi*lo, lo*hi, lo*lo are
 // accumulated in fp32 in tensor memory, so the result matches an fp32 GEMM to about 1e-6 relative.
 //
-// One persistent CTA per SM, 9 warps, no clusters:
+// One persistent CTA per SM, 13 warps, no clusters:
 //   warps 0-3  loaders: cp.async a [128 rows x 32 floats] slab of x into a 4-stage ring in the
-//              128-byte-swizzled K-major layout the tensor core reads, then split what landed into
-//              hi and lo slabs.  Plain cp.async rather than TMA because Reddit-shaped rows
+//              128-byte-swizzled K-major layout the tensor core reads; warps 4-7 split what landed
+//              into hi and lo slabs.  Plain cp.async rather than TMA because Reddit-shaped rows
 //              (602 floats = 2408 bytes) break TMA's 16-byte stride rule; 8- or 16-byte pieces.
-//   warp 8     allocates tensor memory; one lane issues tcgen05.mma (M=128, N=pad16(M), K=8 per
+//   warp 12    allocates tensor memory; one lane issues tcgen05.mma (M=128, N=pad16(M), K=8 per
 //              instruction, 4 k-steps x 4 partial products per slab) and commits to mbarriers.
-//   warps 4-7  epilogue: tcgen05.ld the 128 x N accumulator (double-buffered in tensor memory), apply
+//   warps 8-11 epilogue: tcgen05.ld the 128 x N accumulator (double-buffered in tensor memory), apply
 //              row scale / ReLU, store the rows (and publish them to peers' replicas).
 // w is split and laid out in shared memory once per CTA.  Every wait on an mbarrier is bounded: on
 // expiry the CTA raises a status word the host can read (mggb_dense_device_status), drains its
@@ -37,13 +37,21 @@ constexpr int TILE_M = 128;              // rows of x per tile (UMMA M)
 constexpr int CHUNK_K = 32;              // floats of K per slab = one 128-byte swizzle row
 constexpr int SLAB_BYTES = TILE_M * 128; // 16 KiB
 constexpr int STAGE_BYTES = 2 * SLAB_BYTES;  // hi + lo
-constexpr int LOADERS = 128;
-constexpr int THREADS = 288;
-constexpr int MAX_STAGES = 4;
+constexpr int LOADERS = 128;              // warps 0-3 copy slabs, warps 4-7 split them (same piece mapping)
+constexpr int LOADER_WARPS = LOADERS / 32;
+constexpr int THREADS = 2 * LOADERS + 128 + 32;  // + 4 epilogue warps + the MMA warp
+#ifndef MGGB_DENSE_STAGES
+#define MGGB_DENSE_STAGES 4
+#endif
+constexpr int MAX_STAGES = MGGB_DENSE_STAGES;
+// Consecutive K slabs a loader fetches per row visit: 2 for 8-byte pieces (a warp's copy instruction
+// then covers 256 contiguous bytes of a row pair), 1 for 16-byte pieces.  Measured on B200; the copy
+// rate is bound by the number of cp.async instructions an SM keeps in flight (about 40).
+template <int G> struct Run { static constexpr int value = (G == 8) ? 2 : 1; };
 constexpr unsigned SPIN_LIMIT = 1u << 22;
 constexpr unsigned TF32_MASK = 0xFFFFE000u;
 
-__device__ int g_dense_status = 0;   // 0 ok; otherwise which wait expired (1 full, 2 empty, 3 tmem_full, 4 tmem_empty)
+__device__ int g_dense_status = 0;   // 0 ok; otherwise which wait expired (1 full, 2 empty, 3 tmem_full, 4 tmem_empty, 5 landed)
 
 struct Publish {
     float* dst[MGGB_MAX_PES];
@@ -56,7 +64,7 @@ struct TcParams {
     const float* w;
     const float* row_scale;
     long long n;
-    int K, M, Npad, nchunks, stages, relu;
+    int K, M, Npad, nchunks, stages, relu, stage_out;
     unsigned tmem_cols;
     Publish pub;
 };
@@ -78,10 +86,22 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, unsigned parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+#ifdef MGGB_DENSE_PROFILE
+// Build-time diagnostic: cycles CTA 0 spent inside each kind of wait (index = wait code) and in total
+// per role (index 8 + role).  Read with mggb_dense_profile().
+__device__ unsigned long long g_dense_cycles[16];
+#define MGGB_PROF_ADD(idx, start) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_dense_cycles[idx], (unsigned long long)(clock64() - (start))); } while (0)
+#else
+#define MGGB_PROF_ADD(idx, start) do { } while (0)
+#endif
+
 // Bounded wait: false when the limit ran out or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, unsigned parity, volatile int* abort_flag, int code) {
+#ifdef MGGB_DENSE_PROFILE
+    const long long t0 = clock64();
+#endif
     for (unsigned i = 0; i < SPIN_LIMIT; i++) {
-        if (mbar_try(bar, parity)) return true;
+        if (mbar_try(bar, parity)) { MGGB_PROF_ADD(code, t0); return true; }
         if (*abort_flag) return false;
         if (i > 32) __nanosleep(64);
     }
@@ -129,87 +149,112 @@ __device__ __forceinline__ void cp_async_zfill(uint32_t dst, const void* src, in
 
 // ---- roles ---------------------------------------------------------------------------------------
 
+// Which pieces of a slab a loader thread owns.  Piece q = i*LOADERS + p of the slab is row q / PPR,
+// 16- or 8-byte piece q % PPR of that row.  LOADERS is a multiple of 8*PPR, so for a given thread the
+// piece index and the row's position inside its 8-row swizzle group never change with i: the thread's
+// pieces sit at a fixed stride in shared memory (whole swizzle groups) and in global memory (whole rows).
+template <int G>
+struct Pieces {
+    static constexpr int PPR = 128 / G;                 // pieces per 128-byte slab row
+    static constexpr int COUNT = TILE_M * PPR / LOADERS; // pieces per thread and slab
+    static constexpr int ROW_STEP = LOADERS / PPR;      // rows between a thread's consecutive pieces
+    static constexpr uint32_t SMEM_STEP = (ROW_STEP / 8) * 1024;
+    static_assert(ROW_STEP % 8 == 0, "a thread's pieces must keep their place inside the swizzle group");
+};
+
 // Splits the pieces this thread copied for one slab into TF32-exact hi (in place) and lo parts.
 template <int G>
-__device__ __forceinline__ void split_slab(unsigned char* stage, int p) {
-    constexpr int PPR = 128 / G;
+__device__ __forceinline__ void split_slab(unsigned char* stage, uint32_t off0) {
+    using PC = Pieces<G>;
 #pragma unroll
-    for (int i = 0; i < PPR; i++) {
-        const int q = i * LOADERS + p;
-        const uint32_t off = swz(q / PPR, (q % PPR) * G);
-        float* hi = reinterpret_cast<float*>(stage + off);
-        float* lo = reinterpret_cast<float*>(stage + SLAB_BYTES + off);
+    for (int i = 0; i < PC::COUNT; i++) {
+        float* hi = reinterpret_cast<float*>(stage + off0 + i * PC::SMEM_STEP);
+        float* lo = reinterpret_cast<float*>(stage + SLAB_BYTES + off0 + i * PC::SMEM_STEP);
+        float v[G / 4];
+        if (G == 16) *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(hi);
+        else         *reinterpret_cast<float2*>(v) = *reinterpret_cast<const float2*>(hi);
+        float h[G / 4], l[G / 4];
 #pragma unroll
         for (int e = 0; e < G / 4; e++) {
-            const float v = hi[e];
-            const float h = __uint_as_float(__float_as_uint(v) & TF32_MASK);
-            hi[e] = h;
-            lo[e] = __uint_as_float(__float_as_uint(v - h) & TF32_MASK);
+            h[e] = __uint_as_float(__float_as_uint(v[e]) & TF32_MASK);
+            l[e] = __uint_as_float(__float_as_uint(v[e] - h[e]) & TF32_MASK);
         }
+        if (G == 16) { *reinterpret_cast<float4*>(hi) = *reinterpret_cast<float4*>(h); *reinterpret_cast<float4*>(lo) = *reinterpret_cast<float4*>(l); }
+        else         { *reinterpret_cast<float2*>(hi) = *reinterpret_cast<float2*>(h); *reinterpret_cast<float2*>(lo) = *reinterpret_cast<float2*>(l); }
     }
 }
 
-// Waits until at most `pending` of this thread's cp.async groups are still in flight.
-__device__ __forceinline__ void cp_async_wait_pending(int pending) {
-    switch (pending) {
-        case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-        default: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    }
-}
-
+// Loaders only copy.  For slab c a loader waits until the ring stage is free, issues its cp.async
+// pieces and lets the copy engine arrive on the stage's "landed" barrier when they complete
+// (cp.async.mbarrier.arrive.noinc), so it never waits for data and every stage can be in flight.
 template <int G>
-__device__ __forceinline__ void hand_over_slab(unsigned char* ring, int stage_idx, uint32_t full0, int p) {
-    split_slab<G>(ring + (size_t)stage_idx * STAGE_BYTES, p);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
-    mbar_arrive(full0 + 8 * stage_idx);
-}
-
-// Each slab is one cp.async group per thread.  A thread keeps stages-1 slabs in flight: after
-// committing slab c it waits for slab c-(stages-1), splits its own pieces of it and arrives on that
-// slab's "full" barrier (128 arrivals complete it).
-template <int G>
-__device__ void loader_role(const TcParams& P, unsigned char* ring, uint32_t full0, uint32_t empty0,
+__device__ void loader_role(const TcParams& P, unsigned char* ring, uint32_t landed0, uint32_t empty0,
                             volatile int* abort_flag, long long first_tile, long long tile_step, long long tiles) {
-    constexpr int PPR = 128 / G;
-    const int p = threadIdx.x;           // 0..127
+    using PC = Pieces<G>;
+    const int p = threadIdx.x;                       // 0..LOADERS-1
+    const int piece = p % PC::PPR, r0 = p / PC::PPR; // this thread's piece of the row, and its first row
+    const uint32_t off0 = swz(r0, piece * G);        // byte offset of its first piece in a slab
+    const int kpiece = piece * (G / 4);              // float offset of the piece inside the 32-float slab row
     const int S = P.stages;
-    const int lookahead = S - 1;
-    long long issued = 0, finished = 0;  // slab counters of this CTA
+    long long issued = 0;                            // slab counter of this CTA
     bool ok = true;
     for (long long tile = first_tile; tile < tiles && ok; tile += tile_step) {
-        const long long row0 = tile * TILE_M;
-        for (int kc = 0; kc < P.nchunks; kc++) {
-            const int s = (int)(issued % S);
-            const long long use = issued / S;
-            if (use >= 1) ok = mbar_wait(empty0 + 8 * s, (unsigned)((use - 1) & 1), abort_flag, 2);
+        const long long row0 = tile * TILE_M + r0;
+        const bool rows_full = tile * TILE_M + TILE_M <= P.n;
+        // Slabs are fetched in groups of up to RUN consecutive K slabs of the same rows, piece by piece,
+        // so that each row visit asks HBM for RUN*128 contiguous bytes instead of 128.
+        constexpr int RUN = Run<G>::value;
+        for (int kc0 = 0; kc0 < P.nchunks && ok; kc0 += RUN) {
+            const int run = min(RUN, P.nchunks - kc0);
+            uint32_t dst0[RUN];
+            for (int j = 0; j < run; j++) {
+                const long long c = issued + j;
+                const int s = (int)(c % S);
+                if (c / S >= 1) ok = ok && mbar_wait(empty0 + 8 * s, (unsigned)((c / S - 1) & 1), abort_flag, 2);
+                dst0[j] = smem_u32(ring + (size_t)s * STAGE_BYTES) + off0;
+            }
             if (!ok) break;
-            const uint32_t sbase = smem_u32(ring + (size_t)s * STAGE_BYTES);
+            const size_t src_step = (size_t)PC::ROW_STEP * P.K;
+            const float* src0 = P.x + row0 * P.K + kc0 * CHUNK_K + kpiece;
+            const bool all_valid = rows_full && (kc0 + run) * CHUNK_K <= P.K;
 #pragma unroll
-            for (int i = 0; i < PPR; i++) {
-                const int q = i * LOADERS + p;
-                const int r = q / PPR, piece = q % PPR;
-                const long long gr = row0 + r;
-                const int k = kc * CHUNK_K + piece * (G / 4);
-                const bool valid = gr < P.n && k < P.K;
-                const float* src = valid ? P.x + gr * P.K + k : P.x;
-                cp_async_zfill<G>(sbase + swz(r, piece * G), src, valid ? G : 0);
+            for (int i = 0; i < PC::COUNT; i++) {
+                const bool row_ok = all_valid || (row0 + i * PC::ROW_STEP < P.n);
+#pragma unroll
+                for (int j = 0; j < RUN; j++) {
+                    if (j < run) {
+                        const bool valid = row_ok && (all_valid || (kc0 + j) * CHUNK_K + kpiece < P.K);
+                        cp_async_zfill<G>(dst0[j] + i * PC::SMEM_STEP, valid ? src0 + i * src_step + j * CHUNK_K : P.x, valid ? G : 0);
+                    }
+                }
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            issued++;
-            if (issued - finished > lookahead) {
-                cp_async_wait_pending(lookahead);
-                hand_over_slab<G>(ring, (int)(finished % S), full0, p);
-                finished++;
-            }
+            for (int j = 0; j < run; j++)
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(landed0 + 8 * (int)((issued + j) % S)) : "memory");
+            issued += run;
         }
     }
-    // drain: whatever is still in flight lands; unless the CTA gave up it is split and handed over too
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    while (ok && finished < issued) {
-        hand_over_slab<G>(ring, (int)(finished % S), full0, p);
-        finished++;
+    asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of this thread's is in flight when it leaves
+}
+
+// Splitters turn a landed slab into its TF32-exact hi (in place) and lo halves and hand it to the
+// tensor core.  Same piece mapping as the loaders, but a splitter reads pieces other threads copied:
+// the "landed" barrier makes them visible.
+template <int G>
+__device__ void splitter_role(const TcParams& P, unsigned char* ring, uint32_t landed0, uint32_t full0,
+                              volatile int* abort_flag, long long first_tile, long long tile_step, long long tiles) {
+    using PC = Pieces<G>;
+    const int p = threadIdx.x - LOADERS;
+    const uint32_t off0 = swz(p / PC::PPR, (p % PC::PPR) * G);
+    const int S = P.stages;
+    long long done = 0;
+    for (long long tile = first_tile; tile < tiles; tile += tile_step) {
+        for (int kc = 0; kc < P.nchunks; kc++, done++) {
+            const int s = (int)(done % S);
+            if (!mbar_wait(landed0 + 8 * s, (unsigned)((done / S) & 1), abort_flag, 5)) return;
+            split_slab<G>(ring + (size_t)s * STAGE_BYTES, off0);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
+            mbar_arrive(full0 + 8 * s);
+        }
     }
 }
 
@@ -249,9 +294,9 @@ __device__ void mma_role(const TcParams& P, uint32_t ring_base, uint32_t w_hi, u
     }
 }
 
-__device__ void epilogue_role(const TcParams& P, uint32_t tfull0, uint32_t tempty0, uint32_t tmem_base,
+__device__ void epilogue_role(const TcParams& P, float* out_stage, uint32_t tfull0, uint32_t tempty0, uint32_t tmem_base,
                               volatile int* abort_flag, long long first_tile, long long tile_step, long long tiles) {
-    const int quarter = (threadIdx.x >> 5) & 3;   // warps 4..7 own tensor-memory lanes 32*quarter ..
+    const int quarter = (threadIdx.x >> 5) & 3;   // a warp may only read tensor-memory lanes 32*(warp%4) ..
     const int lane = threadIdx.x & 31;
     long long t = 0;
     for (long long tile = first_tile; tile < tiles; tile += tile_step, t++) {
@@ -285,6 +330,10 @@ __device__ void epilogue_role(const TcParams& P, uint32_t tfull0, uint32_t tempt
                         *reinterpret_cast<float4*>(P.out + o + j) = f;
                         for (int q = 0; q < P.pub.n; q++) *reinterpret_cast<float4*>(P.pub.dst[q] + o + j) = f;
                     }
+                } else if (out_stage != nullptr) {
+                    // odd row widths: park the row in shared memory, the warp stores it coalesced below
+#pragma unroll
+                    for (int j = 0; j < 16; j++) out_stage[lane * (P.Npad + 1) + c0 + j] = v[j];   // odd pitch: no bank conflicts
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; j++)
@@ -296,7 +345,21 @@ __device__ void epilogue_role(const TcParams& P, uint32_t tfull0, uint32_t tempt
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        mbar_arrive(tempty0 + 8 * buf);
+        mbar_arrive(tempty0 + 8 * buf);   // the accumulator is in registers / shared memory: free it early
+        if (out_stage != nullptr && (P.M & 3) != 0) {
+            // the warp's 32 rows are one contiguous run of 32*M floats in the output
+            __syncwarp();
+            const long long first = tile * TILE_M + quarter * 32;
+            const int rows = (int)max(0LL, min(32LL, P.n - first));
+            const long long o = first * P.M;
+            for (int r = 0; r < rows; r++)
+                for (int c = lane; c < P.M; c += 32) {
+                    const float f = out_stage[r * (P.Npad + 1) + c];
+                    P.out[o + r * P.M + c] = f;
+                    for (int q = 0; q < P.pub.n; q++) P.pub.dst[q][o + r * P.M + c] = f;
+                }
+            __syncwarp();
+        }
     }
 }
 
@@ -310,21 +373,21 @@ __global__ void __launch_bounds__(THREADS, 1) dense_tc_kernel(const TcParams P) 
     unsigned char* w_lo = base + w_bytes;
     unsigned char* ring = base + 2 * w_bytes;
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(ring + (size_t)P.stages * STAGE_BYTES);
-    // bars: full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2]
+    // bars: full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2], landed[MAX_STAGES]
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
     const int warp = threadIdx.x >> 5;
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * MAX_STAGES;
-    const uint32_t tfull0 = empty0 + 8 * MAX_STAGES, tempty0 = tfull0 + 16;
+    const uint32_t tfull0 = empty0 + 8 * MAX_STAGES, tempty0 = tfull0 + 16, landed0 = tempty0 + 16;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int s = 0; s < MAX_STAGES; s++) { mbar_init(full0 + 8 * s, LOADERS); mbar_init(empty0 + 8 * s, 1); }
+        for (int s = 0; s < MAX_STAGES; s++) { mbar_init(full0 + 8 * s, LOADERS); mbar_init(empty0 + 8 * s, 1); mbar_init(landed0 + 8 * s, LOADERS); }
         for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 128); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {
+    if (warp == 2 * LOADER_WARPS + 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(P.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -345,17 +408,26 @@ __global__ void __launch_bounds__(THREADS, 1) dense_tc_kernel(const TcParams P) 
     const uint32_t tmem_base = s_tmem_base;
 
     const long long tiles = (P.n + TILE_M - 1) / TILE_M;
-    if (warp < 4) {
-        loader_role<G>(P, ring, full0, empty0, &s_abort, blockIdx.x, gridDim.x, tiles);
-    } else if (warp < 8) {
-        epilogue_role(P, tfull0, tempty0, tmem_base, &s_abort, blockIdx.x, gridDim.x, tiles);
+#ifdef MGGB_DENSE_PROFILE
+    const long long role_t0 = clock64();
+#endif
+    if (warp < LOADER_WARPS) {
+        loader_role<G>(P, ring, landed0, empty0, &s_abort, blockIdx.x, gridDim.x, tiles);
+    } else if (warp < 2 * LOADER_WARPS) {
+        splitter_role<G>(P, ring, landed0, full0, &s_abort, blockIdx.x, gridDim.x, tiles);
+    } else if (warp < 2 * LOADER_WARPS + 4) {
+        // staging rows for odd output widths: 32 rows x (Npad+1) floats per epilogue warp, after the barriers
+        float* out_stage = P.stage_out ? reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + 256) +
+                                             (size_t)(warp - 2 * LOADER_WARPS) * 32 * (P.Npad + 1) : nullptr;
+        epilogue_role(P, out_stage, tfull0, tempty0, tmem_base, &s_abort, blockIdx.x, gridDim.x, tiles);
     } else if ((threadIdx.x & 31) == 0) {
         mma_role(P, smem_u32(ring), smem_u32(w_hi), smem_u32(w_lo), full0, empty0, tfull0, tempty0, tmem_base,
                  &s_abort, blockIdx.x, gridDim.x, tiles);
     }
+    MGGB_PROF_ADD(8 + (warp < LOADER_WARPS ? 0 : warp < 2 * LOADER_WARPS ? 1 : warp < 2 * LOADER_WARPS + 4 ? 2 : 3), role_t0);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 8) {
+    if (warp == 2 * LOADER_WARPS + 4) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P.tmem_cols) : "memory");
     }
@@ -375,9 +447,13 @@ int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, in
     const int Npad = (dim2 + 15) / 16 * 16;
     if (Npad > 256) return MGGB_OK;
     const int nchunks = (dim1 + CHUNK_K - 1) / CHUNK_K;
+    if (nchunks < 2) return MGGB_OK;   // one slab per tile leaves the four epilogue warps as the limit: the CUDA-core kernel is faster
     const size_t w_bytes = 2 * (size_t)nchunks * Npad * 128;
     const size_t budget = 225 * 1024;                                      // of the 227 KiB a CTA may use
-    const size_t fixed = w_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    const size_t out_stage_bytes = (dim2 % 4 != 0) ? (size_t)4 * 32 * (Npad + 1) * sizeof(float) : 0;   // coalescing buffer for odd widths
+    size_t fixed = w_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + out_stage_bytes;
+    bool stage_out = out_stage_bytes != 0;
+    if (stage_out && fixed + 2 * STAGE_BYTES > budget) { fixed -= out_stage_bytes; stage_out = false; }   // no room: strided stores
     if (fixed + 2 * STAGE_BYTES > budget) return MGGB_OK;                  // needs at least a 2-stage ring
     const int stages = (int)std::min<size_t>(MAX_STAGES, (budget - fixed) / STAGE_BYTES);
     unsigned tmem_cols = 32;
@@ -388,6 +464,7 @@ int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, in
     P.out = out; P.x = x; P.w = w; P.row_scale = row_scale; P.n = n;
     P.K = dim1; P.M = dim2; P.Npad = Npad; P.nchunks = nchunks; P.stages = stages;
     P.relu = (flags & MGGB_DENSE_RELU) ? 1 : 0;
+    P.stage_out = stage_out ? 1 : 0;
     P.tmem_cols = tmem_cols;
     P.pub.n = num_publish;
     for (int q = 0; q < num_publish; q++) P.pub.dst[q] = publish_out[q];
@@ -422,3 +499,14 @@ extern "C" int mggb_dense_device_status(int* status, int reset) {
     }
     return MGGB_OK;
 }
+
+#ifdef MGGB_DENSE_PROFILE
+extern "C" int mggb_dense_profile(unsigned long long* cycles16, int reset) {
+    MGGB_CUDA(cudaMemcpyFromSymbol(cycles16, g_dense_cycles, sizeof(unsigned long long) * 16));
+    if (reset) {
+        unsigned long long zero[16] = {0};
+        MGGB_CUDA(cudaMemcpyToSymbol(g_dense_cycles, zero, sizeof(zero)));
+    }
+    return MGGB_OK;
+}
+#endif
