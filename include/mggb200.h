@@ -150,6 +150,30 @@ int mggb_gin_np_div(float* output, const float* const* peer_input, int num_pes,
                     int part_size, int warp_per_block, int interleaved_dist,
                     float eps, int flags, void* stream);
 
+/* The two aggregations with a caller-chosen block schedule.  row_order (device, int32[ub-lb], a
+ * permutation of 0..ub-lb-1, or NULL for the natural order) names the row each thread block takes,
+ * in launch order.  The reference launches block b for node b (include/neighbor_utils.cuh:808-818),
+ * so a high-degree node late in the shard sets the kernel's tail; with the longest rows first
+ * (mggb_degree_order) the tail disappears.  Results are identical: only the order in which rows are
+ * started changes, never which warp sums which edge. */
+int mggb_sag_np_div_ordered(float* output, const float* const* peer_input, int num_pes,
+                            const int32_t* row_ptr_l, const int32_t* col_idx_l,
+                            const int32_t* row_ptr_r, const int32_t* col_idx_r,
+                            int32_t lb, int32_t ub, int dim, int32_t node_per_pe, int pe,
+                            int part_size, int warp_per_block, int interleaved_dist,
+                            const float* row_scale, int flags,
+                            float* const* publish_out, int num_publish,
+                            const int32_t* row_order, void* stream);
+int mggb_gin_np_div_ordered(float* output, const float* const* peer_input, int num_pes,
+                            const int32_t* row_ptr_l, const int32_t* col_idx_l,
+                            const int32_t* row_ptr_r, const int32_t* col_idx_r,
+                            int32_t lb, int32_t ub, int dim, int32_t node_per_pe, int pe,
+                            int part_size, int warp_per_block, int interleaved_dist,
+                            float eps, int flags, const int32_t* row_order, void* stream);
+/* Host helper: order[k] = the shard row with the k-th largest neighbor count (local + remote; ties
+ * in row order).  row_ptr_r may be NULL.  No counterpart in the reference. */
+int mggb_degree_order(const int32_t* row_ptr_l, const int32_t* row_ptr_r, int32_t num_rows, int32_t* order);
+
 /* mggb_sag_np_div for callers that must not trigger a device allocation.  It has no counterpart in
  * the reference.
  *

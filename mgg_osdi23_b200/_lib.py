@@ -59,6 +59,11 @@ SIGNATURES = {
                                _int, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp],
     "mggb_gin_np_div": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
                         _int, _int, _int, _f, _int, _vp],
+    "mggb_sag_np_div_ordered": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
+                                _int, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp, _vp],
+    "mggb_gin_np_div_ordered": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
+                                _int, _int, _int, _f, _int, _vp, _vp],
+    "mggb_degree_order": [_vp, _vp, _i32, _vp],
     "mggb_dense_forward": [_vp, _vp, _vp, _i64, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp],
     "mggb_dense_device_status": [C.POINTER(_int), _int],
     "mggb_softmax_forward": [_vp, _vp, _i64, _int, _vp],

@@ -32,7 +32,7 @@ __all__ = [
     "shard_range", "split_CSR", "build_part", "mgg_SAG_np_div", "mgg_GIN_np_div",
     "dense_param_new_beg", "dense_param_new_hidden", "softmax_new_param",
     "dense_beg_new_forward", "dense_hidden_new_forward", "softmax_new_forward",
-    "dense_forward", "softmax_forward", "row_scale", "inv_sqrt_degree",
+    "dense_forward", "softmax_forward", "row_scale", "inv_sqrt_degree", "degree_order",
 ]
 
 
@@ -129,11 +129,22 @@ def build_part(name: str, indptr, num_nodes: int, partSize: int, exact_sentinel:
     return [part_ptr, part2node, node2part]
 
 
+def degree_order(row_ptr_l, row_ptr_r=None):
+    """Host helper: shard rows sorted by neighbor count, longest first (int32 numpy array); pass it
+    (on the device) as ``row_order`` to the aggregations so that long rows start first."""
+    lp = np.ascontiguousarray(row_ptr_l, dtype=np.int32)
+    rp = None if row_ptr_r is None else np.ascontiguousarray(row_ptr_r, dtype=np.int32)
+    order = np.empty(len(lp) - 1, np.int32)
+    check(lib.mggb_degree_order(_np_ptr(lp), _np_ptr(rp), len(lp) - 1, _np_ptr(order)))
+    return order
+
+
 # ---- aggregation --------------------------------------------------------------------------------
 
 def mgg_SAG_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r, column_index_r,
                    lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist,
-                   *, accumulate: bool = True, row_scale_: torch.Tensor | None = None, publish=None):
+                   *, accumulate: bool = True, row_scale_: torch.Tensor | None = None, publish=None,
+                   row_order: torch.Tensor | None = None):
     """``output[b,:] (+)= sum of the local and remote neighbors' rows`` for the shard ``[lb, ub)``.
 
     ``input`` is this PE's symmetric embedding buffer: a tensor when there is one PE, otherwise the
@@ -142,23 +153,26 @@ def mgg_SAG_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r
     that also receive every output row, see ``mggb_sag_np_div``."""
     table, num_pes = _peer_table(input)
     pub, npub = _publish_table(publish)
-    check(lib.mggb_sag_np_div(
+    check(lib.mggb_sag_np_div_ordered(
         _dev_ptr(output, torch.float32, "output"), table, num_pes,
         _dev_ptr(row_pointers_l, torch.int32, "row_pointers_l"), _dev_ptr(column_index_l, torch.int32, "column_index_l"),
         _dev_ptr(row_pointers_r, torch.int32, "row_pointers_r"), _dev_ptr(column_index_r, torch.int32, "column_index_r"),
         lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist,
-        _dev_ptr(row_scale_, torch.float32, "row_scale"), _lib.AGG_ACCUMULATE if accumulate else 0, pub, npub, _stream()))
+        _dev_ptr(row_scale_, torch.float32, "row_scale"), _lib.AGG_ACCUMULATE if accumulate else 0, pub, npub,
+        _dev_ptr(row_order, torch.int32, "row_order"), _stream()))
 
 
 def mgg_GIN_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r, column_index_r,
-                   lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist, eps):
+                   lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist, eps,
+                   *, row_order: torch.Tensor | None = None):
     """``output[b,:] = (1+eps) * input_self[b,:] + sum`` (``include/neighbor_utils.cuh:1660-1665``)."""
     table, num_pes = _peer_table(input)
-    check(lib.mggb_gin_np_div(
+    check(lib.mggb_gin_np_div_ordered(
         _dev_ptr(output, torch.float32, "output"), table, num_pes,
         _dev_ptr(row_pointers_l, torch.int32, "row_pointers_l"), _dev_ptr(column_index_l, torch.int32, "column_index_l"),
         _dev_ptr(row_pointers_r, torch.int32, "row_pointers_r"), _dev_ptr(column_index_r, torch.int32, "column_index_r"),
-        lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist, float(eps), 0, _stream()))
+        lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist, float(eps), 0,
+        _dev_ptr(row_order, torch.int32, "row_order"), _stream()))
 
 
 # ---- dense update and softmax ---------------------------------------------------------------------

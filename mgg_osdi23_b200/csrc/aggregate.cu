@@ -57,6 +57,7 @@ struct AggParams {
     const int32_t* rp_r;
     const int32_t* ci_r;
     const float* row_scale;
+    const int32_t* row_order;       // NULL, or the row each block takes (a permutation of 0..num_rows-1)
     float* publish[MGGB_MAX_PES];   // extra destinations of every output row (peers' replicas)
     int num_publish;
     int32_t lb;
@@ -249,7 +250,7 @@ __global__ void __launch_bounds__(512, (LPR <= 4 ? MGGB_AGG_MIN_BLOCKS_NARROW : 
     __shared__ const float* s_peer[MGGB_MAX_PES];
     __shared__ int s_deferred;
 
-    const int row = blockIdx.x;
+    const int row = P.row_order ? P.row_order[blockIdx.x] : (int)blockIdx.x;
     if (threadIdx.x < MGGB_MAX_PES) s_peer[threadIdx.x] = P.peer[threadIdx.x < P.num_pes ? threadIdx.x : 0];
     if (threadIdx.x == 0) {
         // A hub row is handed to the wide-block kernel if the list still has room; otherwise this
@@ -361,7 +362,7 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
               const int32_t* ci_l, const int32_t* rp_r, const int32_t* ci_r, int32_t lb, int32_t ub,
               int dim, int32_t node_per_pe, int pe, int ps, int wpb, int dist, const float* row_scale,
               int mode, float self_scale, float* const* publish_out, int num_publish, int flags, void* stream,
-              const HubScratch* caller_scratch = nullptr, int caller_scratch_cap = 0) {
+              const HubScratch* caller_scratch = nullptr, int caller_scratch_cap = 0, const int32_t* row_order = nullptr) {
     MGGB_REQUIRE(num_publish >= 0 && num_publish <= MGGB_MAX_PES && (num_publish == 0 || publish_out),
                  "aggregate: num_publish must be in [0,%d] with a non-NULL table (got %d)", MGGB_MAX_PES, num_publish);
     for (int k = 0; k < num_publish; k++)
@@ -387,6 +388,7 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
     for (int p = 0; p < MGGB_MAX_PES; p++) P.peer[p] = peer_input[p < num_pes ? p : 0];
     P.rp_l = rp_l; P.ci_l = ci_l; P.rp_r = rp_r; P.ci_r = ci_r;
     P.row_scale = row_scale;
+    P.row_order = row_order;
     P.num_publish = num_publish;
     for (int k = 0; k < num_publish; k++) P.publish[k] = publish_out[k];
     P.lb = lb; P.num_rows = ub - lb; P.node_per_pe = node_per_pe;
@@ -516,6 +518,28 @@ int mggb_gin_np_div(float* output, const float* const* peer_input, int num_pes,
     return aggregate(output, peer_input, num_pes, row_ptr_l, col_idx_l, row_ptr_r, col_idx_r, lb, ub, dim,
                      node_per_pe, pe, part_size, warp_per_block, interleaved_dist, nullptr, MODE_GIN,
                      1.0f + eps, nullptr, 0, flags, stream);
+}
+
+int mggb_sag_np_div_ordered(float* output, const float* const* peer_input, int num_pes,
+                            const int32_t* row_ptr_l, const int32_t* col_idx_l, const int32_t* row_ptr_r,
+                            const int32_t* col_idx_r, int32_t lb, int32_t ub, int dim, int32_t node_per_pe,
+                            int pe, int part_size, int warp_per_block, int interleaved_dist,
+                            const float* row_scale, int flags, float* const* publish_out, int num_publish,
+                            const int32_t* row_order, void* stream) {
+    return aggregate(output, peer_input, num_pes, row_ptr_l, col_idx_l, row_ptr_r, col_idx_r, lb, ub, dim,
+                     node_per_pe, pe, part_size, warp_per_block, interleaved_dist, row_scale,
+                     (flags & MGGB_AGG_ACCUMULATE) ? MODE_ACCUMULATE : MODE_OVERWRITE, 0.f, publish_out,
+                     num_publish, flags, stream, nullptr, 0, row_order);
+}
+
+int mggb_gin_np_div_ordered(float* output, const float* const* peer_input, int num_pes,
+                            const int32_t* row_ptr_l, const int32_t* col_idx_l, const int32_t* row_ptr_r,
+                            const int32_t* col_idx_r, int32_t lb, int32_t ub, int dim, int32_t node_per_pe,
+                            int pe, int part_size, int warp_per_block, int interleaved_dist, float eps,
+                            int flags, const int32_t* row_order, void* stream) {
+    return aggregate(output, peer_input, num_pes, row_ptr_l, col_idx_l, row_ptr_r, col_idx_r, lb, ub, dim,
+                     node_per_pe, pe, part_size, warp_per_block, interleaved_dist, nullptr, MODE_GIN,
+                     1.0f + eps, nullptr, 0, flags, stream, nullptr, 0, row_order);
 }
 
 }  // extern "C"

@@ -5,6 +5,7 @@
 // (include/neighbor_utils.cuh:381-405, :411-460), produced differently: the reference grows
 // std::vectors with push_back on one thread; here every array is sized by a counting pass and then
 // filled by all host threads, rows being independent once the per-row offsets are known.
+#include <algorithm>
 #include <climits>
 #include <cstring>
 #include <vector>
@@ -159,6 +160,22 @@ int mggb_build_part_fill(const int32_t* indptr, int32_t num_nodes, int32_t part_
     if (num_nodes > 0 && (exact_sentinel || indptr[num_nodes] > indptr[num_nodes - 1]))
         sentinel = indptr[num_nodes];
     part_ptr[total] = sentinel;
+    return MGGB_OK;
+}
+
+int mggb_degree_order(const int32_t* row_ptr_l, const int32_t* row_ptr_r, int32_t num_rows, int32_t* order) {
+    MGGB_REQUIRE(row_ptr_l && order, "degree_order: NULL argument");
+    MGGB_REQUIRE(num_rows >= 0, "degree_order: need num_rows >= 0");
+    std::vector<int64_t> key((size_t)num_rows);
+#pragma omp parallel for schedule(static)
+    for (int32_t i = 0; i < num_rows; i++) {
+        int64_t deg = (int64_t)row_ptr_l[i + 1] - row_ptr_l[i];
+        if (row_ptr_r) deg += (int64_t)row_ptr_r[i + 1] - row_ptr_r[i];
+        key[i] = deg;
+        order[i] = i;
+    }
+    // longest rows first, ties in row order
+    std::stable_sort(order, order + num_rows, [&](int32_t a, int32_t b) { return key[a] > key[b]; });
     return MGGB_OK;
 }
 

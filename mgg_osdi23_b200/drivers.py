@@ -49,7 +49,8 @@ class Knobs:
 class Shard:
     """What one PE holds of the graph: its node range and the split CSR on the device."""
 
-    def __init__(self, row_ptr, col_idx, pe: int, num_pes: int, device=None, num_nodes: Optional[int] = None):
+    def __init__(self, row_ptr, col_idx, pe: int, num_pes: int, device=None, num_nodes: Optional[int] = None,
+                 order_rows: Optional[bool] = None):
         row_ptr = np.ascontiguousarray(row_ptr)
         n = len(row_ptr) - 1 if num_nodes is None else num_nodes
         self.pe, self.num_pes, self.num_nodes = pe, num_pes, n
@@ -64,6 +65,11 @@ class Shard:
         # never hand the kernel a NULL column array, even for an empty half
         self.ci_l = torch.from_numpy(lc if lc.size else np.zeros(1, np.int32)).to(dev)
         self.ci_r = torch.from_numpy(rc if rc.size else np.zeros(1, np.int32)).to(dev)
+        # block schedule: longest rows first, so that no high-degree row is left for the kernel's tail
+        # (measured on B200: 3-6 % faster on 2-8 PEs, where a shard has few blocks per SM; no gain on one PE)
+        if order_rows is None:
+            order_rows = num_pes > 1
+        self.row_order = torch.from_numpy(api.degree_order(lp, rp)).to(dev) if (order_rows and self.rows) else None
         self._dinv = None
         self.event_sink = None   # when a list: (start, end) CUDA events of every aggregation launch are appended
 
@@ -92,12 +98,12 @@ class Shard:
         self._timed(lambda: api.mgg_SAG_np_div(
             out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim, self.node_per_pe, self.pe,
             knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, accumulate=accumulate, row_scale_=row_scale_,
-            publish=publish))
+            publish=publish, row_order=self.row_order))
 
     def aggregate_gin(self, out, sym, dim, knobs: Knobs, eps: float):
         self._timed(lambda: api.mgg_GIN_np_div(
             out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim, self.node_per_pe, self.pe,
-            knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, eps))
+            knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, eps, row_order=self.row_order))
 
 
 def nccl_stream_barrier(group=None) -> Callable[[], None]:

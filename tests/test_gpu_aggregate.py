@@ -186,3 +186,21 @@ def test_hub_rows_every_epilogue(oracle, G):
     np.testing.assert_allclose(a.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
     np.testing.assert_allclose(b.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
     assert torch.equal(a, pub)
+
+
+def test_row_order_changes_schedule_not_results():
+    """Blocks taking rows longest-first (or in any permutation) give bit-identical sums."""
+    dev = torch.device("cuda")
+    rp, col = random_graph(700, 25, seed=13, hubs=[(650, 6000), (3, 900)])
+    x = torch.from_numpy(np.random.default_rng(2).uniform(-1, 1, (700, 16)).astype(np.float32)).to(dev)
+    plain = drivers.Shard(rp, col, 0, 1, device=dev, order_rows=False)
+    ordered = drivers.Shard(rp, col, 0, 1, device=dev, order_rows=True)
+    assert plain.row_order is None and ordered.row_order[0].item() == 650
+    a, b, c = (torch.zeros(700, 16, device=dev) for _ in range(3))
+    plain.aggregate(a, x, 16, drivers.Knobs())
+    ordered.aggregate(b, x, 16, drivers.Knobs())
+    ordered.row_order = torch.from_numpy(np.random.default_rng(5).permutation(700).astype(np.int32)).to(dev)
+    ordered.aggregate_gin(c, x, 16, drivers.Knobs(), 0.0)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    torch.testing.assert_close(c, a + x, rtol=1e-6, atol=1e-6)

@@ -89,3 +89,11 @@ def test_argument_errors():
     from mgg_osdi23_b200._lib import lib
     assert lib.mggb_split_csr_count(None, None, 0, 0, None, None) != 0
     assert b"NULL" in lib.mggb_last_error()
+
+
+def test_degree_order():
+    lp = np.array([0, 2, 2, 9, 10, 10], np.int32)      # local degrees 2 0 7 1 0
+    rp = np.array([0, 0, 5, 5, 6, 6], np.int32)        # remote degrees 0 5 0 1 0
+    assert mgg.degree_order(lp, rp).tolist() == [2, 1, 0, 3, 4]      # totals 2 5 7 2 0; ties keep row order
+    assert mgg.degree_order(lp).tolist() == [2, 0, 3, 1, 4]
+    assert mgg.degree_order(np.zeros(1, np.int32)).size == 0
