@@ -238,6 +238,20 @@ class _dense_param:
         o = self.d_out.reshape(-1)[: self.numNodes * self.dim2].view(self.numNodes, self.dim2)
         dense_forward(o, x, self.d_W, self.row_scale, self.relu, self.flags, self.publish)
 
+    def _forward_rows(self, r0: int, r1: int):
+        """The same product for rows [r0, r1) only (rows are independent): lets a caller overlap the
+        upload of later rows with the product of earlier ones."""
+        if r1 <= r0:
+            return
+        x = self.d_in.reshape(-1)[: self.numNodes * self.dim1].view(self.numNodes, self.dim1)[r0:r1]
+        o = self.d_out.reshape(-1)[: self.numNodes * self.dim2].view(self.numNodes, self.dim2)[r0:r1]
+        scale = None if self.row_scale is None else self.row_scale[r0:r1]
+        pub = None
+        if self.publish:
+            off = r0 * self.dim2 * 4
+            pub = [(p.data_ptr() if isinstance(p, torch.Tensor) else int(p)) + off for p in self.publish]
+        dense_forward(o, x, self.d_W, scale, self.relu, self.flags, pub)
+
 
 class dense_param_new_beg(_dense_param):
     """``include/layer_new.cuh:272-333``."""

@@ -324,6 +324,16 @@ int launch_kernel(const AggParams& P, int wpb, cudaStream_t st) {
     const size_t smem = (size_t)wpb * P.dim * sizeof(float);
     if (smem > 48 * 1024)
         MGGB_CUDA(cudaFuncSetAttribute(sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // The gather lives on L1/L2 hits and needs little shared memory: ask for the largest L1 split, or
+    // the SM keeps whatever split the previous kernel (e.g. the dense kernel's 200+ KiB) left behind.
+    static thread_local bool carveout_set[64] = {false};
+    int dev_ = 0;
+    MGGB_CUDA(cudaGetDevice(&dev_));
+    if (dev_ >= 0 && dev_ < 64 && !carveout_set[dev_]) {
+        MGGB_CUDA(cudaFuncSetAttribute(sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxL1));
+        MGGB_CUDA(cudaFuncSetAttribute(sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxL1));
+        carveout_set[dev_] = true;
+    }
     if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, sizeof(int), st));
     sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE><<<P.num_rows, wpb * 32, smem, st>>>(P);
     MGGB_CUDA(cudaGetLastError());

@@ -134,6 +134,8 @@ class _Forward:
         self.sym_a, self.sym_b = sym_a, sym_b
         self.stages: List[Callable[[], None]] = []
         self._h_out = None
+        self._copy_stream = None
+        self.first_dense = None     # set by models whose stage 0 is exactly one row-local dense product
 
     def _sym_view(self, sym, dim):
         """Where this PE writes its rows of the published matrix (its own buffer, or its slot of a replica)."""
@@ -143,12 +145,38 @@ class _Forward:
         run_stages([self], barrier)
         return self.out
 
-    def forward_host(self, x_host: torch.Tensor, barrier=None) -> torch.Tensor:
+    def forward_host(self, x_host: torch.Tensor, barrier=None, chunks: int = 8) -> torch.Tensor:
         """The call a user with HOST data makes: uploads this PE's feature rows (pinned ``x_host``
         [rows, in_dim]), runs the forward pass and returns the class probabilities in pinned host
-        memory.  Synchronises the stream before returning."""
-        self.d_in.copy_(x_host, non_blocking=True)
-        self.forward(barrier)
+        memory.  Synchronises the stream before returning.
+
+        The first layer's dense product is row-local, so the upload is cut into ``chunks`` row blocks
+        on a copy stream and each block is multiplied as soon as it has arrived: the product (and the
+        publication to peers) hides behind the PCIe transfer."""
+        first = getattr(self, "first_dense", None)
+        rows = self.shard.rows
+        if first is None or chunks <= 1 or rows < 4096 * chunks:
+            self.d_in.copy_(x_host, non_blocking=True)
+            self.forward(barrier)
+        else:
+            cur = torch.cuda.current_stream()
+            if self._copy_stream is None:
+                self._copy_stream = torch.cuda.Stream()
+            cs = self._copy_stream
+            cs.wait_stream(cur)                 # the previous pass no longer reads d_in
+            step = (rows + chunks - 1) // chunks
+            for r0 in range(0, rows, step):
+                r1 = min(rows, r0 + step)
+                with torch.cuda.stream(cs):
+                    self.d_in[r0:r1].copy_(x_host[r0:r1], non_blocking=True)
+                    arrived = torch.cuda.Event()
+                    arrived.record(cs)
+                cur.wait_event(arrived)
+                first._forward_rows(r0, r1)
+            for s in range(1, len(self.stages)):
+                if barrier is not None:
+                    barrier()
+                self.stages[s]()
         if self._h_out is None:
             self._h_out = torch.empty(self.out.shape, dtype=torch.float32, pin_memory=True)
         self._h_out.copy_(self.out, non_blocking=True)
@@ -192,6 +220,7 @@ class GCN2Forward(_Forward):
             self.scale1 = dinv * dinv          # Z1' = dinv * (dinv * A H1')   (second factor pre-scales layer 2)
             self.scale2 = dinv                 # Z2  = dinv * A Z1'
         self.stages = [self._dense1, self._agg1, self._agg2_dense2_softmax]
+        self.first_dense = self.dp1
 
     def _dense1(self):
         if self.shard.rows:
@@ -242,6 +271,7 @@ class GIN5Forward(_Forward):
         self.smx = api.softmax_new_param("smx", self.logits, self.out, shard.rows, out_dim)
         self._syms = syms
         self.stages = [self._first] + [self._layer(k) for k in range(num_layers)]
+        self.first_dense = self.dense[0]
 
     def _first(self):
         if self.shard.rows:

@@ -153,3 +153,23 @@ def test_symmetric_buffer_single_pe():
     torch.cuda.synchronize()
     assert torch.equal(out, torch.full_like(out, 3.0))
     s.close()
+
+
+def test_forward_host_overlapped_upload(oracle):
+    """Enough rows for the chunked path: row blocks are uploaded on a copy stream and multiplied as
+    they arrive; the result must equal the plain path bit for bit, on repeated calls."""
+    g = gg.chung_lu_graph(40_000, 400_000, 2.3, seed=9)
+    rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
+    n = g.num_nodes
+    dev = torch.device("cuda")
+    sa, sb = drivers.local_symmetric(1, n * 16, dev), drivers.local_symmetric(1, n * 16, dev)
+    sh = drivers.Shard(rp, col, 0, 1, device=dev)
+    w1, w2 = gg.glorot_uniform(100, 16, 1), gg.glorot_uniform(16, 8, 2)
+    m = drivers.GCN2Forward(sh, 100, 16, 8, sa[0], sb[0], drivers.Knobs(), w1=w1.to(dev), w2=w2.to(dev), norm="sym")
+    x = gg.features(n, 100, seed=1).pin_memory()
+    plain = m.forward_host(x, chunks=1).clone()
+    for _ in range(3):
+        chunked = m.forward_host(x, chunks=4)
+        assert torch.equal(chunked, plain)
+    _, want = _oracle_gcn2(oracle, rp, col, x.numpy(), w1.numpy(), w2.numpy(), "sym")
+    np.testing.assert_allclose(plain.numpy(), want, rtol=RTOL, atol=ATOL)
