@@ -47,6 +47,8 @@ def parse_args():
                     help="how peers see a layer's output: 'peer' = rows pulled from the owner inside the aggregation "
                          "kernel; 'replica' = rows pushed into every PE's copy by the producing kernel; 'auto' = replica "
                          "when there are peers and the copy fits")
+    ap.add_argument("--dense", default="auto", choices=["auto", "simt"],
+                    help="'simt' forces the CUDA-core dense kernel (A/B against the tensor-core one)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -292,9 +294,11 @@ def run_ours(args, rank, world, local_rank):
     weights = build_weights(args.config, dev)
     norm = "sym" if model_kind == "gcn2" or args.config == "cfg1" else "none"
     if model_kind == "gcn2":
-        model = drivers.GCN2Forward(shard, din, hid, dout, sym_a, sym_b, knobs, w1=weights[0], w2=weights[1], norm=norm)
+        model = drivers.GCN2Forward(shard, din, hid, dout, sym_a, sym_b, knobs, w1=weights[0], w2=weights[1], norm=norm,
+                                    dense_flags=4 if args.dense == "simt" else 0)
     elif model_kind == "gin5":
-        model = drivers.GIN5Forward(shard, din, hid, dout, sym_a, sym_b, knobs, eps=0.0, weights=weights)
+        model = drivers.GIN5Forward(shard, din, hid, dout, sym_a, sym_b, knobs, eps=0.0, weights=weights,
+                                    dense_flags=4 if args.dense == "simt" else 0)
     else:
         model = drivers.SingleAggregation(shard, hid, sym_a, knobs, norm=norm)
     x_dev = gg.features(shard.rows, din, seed=1, device=dev, first_row=shard.lb)
@@ -387,7 +391,7 @@ def run_ours(args, rank, world, local_rank):
                          "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": agg_ms, "kernel_ms_by_call_site": agg_ms_by_site,
                          "aggregation_roofline_ms": t_roof * 1e3, "aggregation_roofline_frac": t_roof * 1e3 / agg_ms,
                          "nvlink_gbs_assumed": NVLINK_GBS},
-            "fetch": fetch,
+            "fetch": fetch, "dense_kernel": "cuda-core" if args.dense == "simt" else "tcgen05 where the shape fits",
             "per_gpu_edges": [{"local": el, "remote": er, "rows": r} for el, er, r in allstats],
             "remote_fraction": sum(er for _, er, _ in allstats) / max(1, total_edges),
             "gpu_launches": args.steps * model.kernels_per_forward * world,

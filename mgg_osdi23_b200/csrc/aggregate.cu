@@ -251,22 +251,28 @@ __global__ void __launch_bounds__(512, (LPR <= 4 ? MGGB_AGG_MIN_BLOCKS_NARROW : 
     __shared__ int s_deferred;
 
     const int row = P.row_order ? P.row_order[blockIdx.x] : (int)blockIdx.x;
-    if (threadIdx.x < MGGB_MAX_PES) s_peer[threadIdx.x] = P.peer[threadIdx.x < P.num_pes ? threadIdx.x : 0];
-    if (threadIdx.x == 0) {
-        // A hub row is handed to the wide-block kernel if the list still has room; otherwise this
-        // block aggregates it after all (slower, same result).
-        int deferred = 0;
-        if (P.hub_count != nullptr) {
-            const int edges = (P.rp_l[row + 1] - P.rp_l[row]) + (P.rp_r[row + 1] - P.rp_r[row]);
-            if (edges > P.hub_min_edges) {
-                const int slot = atomicAdd(P.hub_count, 1);
-                if (slot < P.hub_cap) { P.hub_list[slot] = row; deferred = 1; }
-            }
-        }
-        s_deferred = deferred;
+    // Only the owner lookup reads the pointer table from shared memory; the other modes skip the
+    // fill and its barrier.
+    if (REMOTE_MODE == 1) {
+        if (threadIdx.x < MGGB_MAX_PES) s_peer[threadIdx.x] = P.peer[threadIdx.x < P.num_pes ? threadIdx.x : 0];
+        __syncthreads();
     }
-    __syncthreads();
-    if (s_deferred) return;
+    // Every thread reads the row's bounds, so "is this a hub" is known block-wide without a barrier;
+    // only an actual hub pays for the hand-over (atomic slot, shared flag, barrier).
+    if (P.hub_count != nullptr) {
+        const int edges = (P.rp_l[row + 1] - P.rp_l[row]) + (P.rp_r[row + 1] - P.rp_r[row]);
+        if (edges > P.hub_min_edges) {
+            if (threadIdx.x == 0) {
+                // handed to the wide-block kernel if the list still has room; otherwise this block
+                // aggregates the row after all (slower, same result)
+                const int slot = atomicAdd(P.hub_count, 1);
+                s_deferred = slot < P.hub_cap;
+                if (slot < P.hub_cap) P.hub_list[slot] = row;
+            }
+            __syncthreads();
+            if (s_deferred) return;
+        }
+    }
     aggregate_row<LPR, VEC, EXACT, REMOTE_MODE, (LPR <= 4) && MGGB_AGG_PREFETCH_NARROW>(P, row, s_part, s_peer);
 }
 
@@ -324,16 +330,6 @@ int launch_kernel(const AggParams& P, int wpb, cudaStream_t st) {
     const size_t smem = (size_t)wpb * P.dim * sizeof(float);
     if (smem > 48 * 1024)
         MGGB_CUDA(cudaFuncSetAttribute(sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    // The gather lives on L1/L2 hits and needs little shared memory: ask for the largest L1 split, or
-    // the SM keeps whatever split the previous kernel (e.g. the dense kernel's 200+ KiB) left behind.
-    static thread_local bool carveout_set[64] = {false};
-    int dev_ = 0;
-    MGGB_CUDA(cudaGetDevice(&dev_));
-    if (dev_ >= 0 && dev_ < 64 && !carveout_set[dev_]) {
-        MGGB_CUDA(cudaFuncSetAttribute(sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxL1));
-        MGGB_CUDA(cudaFuncSetAttribute(sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxL1));
-        carveout_set[dev_] = true;
-    }
     if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, sizeof(int), st));
     sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE><<<P.num_rows, wpb * 32, smem, st>>>(P);
     MGGB_CUDA(cudaGetLastError());
