@@ -56,10 +56,10 @@ def parse_args():
 
 CONFIGS = {
     # name: (model, in_dim, hidden, out_dim, default knobs (ps, wpb, dist), description)
-    "cfg1": ("agg", 16, 16, 16, (32, 2, 1), "R-MAT 16,384 nodes, one sym-normalised aggregation, dim 16"),
+    "cfg1": ("agg", 16, 16, 16, (32, 4, 1), "R-MAT 16,384 nodes, one sym-normalised aggregation, dim 16"),
     "cfg2": ("gcn2", 602, 16, 41, (32, 4, 2), "Reddit-shaped power-law graph 232,965 nodes ~114.6M edges, GCN-2 602-16-41"),
     "cfg3": ("gin5", 100, 64, 47, (16, 1, 2), "products-shaped power-law graph 2,449,029 nodes ~123.7M edges, GIN-5 hidden 64"),
-    "cfg4": ("agg", 16, 16, 16, (32, 4, 1), "skewed directed R-MAT 4,206,785 nodes ~101.3M edges, one aggregation dim 16"),
+    "cfg4": ("agg", 16, 16, 16, (32, 1, 1), "skewed directed R-MAT 4,206,785 nodes ~101.3M edges, one aggregation dim 16"),
 }
 
 

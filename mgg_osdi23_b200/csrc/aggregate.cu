@@ -38,6 +38,9 @@
 #ifndef MGGB_AGG_MAX_ROUNDS
 #define MGGB_AGG_MAX_ROUNDS 4
 #endif
+#ifndef MGGB_AGG_ROW_LOAD
+#define MGGB_AGG_ROW_LOAD 0   // how a row is loaded: 0 read-only path (L1-cached), 1 L2 only, 2 read-only path without L1 allocation
+#endif
 #ifndef MGGB_AGG_PREFETCH_NARROW
 #define MGGB_AGG_PREFETCH_NARROW 0
 #endif
@@ -85,7 +88,15 @@ template <int VEC> struct Vec;
 template <> struct Vec<4> {
     float4 v;
     __device__ __forceinline__ void zero() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
-    __device__ __forceinline__ void load(const float* p) { v = __ldg(reinterpret_cast<const float4*>(p)); }
+    __device__ __forceinline__ void load(const float* p) {
+#if MGGB_AGG_ROW_LOAD == 1
+        v = __ldcg(reinterpret_cast<const float4*>(p));
+#elif MGGB_AGG_ROW_LOAD == 2
+        asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+#else
+        v = __ldg(reinterpret_cast<const float4*>(p));
+#endif
+    }
     __device__ __forceinline__ void add(const Vec& o) { v.x += o.v.x; v.y += o.v.y; v.z += o.v.z; v.w += o.v.w; }
     __device__ __forceinline__ void xor_reduce(int off) {
         v.x += __shfl_xor_sync(0xffffffffu, v.x, off);
@@ -176,11 +187,40 @@ __device__ __forceinline__ void gather_list(Vec<VEC>& acc, const AggParams& P, c
     }
 }
 
-// One block per node.  Dynamic shared memory: nwarps * dim floats (the warps' partial rows).
 // REMOTE_MODE: 0 = one PE, no remote half; 1 = remote rows found through the owner lookup (peers'
 // buffers anywhere); 2 = the PEs' buffers are the consecutive slots of ONE matrix indexed by global id
 // (a local replica), so remote rows are addressed like local ones.
 //
+// Adds into acc this warp's share (warp `warp` of `nwarps`) of one node's neighbor rows, columns
+// [col, col+VEC).
+template <int LPR, int VEC, int REMOTE_MODE, bool PREFETCH>
+__device__ __forceinline__ void accumulate_row(Vec<VEC>& acc, const AggParams& P, const float* const* s_peer,
+                                               int lbeg, int lend, int rbeg, int rend,
+                                               int warp, int nwarps, int lane, int col, bool col_ok) {
+    const unsigned row_bytes = (unsigned)P.dim * 4u;
+    // the shard's first id, lb, is folded into the base of the local rows
+    const char* lbase = reinterpret_cast<const char*>(P.peer[P.pe] + col) - (long long)P.lb * row_bytes;
+    // The remote list's chunks are dealt to the warps starting where the local list's chunks
+    // stopped, so a short remote list does not always land on warp 0 (the reference restarts at
+    // warp 0, include/neighbor_utils.cuh:1432-1437; only the fp32 summation order differs).
+    const int rwarp = (warp + nwarps - (int)(((unsigned)(lend - lbeg) + P.chunk - 1) / P.chunk % nwarps)) % nwarps;
+    if (REMOTE_MODE == 1) {
+        gather_list<LPR, VEC, false, PREFETCH>(acc, P, s_peer, P.ci_l, lbeg, lend, lbase, warp, nwarps, lane, col, col_ok);
+        if (rend > rbeg)
+            gather_list<LPR, VEC, true, PREFETCH>(acc, P, s_peer, P.ci_r, rbeg, rend, nullptr, rwarp, nwarps, lane, col, col_ok);
+    } else {
+        // both halves are directly addressed: one copy of the gather code walks them in turn
+#pragma unroll 1
+        for (int half = 0; half < (REMOTE_MODE == 2 ? 2 : 1); half++) {
+            const int32_t* ci = half ? P.ci_r : P.ci_l;
+            const int beg = half ? rbeg : lbeg, end = half ? rend : lend;
+            const char* base = half ? reinterpret_cast<const char*>(P.peer[0] + col) : lbase;
+            if (end > beg)
+                gather_list<LPR, VEC, false, PREFETCH>(acc, P, s_peer, ci, beg, end, base, half ? rwarp : warp, nwarps, lane, col, col_ok);
+        }
+    }
+}
+
 // Aggregates one node with all warps of the block and stores its output row.  s_part: nwarps * dim
 // floats of shared memory.  Ends with the block's threads past a __syncthreads() only on entry, so a
 // caller that loops over rows must synchronise before reusing s_part.
@@ -199,28 +239,7 @@ __device__ __forceinline__ void aggregate_row(const AggParams& P, const int row,
         const bool col_ok = EXACT || col < P.dim;
         Vec<VEC> acc;
         acc.zero();
-        const unsigned row_bytes = (unsigned)P.dim * 4u;
-        // the shard's first id, lb, is folded into the base of the local rows
-        const char* lbase = reinterpret_cast<const char*>(P.peer[P.pe] + col) - (long long)P.lb * row_bytes;
-        // The remote list's chunks are dealt to the warps starting where the local list's chunks
-        // stopped, so a short remote list does not always land on warp 0 (the reference restarts at
-        // warp 0, include/neighbor_utils.cuh:1432-1437; only the fp32 summation order differs).
-        const int rwarp = (warp + nwarps - (int)(((unsigned)(lend - lbeg) + P.chunk - 1) / P.chunk % nwarps)) % nwarps;
-        if (REMOTE_MODE == 1) {
-            gather_list<LPR, VEC, false, PREFETCH>(acc, P, s_peer, P.ci_l, lbeg, lend, lbase, warp, nwarps, lane, col, col_ok);
-            if (rend > rbeg)
-                gather_list<LPR, VEC, true, PREFETCH>(acc, P, s_peer, P.ci_r, rbeg, rend, nullptr, rwarp, nwarps, lane, col, col_ok);
-        } else {
-            // both halves are directly addressed: one copy of the gather code walks them in turn
-#pragma unroll 1
-            for (int half = 0; half < (REMOTE_MODE == 2 ? 2 : 1); half++) {
-                const int32_t* ci = half ? P.ci_r : P.ci_l;
-                const int beg = half ? rbeg : lbeg, end = half ? rend : lend;
-                const char* base = half ? reinterpret_cast<const char*>(P.peer[0] + col) : lbase;
-                if (end > beg)
-                    gather_list<LPR, VEC, false, PREFETCH>(acc, P, s_peer, ci, beg, end, base, half ? rwarp : warp, nwarps, lane, col, col_ok);
-            }
-        }
+        accumulate_row<LPR, VEC, REMOTE_MODE, PREFETCH>(acc, P, s_peer, lbeg, lend, rbeg, rend, warp, nwarps, lane, col, col_ok);
         // fold the 32/LPR sub-warps together
 #pragma unroll
         for (int off = LPR; off < 32; off <<= 1) acc.xor_reduce(off);
@@ -274,6 +293,61 @@ __global__ void __launch_bounds__(512, (LPR <= 4 ? MGGB_AGG_MIN_BLOCKS_NARROW : 
         }
     }
     aggregate_row<LPR, VEC, EXACT, REMOTE_MODE, (LPR <= 4) && MGGB_AGG_PREFETCH_NARROW>(P, row, s_part, s_peer);
+}
+
+// warp_per_block == 1: a warp owns its node outright, so nothing has to meet in shared memory and no
+// block barrier is needed.  Eight such warps share a CUDA block (consecutive entries of the
+// schedule), which cuts the number of blocks eightfold on graphs whose nodes have a few dozen
+// neighbors.  Same edge-to-lane mapping and summation order as the one-warp block above: identical bits.
+constexpr int ROW_WARPS = 8;
+
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE>
+__global__ void __launch_bounds__(ROW_WARPS * 32, (LPR <= 4 ? 6 : 2)) sag_row_per_warp_kernel(const AggParams P) {
+    __shared__ const float* s_peer[MGGB_MAX_PES];
+    if (REMOTE_MODE == 1) {
+        if (threadIdx.x < MGGB_MAX_PES) s_peer[threadIdx.x] = P.peer[threadIdx.x < P.num_pes ? threadIdx.x : 0];
+        __syncthreads();
+    }
+    const int lane = threadIdx.x & 31;
+    const long long slot_idx = (long long)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+    if (slot_idx >= P.num_rows) return;
+    const int row = P.row_order ? P.row_order[slot_idx] : (int)slot_idx;
+    const int lbeg = P.rp_l[row], lend = P.rp_l[row + 1];
+    const int rbeg = P.rp_r[row], rend = P.rp_r[row + 1];
+    if (P.hub_count != nullptr && (lend - lbeg) + (rend - rbeg) > P.hub_min_edges) {
+        int deferred = 0;
+        if (lane == 0) {
+            const int slot = atomicAdd(P.hub_count, 1);
+            deferred = slot < P.hub_cap;
+            if (deferred) P.hub_list[slot] = row;
+        }
+        if (__shfl_sync(0xffffffffu, deferred, 0)) return;
+    }
+    const int l = lane % LPR;
+    constexpr int COLS = LPR * VEC;
+    const long long obase = (long long)row * P.dim;
+    const float scale = P.row_scale ? P.row_scale[row] : 1.f;
+    for (int cb = 0; cb < (EXACT ? 1 : P.dim); cb += COLS) {
+        const int col = cb + l * VEC;
+        const bool col_ok = EXACT || col < P.dim;
+        Vec<VEC> acc;
+        acc.zero();
+        accumulate_row<LPR, VEC, REMOTE_MODE, (LPR <= 4) && MGGB_AGG_PREFETCH_NARROW>(acc, P, s_peer, lbeg, lend, rbeg, rend, 0, 1, lane, col, col_ok);
+#pragma unroll
+        for (int off = LPR; off < 32; off <<= 1) acc.xor_reduce(off);
+        if (lane < LPR && col_ok) {
+            const float* part = reinterpret_cast<const float*>(&acc.v);
+#pragma unroll
+            for (int e = 0; e < VEC; e++) {
+                float s = 0.f + part[e];
+                if (P.row_scale) s *= scale;
+                if (P.mode == MODE_GIN) s += P.self_scale * P.peer[P.pe][obase + col + e];
+                else if (P.mode == MODE_ACCUMULATE) s += P.out[obase + col + e];
+                P.out[obase + col + e] = s;
+                for (int k = 0; k < P.num_publish; k++) P.publish[k][obase + col + e] = s;
+            }
+        }
+    }
 }
 
 // Hub rows: a fixed grid of 16-warp blocks walks the list the kernel above filled.  Each listed row
@@ -331,7 +405,10 @@ int launch_kernel(const AggParams& P, int wpb, cudaStream_t st) {
     if (smem > 48 * 1024)
         MGGB_CUDA(cudaFuncSetAttribute(sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, sizeof(int), st));
-    sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE><<<P.num_rows, wpb * 32, smem, st>>>(P);
+    if (wpb == 1 && LPR <= 4)   // wide rows stream from HBM and measured no better this way
+        sag_row_per_warp_kernel<LPR, VEC, EXACT, REMOTE_MODE><<<(P.num_rows + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, st>>>(P);
+    else
+        sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE><<<P.num_rows, wpb * 32, smem, st>>>(P);
     MGGB_CUDA(cudaGetLastError());
     if (P.hub_count != nullptr) {
         const size_t hub_smem = (size_t)HUB_WARPS * P.dim * sizeof(float);
