@@ -60,3 +60,13 @@ def test_gcn_and_gin_drivers_run(graph_files):
 def test_usage_error():
     r = subprocess.run([_exe("MGG_np_div_mem"), "a", "b"], capture_output=True, text=True)
     assert r.returncode != 0 and "Usage" in r.stdout
+
+
+def test_knob_sweep_tool(tmp_path):
+    """The in-process ps x wpb x dist sweep (what the reference's 5_MGG_DSE_*.py + extract_search_*.py do)."""
+    from mgg_osdi23_b200 import sweep
+    out = tmp_path / "sweep.csv"
+    sweep.main(["--config", "cfg1", "--iters", "1", "--warmup", "0", "--csv", str(out)])
+    lines = [ln for ln in out.read_text().splitlines() if ln and not ln.startswith("#")]
+    assert lines[0] == "ps,wpb,dist,ms" and len(lines) == 1 + 6 * 5 * 5
+    assert all(float(ln.split(",")[3]) > 0 for ln in lines[1:])
