@@ -47,6 +47,8 @@ def parse_args():
                     help="how peers see a layer's output: 'peer' = rows pulled from the owner inside the aggregation "
                          "kernel; 'replica' = rows pushed into every PE's copy by the producing kernel; 'auto' = replica "
                          "when there are peers and the copy fits")
+    ap.add_argument("--group-per-node", action="store_true", help="aggregate with 4 lanes per node (MGGB_AGG_GROUP_PER_NODE); default for cfg4")
+    ap.add_argument("--no-group-per-node", action="store_true")
     ap.add_argument("--dense", default="auto", choices=["auto", "simt"],
                     help="'simt' forces the CUDA-core dense kernel (A/B against the tensor-core one)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -229,7 +231,7 @@ def workload_config(args, g, model, din, hid, dout, knobs, world):
          "partition": f"node-range x{world}", "l2_policy": "inputs larger than L2 (features 561 MB, neighbor ids 458 MB per aggregation)"
          if args.config == "cfg2" else "inputs larger than L2 where the graph is (see edges x 4 B of neighbor ids per aggregation)"}
     if knobs is not None:
-        c.update({"ps": knobs.partSize, "wpb": knobs.warpPerBlock, "dist": knobs.interleaved_dist})
+        c.update({"ps": knobs.partSize, "wpb": knobs.warpPerBlock, "dist": knobs.interleaved_dist, "group_per_node": bool(knobs.flags & 4)})
     if args.scale != 1.0:
         c["scale"] = args.scale
     return c
@@ -267,7 +269,8 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     model_kind, din, hid, dout, dknobs, desc = CONFIGS[args.config]
-    knobs = drivers.Knobs(args.ps or dknobs[0], args.wpb or dknobs[1], args.dist or dknobs[2])
+    group = (args.group_per_node or args.config in ("cfg4",)) and not args.no_group_per_node
+    knobs = drivers.Knobs(args.ps or dknobs[0], args.wpb or dknobs[1], args.dist or dknobs[2], flags=4 if group else 0)
 
     g = make_graph(args.config, dev, args.scale)
     n = g.num_nodes

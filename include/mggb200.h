@@ -37,10 +37,15 @@ enum {
 enum {
     MGGB_AGG_ACCUMULATE = 1, /* out += sum (what the reference does, include/neighbor_utils.cuh:1456-1458);
                                 without it out = sum, which needs no zero-fill between passes */
-    MGGB_AGG_NO_HUB_SPLIT = 2 /* keep every node on its own warp_per_block-warp block, as the reference does.
+    MGGB_AGG_NO_HUB_SPLIT = 2, /* keep every node on its own warp_per_block-warp block, as the reference does.
                                  By default a node with more than max(16384, 64*ps*dist*wpb) neighbors is passed,
                                  through a work list in library-owned device memory (allocated once per device
                                  and stream, on first use), to a second kernel that gives it a 16-warp block */
+    MGGB_AGG_GROUP_PER_NODE = 4 /* dim 16 only (ignored otherwise): a node is aggregated by one group of 4 lanes,
+                                 8 nodes per warp, instead of by warp_per_block warps; part_size and
+                                 interleaved_dist then do not apply, and nodes above 1024 neighbors take the
+                                 hub path.  For graphs whose nodes have a few dozen neighbors, where the
+                                 per-node fixed cost of a whole warp dominates.  Same sums up to fp32 order */
 };
 
 /* Flags of mggb_dense_forward. */

@@ -144,7 +144,7 @@ def degree_order(row_ptr_l, row_ptr_r=None):
 def mgg_SAG_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r, column_index_r,
                    lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist,
                    *, accumulate: bool = True, row_scale_: torch.Tensor | None = None, publish=None,
-                   row_order: torch.Tensor | None = None):
+                   row_order: torch.Tensor | None = None, flags: int = 0):
     """``output[b,:] (+)= sum of the local and remote neighbors' rows`` for the shard ``[lb, ub)``.
 
     ``input`` is this PE's symmetric embedding buffer: a tensor when there is one PE, otherwise the
@@ -158,20 +158,20 @@ def mgg_SAG_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r
         _dev_ptr(row_pointers_l, torch.int32, "row_pointers_l"), _dev_ptr(column_index_l, torch.int32, "column_index_l"),
         _dev_ptr(row_pointers_r, torch.int32, "row_pointers_r"), _dev_ptr(column_index_r, torch.int32, "column_index_r"),
         lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist,
-        _dev_ptr(row_scale_, torch.float32, "row_scale"), _lib.AGG_ACCUMULATE if accumulate else 0, pub, npub,
+        _dev_ptr(row_scale_, torch.float32, "row_scale"), (_lib.AGG_ACCUMULATE if accumulate else 0) | flags, pub, npub,
         _dev_ptr(row_order, torch.int32, "row_order"), _stream()))
 
 
 def mgg_GIN_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r, column_index_r,
                    lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist, eps,
-                   *, row_order: torch.Tensor | None = None):
+                   *, row_order: torch.Tensor | None = None, flags: int = 0):
     """``output[b,:] = (1+eps) * input_self[b,:] + sum`` (``include/neighbor_utils.cuh:1660-1665``)."""
     table, num_pes = _peer_table(input)
     check(lib.mggb_gin_np_div_ordered(
         _dev_ptr(output, torch.float32, "output"), table, num_pes,
         _dev_ptr(row_pointers_l, torch.int32, "row_pointers_l"), _dev_ptr(column_index_l, torch.int32, "column_index_l"),
         _dev_ptr(row_pointers_r, torch.int32, "row_pointers_r"), _dev_ptr(column_index_r, torch.int32, "column_index_r"),
-        lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist, float(eps), 0,
+        lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist, float(eps), flags,
         _dev_ptr(row_order, torch.int32, "row_order"), _stream()))
 
 

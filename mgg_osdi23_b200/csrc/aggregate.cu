@@ -350,6 +350,95 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, (LPR <= 4 ? 6 : 2)) sag_row_pe
     }
 }
 
+// MGGB_AGG_GROUP_PER_NODE, dim == 16: a node is aggregated by ONE group of 4 lanes (one float4 of the
+// row each), so a warp works on 8 nodes at once, each group walking its own neighbor lists 4 ids at
+// a time (4 row loads in flight per lane, 32 per warp, as in the other kernels).  Nothing is reduced
+// across lanes and the per-node fixed cost (bounds, loop set-up, epilogue) is paid by 4 lanes instead
+// of 32: on graphs whose nodes have a few dozen neighbors that cost, not memory, is the limit.
+// Nodes above hub_min_edges still go to the wide-block kernel.  The chunk knobs do not apply.
+constexpr int GROUP_LANES = 4;
+constexpr int GROUP_BLOCK = 256;
+constexpr int GROUP_ROWS_PER_BLOCK = GROUP_BLOCK / GROUP_LANES;
+
+template <int REMOTE_MODE>
+__device__ __forceinline__ void group_gather_list(float4& acc, const AggParams& P, const float* const* s_peer,
+                                                  const int32_t* __restrict__ ci, int beg, int end,
+                                                  const char* base, bool remote, int l, unsigned group_mask) {
+    const unsigned row_bytes = 64u;
+    // every group of the warp keeps stepping until the longest list among them is done
+    for (int e = beg; __any_sync(0xffffffffu, e < end); e += GROUP_LANES) {
+        const int my = (e + l < end) ? __ldcs(ci + e + l) : -1;
+        float4 v[GROUP_LANES];
+        bool ok[GROUP_LANES];
+#pragma unroll
+        for (int j = 0; j < GROUP_LANES; j++) {
+            const int got = __shfl_sync(0xffffffffu, my, j, GROUP_LANES);
+            ok[j] = got >= 0;
+            const int nid = max(got, 0);
+            const float* src;
+            if (REMOTE_MODE == 1 && remote) {
+                const unsigned owner = (unsigned)(((unsigned long long)(unsigned)nid * P.div_magic) >> P.div_shift);
+                src = s_peer[owner] + (long long)(nid - (int)owner * P.node_per_pe) * 16 + l * 4;
+            } else {
+                src = reinterpret_cast<const float*>(base + (long long)nid * row_bytes);
+            }
+            if (ok[j]) v[j] = __ldg(reinterpret_cast<const float4*>(src));
+        }
+#pragma unroll
+        for (int j = 0; j < GROUP_LANES; j++)
+            if (ok[j]) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+    }
+    (void)group_mask;
+}
+
+template <int REMOTE_MODE>
+__global__ void __launch_bounds__(GROUP_BLOCK, 4) sag_group_per_node_kernel(const AggParams P) {
+    __shared__ const float* s_peer[MGGB_MAX_PES];
+    if (REMOTE_MODE == 1) {
+        if (threadIdx.x < MGGB_MAX_PES) s_peer[threadIdx.x] = P.peer[threadIdx.x < P.num_pes ? threadIdx.x : 0];
+        __syncthreads();
+    }
+    const int l = threadIdx.x & (GROUP_LANES - 1);
+    const long long slot = (long long)blockIdx.x * GROUP_ROWS_PER_BLOCK + (threadIdx.x / GROUP_LANES);
+    const bool active = slot < P.num_rows;
+    int row = 0, lbeg = 0, lend = 0, rbeg = 0, rend = 0;
+    if (active) {
+        row = P.row_order ? P.row_order[slot] : (int)slot;
+        lbeg = P.rp_l[row]; lend = P.rp_l[row + 1];
+        rbeg = P.rp_r[row]; rend = P.rp_r[row + 1];
+    }
+    // A node above the hub threshold is handed to the wide-block kernel by its group's leader (if the
+    // list has room).  The decision is shared with an unconditional group-wide shuffle.
+    const bool hub = active && P.hub_count != nullptr && (lend - lbeg) + (rend - rbeg) > P.hub_min_edges;
+    int handed = 0;
+    if (hub && l == 0) {
+        const int hs = atomicAdd(P.hub_count, 1);
+        handed = hs < P.hub_cap;
+        if (handed) P.hub_list[hs] = row;
+    }
+    handed = __shfl_sync(0xffffffffu, handed, 0, GROUP_LANES);
+    const bool mine = active && !handed;   // false: nothing to aggregate or store here
+    if (!mine) { lbeg = lend = rbeg = rend = 0; }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const char* lbase = reinterpret_cast<const char*>(P.peer[P.pe] + l * 4) - (long long)P.lb * 64;
+    const char* rbase = reinterpret_cast<const char*>(P.peer[0] + l * 4);
+    group_gather_list<REMOTE_MODE>(acc, P, s_peer, P.ci_l, lbeg, lend, lbase, false, l, 0);
+    if (REMOTE_MODE != 0)
+        group_gather_list<REMOTE_MODE>(acc, P, s_peer, P.ci_r, rbeg, rend, rbase, true, l, 0);
+    if (!mine) return;
+    const long long o = (long long)row * 16 + l * 4;
+    if (P.row_scale) { const float sc = P.row_scale[row]; acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc; }
+    if (P.mode == MODE_GIN) {
+        const float4 x = *reinterpret_cast<const float4*>(P.peer[P.pe] + o);
+        acc.x += P.self_scale * x.x; acc.y += P.self_scale * x.y; acc.z += P.self_scale * x.z; acc.w += P.self_scale * x.w;
+    } else if (P.mode == MODE_ACCUMULATE) {
+        const float4 x = *reinterpret_cast<const float4*>(P.out + o);
+        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+    }
+    *reinterpret_cast<float4*>(P.out + o) = acc;
+    for (int k = 0; k < P.num_publish; k++) *reinterpret_cast<float4*>(P.publish[k] + o) = acc;
+}
+
 // Hub rows: a fixed grid of 16-warp blocks walks the list the kernel above filled.  Each listed row
 // is aggregated by ONE block with the same warp/chunk mapping (just more warps), so its result does
 // not depend on the order in which rows were appended.  The next batch of neighbor ids is
@@ -441,6 +530,34 @@ int hub_scratch(cudaStream_t st, HubScratch* out) {
     return MGGB_OK;
 }
 
+constexpr int GROUP_HUB_MIN_EDGES = 1024;   // longer lists would leave one 4-lane group as the kernel's tail
+
+// The group-per-node kernel, then the hub kernel for whatever it deferred.
+int launch_group_per_node(const AggParams& P, cudaStream_t st) {
+    int mode = 1;
+    if (P.num_pes == 1) mode = 0;
+    else {
+        bool one_matrix = true;
+        for (int p = 1; p < P.num_pes; p++)
+            one_matrix = one_matrix && (P.peer[p] == P.peer[0] + (long long)p * P.node_per_pe * P.dim);
+        if (one_matrix) mode = 2;
+    }
+    if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, sizeof(int), st));
+    const int grid = (P.num_rows + GROUP_ROWS_PER_BLOCK - 1) / GROUP_ROWS_PER_BLOCK;
+    const size_t hub_smem = (size_t)HUB_WARPS * P.dim * sizeof(float);
+    if (mode == 0) sag_group_per_node_kernel<0><<<grid, GROUP_BLOCK, 0, st>>>(P);
+    else if (mode == 1) sag_group_per_node_kernel<1><<<grid, GROUP_BLOCK, 0, st>>>(P);
+    else sag_group_per_node_kernel<2><<<grid, GROUP_BLOCK, 0, st>>>(P);
+    MGGB_CUDA(cudaGetLastError());
+    if (P.hub_count != nullptr) {
+        if (mode == 0) sag_hub_rows_kernel<4, 4, true, 0><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
+        else if (mode == 1) sag_hub_rows_kernel<4, 4, true, 1><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
+        else sag_hub_rows_kernel<4, 4, true, 2><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
+        MGGB_CUDA(cudaGetLastError());
+    }
+    return MGGB_OK;
+}
+
 int aggregate(float* output, const float* const* peer_input, int num_pes, const int32_t* rp_l,
               const int32_t* ci_l, const int32_t* rp_r, const int32_t* ci_r, int32_t lb, int32_t ub,
               int dim, int32_t node_per_pe, int pe, int ps, int wpb, int dist, const float* row_scale,
@@ -492,6 +609,15 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
     }
 
     cudaStream_t st = (cudaStream_t)stream;
+    if ((flags & MGGB_AGG_GROUP_PER_NODE) && dim == 16 && caller_scratch == nullptr) {
+        bool aligned = ((uintptr_t)output % 16 == 0);
+        for (int p = 0; p < num_pes; p++) aligned = aligned && ((uintptr_t)peer_input[p] % 16 == 0);
+        for (int k = 0; k < num_publish; k++) aligned = aligned && ((uintptr_t)publish_out[k] % 16 == 0);
+        if (aligned) {
+            if (P.hub_count != nullptr) P.hub_min_edges = GROUP_HUB_MIN_EDGES;   // 4 lanes are slow on long lists
+            return launch_group_per_node(P, st);
+        }
+    }
     bool vec4 = (dim % 4 == 0);
     for (int p = 0; p < num_pes && vec4; p++) vec4 = ((uintptr_t)peer_input[p] % 16 == 0);
     if (vec4) {

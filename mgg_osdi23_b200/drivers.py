@@ -44,6 +44,7 @@ class Knobs:
     partSize: int = 16
     warpPerBlock: int = 4
     interleaved_dist: int = 1
+    flags: int = 0      # extra MGGB_AGG_* flags (e.g. _lib.AGG_GROUP_PER_NODE for graphs with short neighbor lists)
 
 
 class Shard:
@@ -98,12 +99,12 @@ class Shard:
         self._timed(lambda: api.mgg_SAG_np_div(
             out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim, self.node_per_pe, self.pe,
             knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, accumulate=accumulate, row_scale_=row_scale_,
-            publish=publish, row_order=self.row_order))
+            publish=publish, row_order=self.row_order, flags=knobs.flags))
 
     def aggregate_gin(self, out, sym, dim, knobs: Knobs, eps: float):
         self._timed(lambda: api.mgg_GIN_np_div(
             out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim, self.node_per_pe, self.pe,
-            knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, eps, row_order=self.row_order))
+            knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, eps, row_order=self.row_order, flags=knobs.flags))
 
 
 def nccl_stream_barrier(group=None) -> Callable[[], None]:

@@ -20,7 +20,7 @@ def shard_inputs(x: np.ndarray, G: int):
 
 
 def emulated_aggregate(rp, col, x, G, knobs=(16, 4, 1), gin_eps=None, accumulate=False, init=None,
-                       row_scale=None):
+                       row_scale=None, flags=0):
     """Runs every PE's shard of the aggregation on the current device; returns the [N, dim] result."""
     n, dim = x.shape
     sym_np, npp = shard_inputs(x, G)
@@ -32,7 +32,7 @@ def emulated_aggregate(rp, col, x, G, knobs=(16, 4, 1), gin_eps=None, accumulate
         if sh.rows == 0:
             continue
         o = torch.zeros(sh.rows, dim, device=dev) if init is None else torch.from_numpy(init[sh.lb:sh.ub].copy()).to(dev)
-        k = drivers.Knobs(*knobs)
+        k = drivers.Knobs(*knobs, flags=flags)
         if gin_eps is not None:
             sh.aggregate_gin(o, sym, dim, k, gin_eps)
         else:

@@ -204,3 +204,31 @@ def test_row_order_changes_schedule_not_results():
     torch.cuda.synchronize()
     assert torch.equal(a, b)
     torch.testing.assert_close(c, a + x, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("G", [1, 2, 3])
+def test_group_per_node_kernel(oracle, G):
+    """MGGB_AGG_GROUP_PER_NODE (dim 16): four lanes per node, eight nodes per warp; every epilogue,
+    local and remote lists, empty nodes, nodes above its 1024-neighbor hub threshold."""
+    from mgg_osdi23_b200 import _lib
+    n, dim = 1000, 16
+    rp, col = random_graph(n, 9, seed=31, hubs=[(0, 1500), (5, 1024), (6, 1025), (500, 3000), (999, 40), (998, 0), (2, 0)])
+    x = np.random.default_rng(6).uniform(-0.1, 0.1, (n, dim)).astype(np.float32)
+    want = oracle.sag_f64(x, rp, col)
+    knobs = (16, 1, 1)
+    flag = _lib.AGG_GROUP_PER_NODE
+
+    def run(**kw):
+        import gpu_util
+        return gpu_util.emulated_aggregate(rp, col, x, G, knobs=knobs, flags=flag, **kw)
+
+    np.testing.assert_allclose(run(), want, rtol=RTOL, atol=ATOL)
+    scale = np.random.default_rng(7).uniform(0.5, 1.5, n).astype(np.float32)
+    np.testing.assert_allclose(run(row_scale=scale), want * scale[:, None], rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(run(gin_eps=0.5), want + 1.5 * x, rtol=RTOL, atol=ATOL)
+    init = np.random.default_rng(8).uniform(-1, 1, (n, dim)).astype(np.float32)
+    np.testing.assert_allclose(run(accumulate=True, init=init), want + init, rtol=RTOL, atol=ATOL)
+    # other widths ignore the flag and still give the right sums
+    x8 = np.ascontiguousarray(x[:, :8])
+    import gpu_util
+    np.testing.assert_allclose(gpu_util.emulated_aggregate(rp, col, x8, G, knobs=knobs, flags=flag), oracle.sag_f64(x8, rp, col), rtol=RTOL, atol=ATOL)
