@@ -238,7 +238,7 @@ class GCN2Forward(_Forward):
             api.dense_hidden_new_forward(self.dp2)
             api.softmax_new_forward(self.smx)
 
-    kernels_per_forward = 5   # dense, aggregate, aggregate, dense, softmax
+    kernels_per_forward = 7   # dense, aggregate (+ its hub-row kernel), aggregate (+ hub), dense, softmax
     aggregations_per_forward = 2
 
 
@@ -290,7 +290,7 @@ class GIN5Forward(_Forward):
 
     @property
     def kernels_per_forward(self):
-        return 2 * self.num_layers + 2
+        return 3 * self.num_layers + 2   # dense x (layers+1), aggregate + hub-row kernel per layer, softmax
 
     @property
     def aggregations_per_forward(self):
@@ -314,7 +314,7 @@ class SingleAggregation(_Forward):
         if self.shard.rows:
             self.shard.aggregate(self.out, self.sym_a, self.dim, self.knobs, row_scale_=self.scale)
 
-    kernels_per_forward = 1
+    kernels_per_forward = 2   # the aggregation and its hub-row kernel
     aggregations_per_forward = 1
 
 
