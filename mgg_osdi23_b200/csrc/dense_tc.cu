@@ -44,6 +44,9 @@ constexpr int THREADS = 2 * LOADERS + 128 + 32;  // + 4 epilogue warps + the MMA
 #define MGGB_DENSE_STAGES 4
 #endif
 constexpr int MAX_STAGES = MGGB_DENSE_STAGES;
+// Which warps bring x in: register-staged producers for 8-byte pieces, the cp.async loader/splitter
+// pair for 16-byte pieces (each measured faster on its shapes, see producer_role).
+template <int G> struct UseProducer { static constexpr bool value = (G == 8); };
 // Consecutive K slabs a loader fetches per row visit: 2 for 8-byte pieces (a warp's copy instruction
 // then covers 256 contiguous bytes of a row pair), 1 for 16-byte pieces.  Measured on B200; the copy
 // rate is bound by the number of cp.async instructions an SM keeps in flight (about 40).
@@ -258,6 +261,82 @@ __device__ void splitter_role(const TcParams& P, unsigned char* ring, uint32_t l
     }
 }
 
+// Register-staged producers, used for 8-byte pieces (rows that are only 8-byte aligned, e.g. 602
+// floats); 16-byte pieces use the cp.async loader/splitter pair above.  All eight producer warps load their pieces of slab c+1 into registers with
+// streaming loads, then split slab c (already in registers) into hi/lo straight into its ring stage
+// and hand it to the tensor core.  Measured on B200: an SM keeps only about 40 cp.async instructions
+// in flight (10-20 KB), while plain loads are limited by registers: 256 threads x 2 slabs x 64 bytes
+// = 32 KB in flight per SM here.  Measured (232,965 x 602 -> 16): 0.30 ms against 0.34 ms with
+// cp.async; for 16-byte pieces (2,449,029 x 64 -> 64) cp.async wins, 0.32 ms against 0.37 ms.
+constexpr int PRODUCERS = 2 * LOADERS;
+
+template <int G> struct PVec;
+template <> struct PVec<16> { using T = float4; };
+template <> struct PVec<8> { using T = float2; };
+
+template <int G>
+__device__ void producer_role(const TcParams& P, unsigned char* ring, uint32_t full0, uint32_t empty0,
+                              volatile int* abort_flag, long long first_tile, long long tile_step, long long tiles) {
+    using V = typename PVec<G>::T;
+    constexpr int PPR = 128 / G;                       // pieces per 128-byte slab row
+    constexpr int COUNT = TILE_M * PPR / PRODUCERS;    // pieces per thread and slab
+    constexpr int ROW_STEP = PRODUCERS / PPR;          // rows between a thread's consecutive pieces
+    constexpr uint32_t SMEM_STEP = (ROW_STEP / 8) * 1024;
+    static_assert(ROW_STEP % 8 == 0 && COUNT >= 1, "piece mapping");
+    const int p = threadIdx.x;                         // 0..PRODUCERS-1
+    const int piece = p % PPR, r0 = p / PPR;
+    const uint32_t off0 = swz(r0, piece * G);
+    const int kpiece = piece * (G / 4);
+    const int S = P.stages;
+    const long long my_tiles = first_tile < tiles ? (tiles - first_tile + tile_step - 1) / tile_step : 0;
+    const long long slabs = my_tiles * P.nchunks;
+    const size_t src_step = (size_t)ROW_STEP * P.K;
+
+    auto load_slab = [&](long long c, V* buf) {
+        const long long tile = first_tile + (c / P.nchunks) * tile_step;
+        const int kc = (int)(c % P.nchunks);
+        const long long row0 = tile * TILE_M + r0;
+        const int k = kc * CHUNK_K + kpiece;
+        const float* src0 = P.x + row0 * P.K + k;
+        const bool k_ok = k < P.K;
+        const bool rows_full = tile * TILE_M + TILE_M <= P.n;
+#pragma unroll
+        for (int i = 0; i < COUNT; i++) {
+            V v;
+            if (G == 16) v = V{};
+            if (k_ok && (rows_full || row0 + i * ROW_STEP < P.n)) v = __ldcs(reinterpret_cast<const V*>(src0 + i * src_step));
+            else v = V{};
+            buf[i] = v;
+        }
+    };
+
+    V cur[COUNT], nxt[COUNT];
+    if (slabs > 0) load_slab(0, cur);
+    for (long long c = 0; c < slabs; c++) {
+        if (c + 1 < slabs) load_slab(c + 1, nxt);          // in flight while this slab is split and stored
+        const int s = (int)(c % S);
+        const long long use = c / S;
+        if (use >= 1 && !mbar_wait(empty0 + 8 * s, (unsigned)((use - 1) & 1), abort_flag, 2)) return;
+        unsigned char* stage = ring + (size_t)s * STAGE_BYTES;
+#pragma unroll
+        for (int i = 0; i < COUNT; i++) {
+            const float* v = reinterpret_cast<const float*>(&cur[i]);
+            float h[G / 4], l[G / 4];
+#pragma unroll
+            for (int e = 0; e < G / 4; e++) {
+                h[e] = __uint_as_float(__float_as_uint(v[e]) & TF32_MASK);
+                l[e] = __uint_as_float(__float_as_uint(v[e] - h[e]) & TF32_MASK);
+            }
+            *reinterpret_cast<V*>(stage + off0 + i * SMEM_STEP) = *reinterpret_cast<V*>(h);
+            *reinterpret_cast<V*>(stage + SLAB_BYTES + off0 + i * SMEM_STEP) = *reinterpret_cast<V*>(l);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
+        mbar_arrive(full0 + 8 * s);
+#pragma unroll
+        for (int i = 0; i < COUNT; i++) cur[i] = nxt[i];
+    }
+}
+
 __device__ void mma_role(const TcParams& P, uint32_t ring_base, uint32_t w_hi, uint32_t w_lo, uint32_t full0,
                          uint32_t empty0, uint32_t tfull0, uint32_t tempty0, uint32_t tmem_base,
                          volatile int* abort_flag, long long first_tile, long long tile_step, long long tiles) {
@@ -383,7 +462,11 @@ __global__ void __launch_bounds__(THREADS, 1) dense_tc_kernel(const TcParams P) 
 
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int s = 0; s < MAX_STAGES; s++) { mbar_init(full0 + 8 * s, LOADERS); mbar_init(empty0 + 8 * s, 1); mbar_init(landed0 + 8 * s, LOADERS); }
+        for (int s = 0; s < MAX_STAGES; s++) {
+            mbar_init(full0 + 8 * s, UseProducer<G>::value ? PRODUCERS : LOADERS);
+            mbar_init(empty0 + 8 * s, 1);
+            mbar_init(landed0 + 8 * s, LOADERS);
+        }
         for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 128); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -411,7 +494,9 @@ __global__ void __launch_bounds__(THREADS, 1) dense_tc_kernel(const TcParams P) 
 #ifdef MGGB_DENSE_PROFILE
     const long long role_t0 = clock64();
 #endif
-    if (warp < LOADER_WARPS) {
+    if (UseProducer<G>::value && warp < 2 * LOADER_WARPS) {
+        producer_role<G>(P, ring, full0, empty0, &s_abort, blockIdx.x, gridDim.x, tiles);
+    } else if (warp < LOADER_WARPS) {
         loader_role<G>(P, ring, landed0, empty0, &s_abort, blockIdx.x, gridDim.x, tiles);
     } else if (warp < 2 * LOADER_WARPS) {
         splitter_role<G>(P, ring, landed0, full0, &s_abort, blockIdx.x, gridDim.x, tiles);
