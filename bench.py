@@ -323,8 +323,8 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     model_kind, din, hid, dout, dknobs, desc = CONFIGS[args.config]
-    group = (args.group_per_node or args.config in ("cfg4",)) and not args.no_group_per_node
-    knobs = drivers.Knobs(args.ps or dknobs[0], args.wpb or dknobs[1], args.dist or dknobs[2], flags=4 if group else 0)
+    group_kernel = (args.group_per_node or args.config in ("cfg4",)) and not args.no_group_per_node
+    knobs = drivers.Knobs(args.ps or dknobs[0], args.wpb or dknobs[1], args.dist or dknobs[2], flags=4 if group_kernel else 0)
 
     g = make_graph(args.config, dev, args.scale)
     n = g.num_nodes
@@ -405,6 +405,14 @@ def run_ours(args, rank, world, local_rank):
                       for s in range(nsite)]
     clocks = sampler.stop() if rank == 0 else None
 
+    # ---- where the time of a pass goes (a few extra passes, outside the timed region) ---------------
+    marks = []
+    for _ in range(5):
+        model.forward(barrier, marks)
+    sync_all()
+    spans = len(marks[0]) - 1
+    breakdown = [max_over_ranks(sum(m[i].elapsed_time(m[i + 1]) for m in marks) / len(marks)) for i in range(spans)]
+
     # ---- end to end through the host-buffer entry point ---------------------------------------
     e2e = None
     if not args.no_e2e:
@@ -452,6 +460,8 @@ def run_ours(args, rank, world, local_rank):
             "per_gpu_edges": [{"local": el, "remote": er, "rows": r} for el, er, r in allstats],
             "remote_fraction": sum(er for _, er, _ in allstats) / max(1, total_edges),
             "gpu_launches": args.steps * model.kernels_per_forward * world,
+            "pass_breakdown_ms": {"spans": "stage" + (", barrier, stage" * ((spans - 1) // 2) if world > 1 else ", stage" * (spans - 1)),
+                                  "ms": breakdown},
             "preproc_ms": preproc_ms, "clocks": clocks,
         }
         if not args.no_e2e:

@@ -117,14 +117,26 @@ def nccl_stream_barrier(group=None) -> Callable[[], None]:
     return barrier
 
 
-def run_stages(models: Sequence, barrier: Optional[Callable[[], None]] = None):
-    """Runs every model's stage s (all PEs held by this process), then the barrier, for each s."""
+def run_stages(models: Sequence, barrier: Optional[Callable[[], None]] = None, marks: Optional[list] = None):
+    """Runs every model's stage s (all PEs held by this process), then the barrier, for each s.
+    ``marks``: when a list, a CUDA event is recorded before the first stage and after every stage and
+    barrier, and the events of this pass are appended as one list (for a time breakdown)."""
     n = len(models[0].stages)
+    ev = None
+    if marks is not None:
+        ev = [torch.cuda.Event(enable_timing=True)]
+        ev[0].record()
     for s in range(n):
         for m in models:
             m.stages[s]()
+        if ev is not None:
+            ev.append(torch.cuda.Event(enable_timing=True)); ev[-1].record()
         if barrier is not None and s + 1 < n:
             barrier()
+            if ev is not None:
+                ev.append(torch.cuda.Event(enable_timing=True)); ev[-1].record()
+    if marks is not None:
+        marks.append(ev)
 
 
 class _Forward:
@@ -142,8 +154,8 @@ class _Forward:
         """Where this PE writes its rows of the published matrix (its own buffer, or its slot of a replica)."""
         return sym.own(self.shard.rows, dim)
 
-    def forward(self, barrier=None):
-        run_stages([self], barrier)
+    def forward(self, barrier=None, marks=None):
+        run_stages([self], barrier, marks)
         return self.out
 
     def forward_host(self, x_host: torch.Tensor, barrier=None, chunks: int = 8) -> torch.Tensor:
