@@ -154,7 +154,8 @@ __device__ __forceinline__ void gather_batch(Vec<VEC>& acc, const AggParams& P, 
 // The warp's share is walked as a sequence of batches of up to 32 ids: chunk q of the warp starts
 // at beg + (q*nwarps + warp)*chunk.  The ids of batch t+1 are requested before the rows of batch t
 // are gathered, so the id fetch (from HBM) overlaps the row fetch (mostly from L2).
-template <int LPR, int VEC, bool REMOTE, bool PREFETCH>
+// WALK: 0 chunk by chunk; 1 the same with the next batch of ids requested early; 2 chunks shorter than a batch
+template <int LPR, int VEC, bool REMOTE, int WALK>
 __device__ __forceinline__ void gather_list(Vec<VEC>& acc, const AggParams& P, const float* const* s_peer,
                                             const int32_t* __restrict__ ci, int beg, int end, const char* lbase,
                                             int warp, int nwarps, int lane, int col, bool col_ok) {
@@ -165,6 +166,23 @@ __device__ __forceinline__ void gather_list(Vec<VEC>& acc, const AggParams& P, c
     // so the walk uses unsigned arithmetic.
     const unsigned uend = (unsigned)end, chunk = (unsigned)P.chunk;
     const unsigned block_stride = chunk * (unsigned)nwarps;
+    if (WALK == 2) {
+        // Chunks shorter than a batch: the warp's edges, chunk after chunk, form one virtual sequence
+        // and every batch takes its next 32 of them (lane k's edge sits in the warp's chunk k / chunk),
+        // so that small part_size * interleaved_dist settings still gather 32 rows per batch.
+        for (unsigned k0 = 0;; k0 += 32) {
+            const unsigned k = k0 + (unsigned)lane, q = k / chunk;
+            const unsigned pos = (unsigned)beg + (q * (unsigned)nwarps + (unsigned)warp) * chunk + (k - q * chunk);
+            const unsigned valid = __ballot_sync(0xffffffffu, pos < uend);   // positions grow with k: a prefix of the lanes
+            if (valid == 0u) break;
+            const int cnt = __popc(valid);
+            const int my = pos < uend ? __ldcs(ci + pos) : -1;
+            if (cnt == 32) gather_batch<LPR, VEC, REMOTE, true>(acc, P, s_peer, lbase, row_bytes, my, cnt, g, col, col_ok);
+            else           gather_batch<LPR, VEC, REMOTE, false>(acc, P, s_peer, lbase, row_bytes, my, cnt, g, col, col_ok);
+            if (cnt < 32) break;
+        }
+        return;
+    }
     unsigned cstart = (unsigned)beg + (unsigned)warp * chunk;         // start of the current chunk
     if (cstart >= uend) return;
     unsigned r = 0;                                                   // offset of the batch in its chunk
@@ -177,12 +195,12 @@ __device__ __forceinline__ void gather_list(Vec<VEC>& acc, const AggParams& P, c
         int ncnt = 0, nxt = -1;
         if (more) {
             ncnt = (int)min(32u, min(chunk - nr, uend - (ncs + nr)));
-            if (PREFETCH && lane < ncnt) nxt = __ldcs(ci + ncs + nr + lane);
+            if (WALK == 1 && lane < ncnt) nxt = __ldcs(ci + ncs + nr + lane);
         }
         if (cnt == 32) gather_batch<LPR, VEC, REMOTE, true>(acc, P, s_peer, lbase, row_bytes, my, cnt, g, col, col_ok);
         else           gather_batch<LPR, VEC, REMOTE, false>(acc, P, s_peer, lbase, row_bytes, my, cnt, g, col, col_ok);
         if (!more) break;
-        if (!PREFETCH && lane < ncnt) nxt = __ldcs(ci + ncs + nr + lane);
+        if (WALK != 1 && lane < ncnt) nxt = __ldcs(ci + ncs + nr + lane);
         cstart = ncs; r = nr; cnt = ncnt; my = nxt;
     }
 }
@@ -193,7 +211,7 @@ __device__ __forceinline__ void gather_list(Vec<VEC>& acc, const AggParams& P, c
 //
 // Adds into acc this warp's share (warp `warp` of `nwarps`) of one node's neighbor rows, columns
 // [col, col+VEC).
-template <int LPR, int VEC, int REMOTE_MODE, bool PREFETCH>
+template <int LPR, int VEC, int REMOTE_MODE, int WALK>
 __device__ __forceinline__ void accumulate_row(Vec<VEC>& acc, const AggParams& P, const float* const* s_peer,
                                                int lbeg, int lend, int rbeg, int rend,
                                                int warp, int nwarps, int lane, int col, bool col_ok) {
@@ -205,9 +223,9 @@ __device__ __forceinline__ void accumulate_row(Vec<VEC>& acc, const AggParams& P
     // warp 0, include/neighbor_utils.cuh:1432-1437; only the fp32 summation order differs).
     const int rwarp = (warp + nwarps - (int)(((unsigned)(lend - lbeg) + P.chunk - 1) / P.chunk % nwarps)) % nwarps;
     if (REMOTE_MODE == 1) {
-        gather_list<LPR, VEC, false, PREFETCH>(acc, P, s_peer, P.ci_l, lbeg, lend, lbase, warp, nwarps, lane, col, col_ok);
+        gather_list<LPR, VEC, false, WALK>(acc, P, s_peer, P.ci_l, lbeg, lend, lbase, warp, nwarps, lane, col, col_ok);
         if (rend > rbeg)
-            gather_list<LPR, VEC, true, PREFETCH>(acc, P, s_peer, P.ci_r, rbeg, rend, nullptr, rwarp, nwarps, lane, col, col_ok);
+            gather_list<LPR, VEC, true, WALK>(acc, P, s_peer, P.ci_r, rbeg, rend, nullptr, rwarp, nwarps, lane, col, col_ok);
     } else {
         // both halves are directly addressed: one copy of the gather code walks them in turn
 #pragma unroll 1
@@ -216,7 +234,7 @@ __device__ __forceinline__ void accumulate_row(Vec<VEC>& acc, const AggParams& P
             const int beg = half ? rbeg : lbeg, end = half ? rend : lend;
             const char* base = half ? reinterpret_cast<const char*>(P.peer[0] + col) : lbase;
             if (end > beg)
-                gather_list<LPR, VEC, false, PREFETCH>(acc, P, s_peer, ci, beg, end, base, half ? rwarp : warp, nwarps, lane, col, col_ok);
+                gather_list<LPR, VEC, false, WALK>(acc, P, s_peer, ci, beg, end, base, half ? rwarp : warp, nwarps, lane, col, col_ok);
         }
     }
 }
@@ -224,7 +242,7 @@ __device__ __forceinline__ void accumulate_row(Vec<VEC>& acc, const AggParams& P
 // Aggregates one node with all warps of the block and stores its output row.  s_part: nwarps * dim
 // floats of shared memory.  Ends with the block's threads past a __syncthreads() only on entry, so a
 // caller that loops over rows must synchronise before reusing s_part.
-template <int LPR, int VEC, bool EXACT, int REMOTE_MODE, bool PREFETCH>
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE, int WALK>
 __device__ __forceinline__ void aggregate_row(const AggParams& P, const int row, float* s_part,
                                               const float* const* s_peer) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -239,7 +257,7 @@ __device__ __forceinline__ void aggregate_row(const AggParams& P, const int row,
         const bool col_ok = EXACT || col < P.dim;
         Vec<VEC> acc;
         acc.zero();
-        accumulate_row<LPR, VEC, REMOTE_MODE, PREFETCH>(acc, P, s_peer, lbeg, lend, rbeg, rend, warp, nwarps, lane, col, col_ok);
+        accumulate_row<LPR, VEC, REMOTE_MODE, WALK>(acc, P, s_peer, lbeg, lend, rbeg, rend, warp, nwarps, lane, col, col_ok);
         // fold the 32/LPR sub-warps together
 #pragma unroll
         for (int off = LPR; off < 32; off <<= 1) acc.xor_reduce(off);
@@ -263,7 +281,7 @@ __device__ __forceinline__ void aggregate_row(const AggParams& P, const int row,
 }
 
 // One block per node.  Dynamic shared memory: nwarps * dim floats (the warps' partial rows).
-template <int LPR, int VEC, bool EXACT, int REMOTE_MODE>
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE, int WALK>
 __global__ void __launch_bounds__(512, (LPR <= 4 ? MGGB_AGG_MIN_BLOCKS_NARROW : 1)) sag_np_div_kernel(const AggParams P) {
     extern __shared__ __align__(16) float s_part[];
     __shared__ const float* s_peer[MGGB_MAX_PES];
@@ -292,7 +310,7 @@ __global__ void __launch_bounds__(512, (LPR <= 4 ? MGGB_AGG_MIN_BLOCKS_NARROW : 
             if (s_deferred) return;
         }
     }
-    aggregate_row<LPR, VEC, EXACT, REMOTE_MODE, (LPR <= 4) && MGGB_AGG_PREFETCH_NARROW>(P, row, s_part, s_peer);
+    aggregate_row<LPR, VEC, EXACT, REMOTE_MODE, WALK>(P, row, s_part, s_peer);
 }
 
 // warp_per_block == 1: a warp owns its node outright, so nothing has to meet in shared memory and no
@@ -301,7 +319,7 @@ __global__ void __launch_bounds__(512, (LPR <= 4 ? MGGB_AGG_MIN_BLOCKS_NARROW : 
 // neighbors.  Same edge-to-lane mapping and summation order as the one-warp block above: identical bits.
 constexpr int ROW_WARPS = 8;
 
-template <int LPR, int VEC, bool EXACT, int REMOTE_MODE>
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE, int WALK>
 __global__ void __launch_bounds__(ROW_WARPS * 32, (LPR <= 4 ? 6 : 2)) sag_row_per_warp_kernel(const AggParams P) {
     __shared__ const float* s_peer[MGGB_MAX_PES];
     if (REMOTE_MODE == 1) {
@@ -332,7 +350,7 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, (LPR <= 4 ? 6 : 2)) sag_row_pe
         const bool col_ok = EXACT || col < P.dim;
         Vec<VEC> acc;
         acc.zero();
-        accumulate_row<LPR, VEC, REMOTE_MODE, (LPR <= 4) && MGGB_AGG_PREFETCH_NARROW>(acc, P, s_peer, lbeg, lend, rbeg, rend, 0, 1, lane, col, col_ok);
+        accumulate_row<LPR, VEC, REMOTE_MODE, WALK>(acc, P, s_peer, lbeg, lend, rbeg, rend, 0, 1, lane, col, col_ok);
 #pragma unroll
         for (int off = LPR; off < 32; off <<= 1) acc.xor_reduce(off);
         if (lane < LPR && col_ok) {
@@ -443,7 +461,7 @@ __global__ void __launch_bounds__(GROUP_BLOCK, 4) sag_group_per_node_kernel(cons
 // is aggregated by ONE block with the same warp/chunk mapping (just more warps), so its result does
 // not depend on the order in which rows were appended.  The next batch of neighbor ids is
 // prefetched here: a hub's warps run hundreds of batches back to back.
-template <int LPR, int VEC, bool EXACT, int REMOTE_MODE>
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE, int WALK>
 __global__ void __launch_bounds__(512, 2) sag_hub_rows_kernel(const AggParams P) {
     extern __shared__ __align__(16) float s_part[];
     __shared__ const float* s_peer[MGGB_MAX_PES];
@@ -451,7 +469,7 @@ __global__ void __launch_bounds__(512, 2) sag_hub_rows_kernel(const AggParams P)
     __syncthreads();
     const int count = min(*P.hub_count, P.hub_cap);
     for (int i = blockIdx.x; i < count; i += gridDim.x) {
-        aggregate_row<LPR, VEC, EXACT, REMOTE_MODE, true>(P, P.hub_list[i], s_part, s_peer);
+        aggregate_row<LPR, VEC, EXACT, REMOTE_MODE, WALK>(P, P.hub_list[i], s_part, s_peer);
         __syncthreads();   // s_part is reused by the next row
     }
 }
@@ -488,25 +506,32 @@ int launch_exact(const AggParams& P, int wpb, cudaStream_t st) {
     return launch_kernel<LPR, VEC, EXACT, 1>(P, wpb, st);
 }
 
-template <int LPR, int VEC, bool EXACT, int REMOTE_MODE>
-int launch_kernel(const AggParams& P, int wpb, cudaStream_t st) {
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE, int WALK>
+int launch_walk(const AggParams& P, int wpb, cudaStream_t st) {
     const size_t smem = (size_t)wpb * P.dim * sizeof(float);
     if (smem > 48 * 1024)
-        MGGB_CUDA(cudaFuncSetAttribute(sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        MGGB_CUDA(cudaFuncSetAttribute(sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE, WALK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, sizeof(int), st));
     if (wpb == 1 && LPR <= 4)   // wide rows stream from HBM and measured no better this way
-        sag_row_per_warp_kernel<LPR, VEC, EXACT, REMOTE_MODE><<<(P.num_rows + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, st>>>(P);
+        sag_row_per_warp_kernel<LPR, VEC, EXACT, REMOTE_MODE, WALK><<<(P.num_rows + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, st>>>(P);
     else
-        sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE><<<P.num_rows, wpb * 32, smem, st>>>(P);
+        sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE, WALK><<<P.num_rows, wpb * 32, smem, st>>>(P);
     MGGB_CUDA(cudaGetLastError());
     if (P.hub_count != nullptr) {
         const size_t hub_smem = (size_t)HUB_WARPS * P.dim * sizeof(float);
         if (hub_smem > 48 * 1024)
-            MGGB_CUDA(cudaFuncSetAttribute(sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem));
-        sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
+            MGGB_CUDA(cudaFuncSetAttribute(sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE, (WALK == 2 ? 2 : 1)>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem));
+        sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE, (WALK == 2 ? 2 : 1)><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
         MGGB_CUDA(cudaGetLastError());
     }
     return MGGB_OK;
+}
+
+// Chunks shorter than one 32-id batch get the walk that packs several chunks into a batch.
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE>
+int launch_kernel(const AggParams& P, int wpb, cudaStream_t st) {
+    if (P.chunk < 32) return launch_walk<LPR, VEC, EXACT, REMOTE_MODE, 2>(P, wpb, st);
+    return launch_walk<LPR, VEC, EXACT, REMOTE_MODE, ((LPR <= 4) && MGGB_AGG_PREFETCH_NARROW) ? 1 : 0>(P, wpb, st);
 }
 
 // Hub work list: per (device, stream) so that calls ordered on one stream reuse it safely and calls
@@ -550,9 +575,9 @@ int launch_group_per_node(const AggParams& P, cudaStream_t st) {
     else sag_group_per_node_kernel<2><<<grid, GROUP_BLOCK, 0, st>>>(P);
     MGGB_CUDA(cudaGetLastError());
     if (P.hub_count != nullptr) {
-        if (mode == 0) sag_hub_rows_kernel<4, 4, true, 0><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
-        else if (mode == 1) sag_hub_rows_kernel<4, 4, true, 1><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
-        else sag_hub_rows_kernel<4, 4, true, 2><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
+        if (mode == 0) sag_hub_rows_kernel<4, 4, true, 0, 1><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
+        else if (mode == 1) sag_hub_rows_kernel<4, 4, true, 1, 1><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
+        else sag_hub_rows_kernel<4, 4, true, 2, 1><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
         MGGB_CUDA(cudaGetLastError());
     }
     return MGGB_OK;
