@@ -38,7 +38,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4"])
+    ap.add_argument("--config", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (quick checks only; not a bench value)")
     ap.add_argument("--ps", type=int, default=None)
     ap.add_argument("--wpb", type=int, default=None)
@@ -62,6 +62,7 @@ CONFIGS = {
     "cfg2": ("gcn2", 602, 16, 41, (32, 4, 2), "Reddit-shaped power-law graph 232,965 nodes ~114.6M edges, GCN-2 602-16-41"),
     "cfg3": ("gin5", 100, 64, 47, (16, 1, 2), "products-shaped power-law graph 2,449,029 nodes ~123.7M edges, GIN-5 hidden 64"),
     "cfg4": ("agg", 16, 16, 16, (32, 1, 1), "skewed directed R-MAT 4,206,785 nodes ~101.3M edges, one aggregation dim 16"),
+    "cfg5": ("gcn2", 128, 16, 172, (32, 4, 2), "symmetric R-MAT 111M nodes ~3.2B edges built shard-locally (64-bit row pointers), GCN-2 128-16-172"),
 }
 
 
@@ -240,6 +241,9 @@ def run_reference(args, rank, world):
     import torch
     if rank != 0:
         return
+    if args.config == "cfg5":
+        print(json.dumps({"impl": "reference", "unavailable": "config 5 is never materialised as one graph (built shard by shard); the host reference needs the whole CSR"}), flush=True)
+        return
     from mgg_osdi23_b200 import graphgen as gg
     model, din, hid, dout, _, desc = CONFIGS[args.config]
     dev = "cuda" if torch.cuda.is_available() else "cpu"
@@ -326,13 +330,24 @@ def run_ours(args, rank, world, local_rank):
     group_kernel = (args.group_per_node or args.config in ("cfg4",)) and not args.no_group_per_node
     knobs = drivers.Knobs(args.ps or dknobs[0], args.wpb or dknobs[1], args.dist or dknobs[2], flags=4 if group_kernel else 0)
 
-    g = make_graph(args.config, dev, args.scale)
+    shard_local = args.config == "cfg5"          # too large to replicate: every rank builds only its rows
+    if shard_local:
+        shift = 0
+        while args.scale < 1.0 and (1 << shift) * args.scale < 1.0:
+            shift += 1
+        g = gg.config5_shard(rank, world, device=dev, scale_shift=shift)
+    else:
+        g = make_graph(args.config, dev, args.scale)
     n = g.num_nodes
     rp_host, col_host = g.row_ptr.cpu().numpy(), g.col_idx.cpu().numpy()
     t0 = time.perf_counter()
-    shard = drivers.Shard(rp_host, col_host, rank, world, device=dev)
+    shard = drivers.Shard(rp_host, col_host, rank, world, device=dev, num_nodes=n, shard_local=shard_local)
     preproc_ms = (time.perf_counter() - t0) * 1e3
     g_meta, g_edges = g.meta, g.num_edges
+    if shard_local and world > 1:                 # stored edges of the whole graph = sum over the shards
+        t = torch.tensor([g_edges], dtype=torch.int64, device=dev)
+        dist.all_reduce(t)
+        g_edges = int(t.item())
     del g
     torch.cuda.empty_cache()
 
@@ -470,7 +485,7 @@ def run_ours(args, rank, world, local_rank):
             line["e2e"] = {"value": naggs * total_edges / (e2e_ms * 1e-3), "unit": "edges/s", "ms_per_step": e2e_ms,
                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                            "note": "pinned host features -> device, forward, probabilities -> pinned host; graph structure resident"}
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not shard_local:
             line["cpu_baseline"] = cpu_baseline(args, rp_host, col_host, n, din, weights, norm, naggs, total_edges, g_meta)
         print(json.dumps(line), flush=True)
 

@@ -88,25 +88,31 @@ def shard_range(num_nodes: int, num_gpus: int, pe: int):
     return a.value, b.value, c.value
 
 
-def split_CSR(origin_ptr, origin_col_idx, lb: int, ub: int):
+def split_CSR(origin_ptr, origin_col_idx, lb: int, ub: int, *, first_row: int = 0):
     """Returns ``[local_ptr, remote_ptr, local_col_idx, remote_col_idx]`` (int32 numpy arrays), in the
-    reference's order.  ``origin_ptr`` may be int32 or int64."""
+    reference's order.  ``origin_ptr`` may be int32 or int64.
+
+    ``first_row``: ``origin_ptr[0]`` belongs to that global row.  The reference hands every rank the
+    whole graph's pointers (first_row = 0); a rank that holds only its own rows' pointers (a graph
+    too large to replicate) passes ``first_row = lb`` and gets the same four arrays."""
     ptr = np.ascontiguousarray(origin_ptr)
     if ptr.dtype not in (np.int32, np.int64):
         ptr = ptr.astype(np.int64)
     col = np.ascontiguousarray(origin_col_idx, dtype=np.int32)
-    if ub > len(ptr) - 1:
-        raise ValueError(f"ub={ub} exceeds the {len(ptr) - 1} rows of the graph")
+    if lb < first_row or ub - first_row > len(ptr) - 1:
+        raise ValueError(f"rows [{lb}, {ub}) are not inside the {len(ptr) - 1} rows held from row {first_row}")
     wide = ptr.dtype == np.int64
     count = lib.mggb_split_csr_count_i64 if wide else lib.mggb_split_csr_count
     fill = lib.mggb_split_csr_fill_i64 if wide else lib.mggb_split_csr_fill
+    # the C entry points only read row_ptr[lb .. ub]: pass the address row 0 would have
+    base = C.c_void_p(ptr.ctypes.data - first_row * ptr.itemsize)
     nl, nr = C.c_int64(), C.c_int64()
-    check(count(_np_ptr(ptr), _np_ptr(col), lb, ub, C.byref(nl), C.byref(nr)))
+    check(count(base, _np_ptr(col), lb, ub, C.byref(nl), C.byref(nr)))
     local_ptr = np.empty(ub - lb + 1, np.int32)
     remote_ptr = np.empty(ub - lb + 1, np.int32)
     local_col = np.empty(nl.value, np.int32)
     remote_col = np.empty(nr.value, np.int32)
-    check(fill(_np_ptr(ptr), _np_ptr(col), lb, ub, _np_ptr(local_ptr), _np_ptr(remote_ptr),
+    check(fill(base, _np_ptr(col), lb, ub, _np_ptr(local_ptr), _np_ptr(remote_ptr),
                _np_ptr(local_col), _np_ptr(remote_col)))
     return [local_ptr, remote_ptr, local_col, remote_col]
 

@@ -51,13 +51,18 @@ class Shard:
     """What one PE holds of the graph: its node range and the split CSR on the device."""
 
     def __init__(self, row_ptr, col_idx, pe: int, num_pes: int, device=None, num_nodes: Optional[int] = None,
-                 order_rows: Optional[bool] = None):
+                 order_rows: Optional[bool] = None, shard_local: bool = False):
+        """row_ptr / col_idx: the whole graph's CSR (what every rank of the reference loads), or, with
+        ``shard_local=True`` and ``num_nodes`` given, only this PE's rows (pointers starting at 0 for
+        row lb): for graphs too large to replicate per rank."""
         row_ptr = np.ascontiguousarray(row_ptr)
+        if shard_local and num_nodes is None:
+            raise ValueError("shard_local needs num_nodes")
         n = len(row_ptr) - 1 if num_nodes is None else num_nodes
         self.pe, self.num_pes, self.num_nodes = pe, num_pes, n
         self.node_per_pe, self.lb, self.ub = api.shard_range(n, num_pes, pe)
         self.rows = self.ub - self.lb
-        lp, rp, lc, rc = api.split_CSR(row_ptr, col_idx, self.lb, self.ub)
+        lp, rp, lc, rc = api.split_CSR(row_ptr, col_idx, self.lb, self.ub, first_row=self.lb if shard_local else 0)
         self.e_local, self.e_remote = int(lc.size), int(rc.size)
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.device = dev

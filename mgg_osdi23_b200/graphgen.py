@@ -221,3 +221,44 @@ def config4_graph(device="cpu", seed=0, scale_shift: int = 0) -> Graph:
     n = 4_206_785 >> scale_shift
     return rmat_graph(23 - scale_shift, 101_300_000 >> scale_shift, 0.6, 0.15, 0.15, seed=seed,
                       symmetric=False, self_loops=False, num_nodes=n, device=device)
+
+
+def rmat_shard(scale: int, n_pairs: int, num_nodes: int, lb: int, ub: int, a=0.57, b=0.19, c=0.19, seed=0,
+               device="cpu", batch: int = 1 << 25) -> Graph:
+    """The rows [lb, ub) of the symmetrised R-MAT graph on ``num_nodes`` ids, built WITHOUT
+    materialising the whole graph: every rank walks the same ``n_pairs`` sampled pairs in batches
+    (counter-based randomness, so all ranks see the same pairs) and keeps, in both directions, only
+    the edges whose source row it owns.  Pairs with an endpoint >= num_nodes are dropped.  Returns a
+    Graph whose ``row_ptr`` (int64, ub-lb+1 entries, starting at 0) indexes the shard's rows and
+    whose ``col_idx`` holds global ids; self-loops are added for the shard's own rows."""
+    rows = ub - lb
+    kept = []
+    for first in range(0, n_pairs, batch):
+        cnt = min(batch, n_pairs - first)
+        s, d = rmat_edges(scale, cnt, a, b, c, seed, device, first)
+        ok = (s < num_nodes) & (d < num_nodes)
+        s, d = s[ok], d[ok]
+        fwd = (s >= lb) & (s < ub)
+        bwd = (d >= lb) & (d < ub)
+        kept.append(torch.cat([(s[fwd] - lb) * num_nodes + d[fwd], (d[bwd] - lb) * num_nodes + s[bwd]]))
+        if len(kept) >= 8:       # keep the working set bounded: deduplicate as we go
+            kept = [torch.unique(torch.cat(kept))]
+    ids = torch.arange(lb, ub, dtype=torch.int64, device=device)
+    kept.append((ids - lb) * num_nodes + ids)
+    keys = torch.unique(torch.cat(kept), sorted=True)
+    src = keys // num_nodes
+    col = (keys - src * num_nodes).to(torch.int32)
+    row_ptr = torch.zeros(rows + 1, dtype=torch.int64, device=keys.device)
+    torch.cumsum(torch.bincount(src, minlength=rows), 0, out=row_ptr[1:])
+    meta = dict(kind="rmat_shard", scale=scale, sampled_pairs=n_pairs, lb=lb, ub=ub, seed=seed)
+    return Graph(num_nodes, row_ptr, col, meta)
+
+
+def config5_shard(pe: int, num_pes: int, device="cpu", seed=0, scale_shift: int = 0) -> Graph:
+    """paper100M-shaped: 111 M nodes, ~3.2 B stored edges (1.6 B sampled pairs), symmetric R-MAT; only
+    PE ``pe``'s rows are built (see rmat_shard).  scale_shift halves ids and pairs that many times."""
+    n = 111_000_000 >> scale_shift
+    npp = (n + num_pes - 1) // num_pes
+    lb = min(n, pe * npp)
+    ub = min(n, lb + npp)
+    return rmat_shard(27 - scale_shift, 1_600_000_000 >> scale_shift, n, lb, ub, seed=seed, device=device)

@@ -1,0 +1,58 @@
+"""bench.py prints one JSON line with the agreed keys: the CPU arm runs anywhere, the GPU arm on a B200."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+COMMON = {"metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+          "vs_baseline", "dtype", "data", "config", "e2e", "gpu_launches"}
+
+
+def _run(*args, timeout=600):
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), *args], capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1, r.stdout[-2000:]
+    return json.loads(lines[0])
+
+
+def test_reference_arm_line():
+    d = _run("--impl", "reference", "--config", "cfg1", "--steps", "2", "--warmup", "1")
+    assert COMMON <= set(d) and d["impl"] == "reference"
+    assert d["unit"] == "edges/s" and d["value"] > 0 and d["higher_is_better"] is True
+    assert d["cpu_baseline"]["kind"] in ("reference", "port") and d["cpu_baseline"]["cores"] == 1
+    assert d["cpu_baseline"]["value"] == d["value"]
+    assert d["e2e"] == {"value": d["value"], "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert d["config"]["workload"].startswith("cfg1") and d["gpu_launches"] == 0
+
+
+def test_gpu_arm_needs_a_gpu_or_runs():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("covered by the gpu-marked test")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--config", "cfg1"], capture_output=True, text=True, timeout=300)
+    assert r.returncode != 0 and "no CPU path" in (r.stdout + r.stderr)
+
+
+@pytest.mark.gpu
+def test_gpu_arm_line():
+    d = _run("--config", "cfg1", "--steps", "5", "--warmup", "3")
+    assert COMMON | {"roofline", "cpu_baseline", "clocks"} <= set(d) and "impl" not in d
+    assert d["n_gpus"] == 1 and d["warmup"] >= 3 and d["steps"] == 5 and d["data"] == "synthetic" and d["dtype"] == "f32"
+    rf = d["roofline"]
+    assert rf["bound"] == "hbm" and rf["unit"] == "GB/s" and rf["peak"] > 1000 and abs(rf["frac"] - rf["achieved"] / rf["peak"]) < 1e-9
+    assert d["e2e"]["h2d_bytes_per_step"] == d["config"]["nodes"] * 16 * 4 and d["e2e"]["d2h_bytes_per_step"] > 0
+    assert d["e2e"]["value"] != d["value"] and d["gpu_launches"] == 5 * 2
+    assert d["cpu_baseline"]["value"] > 0 and "sample" in d["cpu_baseline"]
+    assert d["clocks"]["sm_max_mhz"] and isinstance(d["clocks"]["reasons"], list)
+
+
+@pytest.mark.gpu
+def test_config5_shard_local_path_small():
+    """Config 5's code path (shard-local graph, 64-bit row pointers, 128-16-172 GCN) at 1/16384 scale."""
+    d = _run("--config", "cfg5", "--scale", "0.00006", "--steps", "3", "--warmup", "3")
+    assert d["config"]["workload"].startswith("cfg5") and d["config"]["nodes"] == 111_000_000 >> 15
+    assert d["config"]["classes"] == 172 and d["value"] > 0 and "cpu_baseline" not in d

@@ -97,3 +97,19 @@ def test_degree_order():
     assert mgg.degree_order(lp, rp).tolist() == [2, 1, 0, 3, 4]      # totals 2 5 7 2 0; ties keep row order
     assert mgg.degree_order(lp).tolist() == [2, 0, 3, 1, 4]
     assert mgg.degree_order(np.zeros(1, np.int32)).size == 0
+
+
+def test_split_from_shard_local_rows(oracle):
+    """A rank that holds only its own rows' pointers (rebased to 0) gets the same split."""
+    g = gg.rmat_graph(10, 8000, seed=6)
+    rp, col = g.row_ptr.numpy(), g.col_idx.numpy()
+    for G in (2, 3):
+        for pe in range(G):
+            npp, lb, ub = mgg.shard_range(g.num_nodes, G, pe)
+            local_rp = (rp[lb:ub + 1] - rp[lb]).astype(np.int64)
+            local_col = col[rp[lb]:rp[ub]]
+            got = mgg.split_CSR(local_rp, local_col, lb, ub, first_row=lb)
+            for u, v in zip(got, oracle.split_csr(rp.astype(np.int32), col, lb, ub)):
+                assert np.array_equal(u, v)
+    with pytest.raises(ValueError):
+        mgg.split_CSR(np.zeros(3, np.int64), np.zeros(0, np.int32), 5, 9, first_row=6)
