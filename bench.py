@@ -47,7 +47,7 @@ def parse_args():
                     help="how peers see a layer's output: 'peer' = rows pulled from the owner inside the aggregation "
                          "kernel; 'replica' = rows pushed into every PE's copy by the producing kernel; 'auto' = replica "
                          "when there are peers and the copy fits")
-    ap.add_argument("--group-per-node", action="store_true", help="aggregate with 4 lanes per node (MGGB_AGG_GROUP_PER_NODE); default for cfg4")
+    ap.add_argument("--group-per-node", action="store_true", help="aggregate with 4 lanes per node (MGGB_AGG_GROUP_PER_NODE); default for cfg4 and cfg5")
     ap.add_argument("--no-group-per-node", action="store_true")
     ap.add_argument("--dense", default="auto", choices=["auto", "simt"],
                     help="'simt' forces the CUDA-core dense kernel (A/B against the tensor-core one)")
@@ -62,7 +62,7 @@ CONFIGS = {
     "cfg2": ("gcn2", 602, 16, 41, (32, 4, 2), "Reddit-shaped power-law graph 232,965 nodes ~114.6M edges, GCN-2 602-16-41"),
     "cfg3": ("gin5", 100, 64, 47, (16, 1, 2), "products-shaped power-law graph 2,449,029 nodes ~123.7M edges, GIN-5 hidden 64"),
     "cfg4": ("agg", 16, 16, 16, (32, 1, 1), "skewed directed R-MAT 4,206,785 nodes ~101.3M edges, one aggregation dim 16"),
-    "cfg5": ("gcn2", 128, 16, 172, (32, 4, 2), "symmetric R-MAT 111M nodes ~3.2B edges built shard-locally (64-bit row pointers), GCN-2 128-16-172"),
+    "cfg5": ("gcn2", 128, 16, 172, (32, 1, 1), "symmetric R-MAT 111M nodes ~3.2B edges built shard-locally (64-bit row pointers), GCN-2 128-16-172"),
 }
 
 
@@ -327,7 +327,7 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     model_kind, din, hid, dout, dknobs, desc = CONFIGS[args.config]
-    group_kernel = (args.group_per_node or args.config in ("cfg4",)) and not args.no_group_per_node
+    group_kernel = (args.group_per_node or args.config in ("cfg4", "cfg5")) and not args.no_group_per_node
     knobs = drivers.Knobs(args.ps or dknobs[0], args.wpb or dknobs[1], args.dist or dknobs[2], flags=4 if group_kernel else 0)
 
     shard_local = args.config == "cfg5"          # too large to replicate: every rank builds only its rows
