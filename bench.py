@@ -47,6 +47,10 @@ def parse_args():
                     help="how peers see a layer's output: 'peer' = rows pulled from the owner inside the aggregation "
                          "kernel; 'replica' = rows pushed into every PE's copy by the producing kernel; 'auto' = replica "
                          "when there are peers and the copy fits")
+    ap.add_argument("--keep-logits", action="store_true",
+                    help="also store the last dense layer's output (the fused dense+softmax kernel writes only the probabilities by default)")
+    ap.add_argument("--row-order", default="auto", choices=["auto", "degree", "natural"],
+                    help="block schedule of the aggregation: rows by decreasing degree, or in id order (auto: the driver's default)")
     ap.add_argument("--group-per-node", action="store_true", help="aggregate with 4 lanes per node (MGGB_AGG_GROUP_PER_NODE); default for cfg4 and cfg5")
     ap.add_argument("--no-group-per-node", action="store_true")
     ap.add_argument("--dense", default="auto", choices=["auto", "simt"],
@@ -316,7 +320,7 @@ def run_ours(args, rank, world, local_rank):
     import numpy as np
     import torch
     import torch.distributed as dist
-    from mgg_osdi23_b200 import drivers, graphgen as gg
+    from mgg_osdi23_b200 import api, drivers, graphgen as gg
     from mgg_osdi23_b200.symmem import SymmetricBuffer, ReplicaBuffer
 
     if not torch.cuda.is_available():
@@ -341,7 +345,8 @@ def run_ours(args, rank, world, local_rank):
     n = g.num_nodes
     rp_host, col_host = g.row_ptr.cpu().numpy(), g.col_idx.cpu().numpy()
     t0 = time.perf_counter()
-    shard = drivers.Shard(rp_host, col_host, rank, world, device=dev, num_nodes=n, shard_local=shard_local)
+    shard = drivers.Shard(rp_host, col_host, rank, world, device=dev, num_nodes=n, shard_local=shard_local,
+                          order_rows={"auto": None, "degree": True, "natural": False}[args.row_order])
     preproc_ms = (time.perf_counter() - t0) * 1e3
     g_meta, g_edges = g.meta, g.num_edges
     if shard_local and world > 1:                 # stored edges of the whole graph = sum over the shards
@@ -354,9 +359,7 @@ def run_ours(args, rank, world, local_rank):
     npp = shard.node_per_pe
     fetch = args.fetch
     if fetch == "auto":
-        fetch = "replica" if world > 1 and model_kind != "agg" and world * npp * hid * 4 < (8 << 30) else "peer"
-    if fetch == "replica" and model_kind == "agg":
-        raise SystemExit("--fetch replica needs a producing layer in front of the aggregation; the single-aggregation configs pull from peers")
+        fetch = "replica" if world > 1 and world * npp * hid * 4 < (8 << 30) else "peer"
     if fetch == "replica":
         sym_a = ReplicaBuffer(npp, hid, group, rank, world)
         sym_b = ReplicaBuffer(npp, hid, group, rank, world)
@@ -373,6 +376,7 @@ def run_ours(args, rank, world, local_rank):
                                     dense_flags=4 if args.dense == "simt" else 0)
     else:
         model = drivers.SingleAggregation(shard, hid, sym_a, knobs, norm=norm)
+    model.keep_logits = args.keep_logits
     x_dev = gg.features(shard.rows, din, seed=1, device=dev, first_row=shard.lb)
     if model_kind == "agg" and norm == "sym":
         x_dev = x_dev * shard.inv_sqrt_degree()[:, None]
@@ -395,6 +399,13 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def sum_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
     # ---- device-resident timing ---------------------------------------------------------------
     for _ in range(max(args.warmup, 3)):
         model.forward(barrier)
@@ -406,12 +417,14 @@ def run_ours(args, rank, world, local_rank):
     shard.event_sink = agg_events
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
+    launches0 = api.kernel_launches[0]
     e0.record()
     for _ in range(args.steps):
         model.forward(barrier)
     e1.record()
     sync_all()
     shard.event_sink = None
+    launches = api.kernel_launches[0] - launches0      # this rank's kernels in the timed region
     step_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     agg_ms_local = sum(a.elapsed_time(b) for a, b in agg_events) / max(1, len(agg_events))
     agg_ms = max_over_ranks(agg_ms_local)
@@ -472,9 +485,10 @@ def run_ours(args, rank, world, local_rank):
                          "aggregation_roofline_ms": t_roof * 1e3, "aggregation_roofline_frac": t_roof * 1e3 / agg_ms,
                          "nvlink_gbs_assumed": NVLINK_GBS},
             "fetch": fetch, "dense_kernel": "cuda-core" if args.dense == "simt" else "tcgen05 where the shape fits",
+            "last_layer": "dense + softmax in one kernel" + (", logits stored too" if args.keep_logits else ", logits not stored"),
             "per_gpu_edges": [{"local": el, "remote": er, "rows": r} for el, er, r in allstats],
             "remote_fraction": sum(er for _, er, _ in allstats) / max(1, total_edges),
-            "gpu_launches": args.steps * model.kernels_per_forward * world,
+            "gpu_launches": int(sum_over_ranks(launches)),
             "pass_breakdown_ms": {"spans": "stage" + (", barrier, stage" * ((spans - 1) // 2) if world > 1 else ", stage" * (spans - 1)),
                                   "ms": breakdown},
             "preproc_ms": preproc_ms, "clocks": clocks,

@@ -209,3 +209,12 @@ inline void dense_hidden_new_forward(dense_param_new_hidden* dp, cudaStream_t st
 inline void softmax_new_forward(softmax_new_param* smx, cudaStream_t stream = nullptr) {
     MGG_COMPAT_CHECK(mggb_softmax_forward(smx->d_out, smx->d_in, smx->numNodes, smx->dim, stream));
 }
+// dense_hidden_new_forward(dp); softmax_new_forward(smx); (src/mgg_np_div_mem.cu:220-226) as one kernel that
+// also stores the logits in dp->d_out; falls back to the two calls for shapes the fused kernel refuses.
+inline void dense_hidden_softmax_new_forward(dense_param_new_hidden* dp, softmax_new_param* smx, cudaStream_t stream = nullptr) {
+    if (smx->d_in == dp->d_out && smx->numNodes == dp->numNodes && smx->dim == dp->dim2 &&
+        mggb_dense_softmax_forward(smx->d_out, dp->d_out, dp->d_in, dp->d_W, dp->numNodes, dp->dim1, dp->dim2, stream) == MGGB_OK)
+        return;
+    dense_hidden_new_forward(dp, stream);
+    softmax_new_forward(smx, stream);
+}

@@ -175,6 +175,31 @@ int mggb_gin_np_div_ordered(float* output, const float* const* peer_input, int n
                             int32_t lb, int32_t ub, int dim, int32_t node_per_pe, int pe,
                             int part_size, int warp_per_block, int interleaved_dist,
                             float eps, int flags, const int32_t* row_order, void* stream);
+/* The same two operators over a LIST of rows: row_list holds row_count distinct shard-relative row ids
+ * (0 .. ub-lb-1); only those rows of `output` are written, block k taking row_list[k].  A caller that
+ * cuts a shard into row blocks can hand each finished block to the next kernel (the dense update and
+ * its push to the peers) while the aggregation of the following block is still running.  No
+ * counterpart in the reference, which always launches the whole shard. */
+int mggb_sag_np_div_rows(float* output, const float* const* peer_input, int num_pes,
+                         const int32_t* row_ptr_l, const int32_t* col_idx_l,
+                         const int32_t* row_ptr_r, const int32_t* col_idx_r,
+                         int32_t lb, int32_t ub, int dim, int32_t node_per_pe, int pe,
+                         int part_size, int warp_per_block, int interleaved_dist,
+                         const float* row_scale, int flags,
+                         float* const* publish_out, int num_publish,
+                         const int32_t* row_list, int64_t row_count, void* stream);
+int mggb_gin_np_div_rows(float* output, const float* const* peer_input, int num_pes,
+                         const int32_t* row_ptr_l, const int32_t* col_idx_l,
+                         const int32_t* row_ptr_r, const int32_t* col_idx_r,
+                         int32_t lb, int32_t ub, int dim, int32_t node_per_pe, int pe,
+                         int part_size, int warp_per_block, int interleaved_dist,
+                         float eps, int flags, const int32_t* row_list, int64_t row_count, void* stream);
+/* Copies in[0, count) floats to every publish_out[k][0, count) with consecutive threads on consecutive
+ * addresses.  For rows that a kernel wrote in a scattered order (an aggregation walking its rows by
+ * degree): pushing them to the peers' replicas afterwards, as one contiguous run, moves the same bytes
+ * over NVLink in full-width writes instead of one row-sized write per row.  No counterpart in the
+ * reference (its PEs pull rows; nothing is pushed). */
+int mggb_publish_rows(const float* in, int64_t count, float* const* publish_out, int num_publish, void* stream);
 /* Host helper: order[k] = the shard row with the k-th largest neighbor count (local + remote; ties
  * in row order).  row_ptr_r may be NULL.  No counterpart in the reference. */
 int mggb_degree_order(const int32_t* row_ptr_l, const int32_t* row_ptr_r, int32_t num_rows, int32_t* order);
@@ -234,6 +259,17 @@ int mggb_dense_device_status(int* status, int reset);
 /* Replaces softmax_new_forward (include/gnn_layer.cuh:36-40; descriptors include/layer_new.cuh:80-85):
  * max-subtracted softmax over the dim classes of each row; in and out may alias. */
 int mggb_softmax_forward(float* out, const float* in, int64_t n, int dim, void* stream);
+
+/* The last layer in one pass: out[n, dim2] = softmax over each row of x[n, dim1] * w[dim1, dim2].
+ * Replaces the pair dense_hidden_new_forward + softmax_new_forward at the end of both models
+ * (src/mgg_np_div_mem.cu:220-226, src/mgg_np_div_gin_mem.cu:220-222) without writing the logits to
+ * memory and reading them back; pass a non-NULL `logits` [n, dim2] to keep them as well.  fp32 FMA
+ * product as in the CUDA-core dense kernel, max-subtracted exp / sum with the exponential taken on
+ * the special-function unit (relative error below 1e-5 for every term that is not flushed to 0).
+ * Returns MGGB_ERR_UNSUPPORTED when dim2 > 256 or w and the staging rows need more than
+ * 160 KiB of shared memory; call the two separate entry points then. */
+int mggb_dense_softmax_forward(float* out, float* logits, const float* x, const float* w, int64_t n,
+                               int dim1, int dim2, void* stream);
 
 /* out[i,:] = scale[i] * in[i,:] (in and out may alias); scale[i] = 1/sqrt(row_ptr[i+1]-row_ptr[i]),
  * 0 for empty rows.  Helpers for symmetric normalisation; no counterpart in the reference, whose

@@ -63,10 +63,16 @@ SIGNATURES = {
                                 _int, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp, _vp],
     "mggb_gin_np_div_ordered": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
                                 _int, _int, _int, _f, _int, _vp, _vp],
+    "mggb_sag_np_div_rows": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
+                             _int, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp, _i64, _vp],
+    "mggb_gin_np_div_rows": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
+                             _int, _int, _int, _f, _int, _vp, _i64, _vp],
+    "mggb_publish_rows": [_vp, _i64, C.POINTER(_vp), _int, _vp],
     "mggb_degree_order": [_vp, _vp, _i32, _vp],
     "mggb_dense_forward": [_vp, _vp, _vp, _i64, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp],
     "mggb_dense_device_status": [C.POINTER(_int), _int],
     "mggb_softmax_forward": [_vp, _vp, _i64, _int, _vp],
+    "mggb_dense_softmax_forward": [_vp, _vp, _vp, _vp, _i64, _int, _int, _vp],
     "mggb_row_scale": [_vp, _vp, _vp, _i64, _int, _vp],
     "mggb_inv_sqrt_degree": [_vp, _vp, _vp, _i64, _vp],
     "mggb_graph_file_info": [C.c_char_p, C.c_char_p, _pi64, _pi64],

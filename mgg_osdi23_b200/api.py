@@ -31,9 +31,22 @@ from ._lib import lib, check
 __all__ = [
     "shard_range", "split_CSR", "build_part", "mgg_SAG_np_div", "mgg_GIN_np_div",
     "dense_param_new_beg", "dense_param_new_hidden", "softmax_new_param",
-    "dense_beg_new_forward", "dense_hidden_new_forward", "softmax_new_forward",
-    "dense_forward", "softmax_forward", "row_scale", "inv_sqrt_degree", "degree_order",
+    "dense_beg_new_forward", "dense_hidden_new_forward", "softmax_new_forward", "dense_hidden_softmax_new_forward",
+    "dense_forward", "softmax_forward", "dense_softmax_forward", "dense_softmax_fits", "publish_rows", "row_scale", "inv_sqrt_degree", "degree_order",
 ]
+
+
+# Kernels launched through this module since import (each wrapper adds what its call launches):
+# lets a benchmark report how many kernels one timed pass really issued.
+kernel_launches = [0]
+
+
+def _count_aggregation(dim: int, warpPerBlock: int, flags: int, rows) -> None:
+    if rows is not None and rows.numel() == 0:
+        return
+    # the hub-row kernel follows whenever the library keeps a hub list (mggb_sag_np_div's default)
+    hub = not (flags & _lib.AGG_NO_HUB_SPLIT) and warpPerBlock <= 8 and 16 * dim * 4 <= 200 * 1024
+    kernel_launches[0] += 2 if hub else 1
 
 
 # ---- helpers ------------------------------------------------------------------------------------
@@ -150,8 +163,10 @@ def degree_order(row_ptr_l, row_ptr_r=None):
 def mgg_SAG_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r, column_index_r,
                    lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist,
                    *, accumulate: bool = True, row_scale_: torch.Tensor | None = None, publish=None,
-                   row_order: torch.Tensor | None = None, flags: int = 0):
+                   row_order: torch.Tensor | None = None, rows: torch.Tensor | None = None, flags: int = 0):
     """``output[b,:] (+)= sum of the local and remote neighbors' rows`` for the shard ``[lb, ub)``.
+    ``rows`` (int32 device tensor of shard-relative row ids, each at most once): only those rows are
+    computed, in that block order; ``output`` is still the whole shard's matrix.
 
     ``input`` is this PE's symmetric embedding buffer: a tensor when there is one PE, otherwise the
     table of all PEs' buffers (see ``_peer_table``).  ``accumulate=True`` is the reference's
@@ -159,6 +174,17 @@ def mgg_SAG_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r
     that also receive every output row, see ``mggb_sag_np_div``."""
     table, num_pes = _peer_table(input)
     pub, npub = _publish_table(publish)
+    if ub > lb:
+        _count_aggregation(dim, warpPerBlock, flags, rows)
+    if rows is not None:
+        check(lib.mggb_sag_np_div_rows(
+            _dev_ptr(output, torch.float32, "output"), table, num_pes,
+            _dev_ptr(row_pointers_l, torch.int32, "row_pointers_l"), _dev_ptr(column_index_l, torch.int32, "column_index_l"),
+            _dev_ptr(row_pointers_r, torch.int32, "row_pointers_r"), _dev_ptr(column_index_r, torch.int32, "column_index_r"),
+            lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist,
+            _dev_ptr(row_scale_, torch.float32, "row_scale"), (_lib.AGG_ACCUMULATE if accumulate else 0) | flags, pub, npub,
+            _dev_ptr(rows, torch.int32, "rows"), rows.numel(), _stream()))
+        return
     check(lib.mggb_sag_np_div_ordered(
         _dev_ptr(output, torch.float32, "output"), table, num_pes,
         _dev_ptr(row_pointers_l, torch.int32, "row_pointers_l"), _dev_ptr(column_index_l, torch.int32, "column_index_l"),
@@ -170,9 +196,20 @@ def mgg_SAG_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r
 
 def mgg_GIN_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r, column_index_r,
                    lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist, eps,
-                   *, row_order: torch.Tensor | None = None, flags: int = 0):
-    """``output[b,:] = (1+eps) * input_self[b,:] + sum`` (``include/neighbor_utils.cuh:1660-1665``)."""
+                   *, row_order: torch.Tensor | None = None, rows: torch.Tensor | None = None, flags: int = 0):
+    """``output[b,:] = (1+eps) * input_self[b,:] + sum`` (``include/neighbor_utils.cuh:1660-1665``).
+    ``rows``: as for ``mgg_SAG_np_div``."""
     table, num_pes = _peer_table(input)
+    if ub > lb:
+        _count_aggregation(dim, warpPerBlock, flags, rows)
+    if rows is not None:
+        check(lib.mggb_gin_np_div_rows(
+            _dev_ptr(output, torch.float32, "output"), table, num_pes,
+            _dev_ptr(row_pointers_l, torch.int32, "row_pointers_l"), _dev_ptr(column_index_l, torch.int32, "column_index_l"),
+            _dev_ptr(row_pointers_r, torch.int32, "row_pointers_r"), _dev_ptr(column_index_r, torch.int32, "column_index_r"),
+            lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist, float(eps), flags,
+            _dev_ptr(rows, torch.int32, "rows"), rows.numel(), _stream()))
+        return
     check(lib.mggb_gin_np_div_ordered(
         _dev_ptr(output, torch.float32, "output"), table, num_pes,
         _dev_ptr(row_pointers_l, torch.int32, "row_pointers_l"), _dev_ptr(column_index_l, torch.int32, "column_index_l"),
@@ -188,6 +225,7 @@ def dense_forward(out, x, w, row_scale_=None, relu=False, flags=0, publish=None)
     dim2 = w.shape[1]
     if w.shape[0] != dim1 or tuple(out.shape) != (n, dim2):
         raise ValueError(f"shape mismatch: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    kernel_launches[0] += 1 if n else 0
     check(lib.mggb_dense_forward(_dev_ptr(out, torch.float32, "out"), _dev_ptr(x, torch.float32, "x"),
                                  _dev_ptr(w, torch.float32, "w"), n, dim1, dim2,
                                  _dev_ptr(row_scale_, torch.float32, "row_scale"),
@@ -196,12 +234,48 @@ def dense_forward(out, x, w, row_scale_=None, relu=False, flags=0, publish=None)
 
 def softmax_forward(out, inp):
     n, dim = inp.shape
+    kernel_launches[0] += 1 if n else 0
     check(lib.mggb_softmax_forward(_dev_ptr(out, torch.float32, "out"), _dev_ptr(inp, torch.float32, "in"),
                                    n, dim, _stream()))
 
 
+def dense_softmax_forward(out, x, w, logits=None):
+    """out = softmax_rows(x @ w) in one kernel (the models' last dense layer and softmax,
+    ``src/mgg_np_div_mem.cu:220-226``); ``logits`` (optional) also receives x @ w.  Raises MggbError with
+    status ERR_UNSUPPORTED for shapes the fused kernel does not take."""
+    n, dim1 = x.shape
+    dim2 = w.shape[1]
+    if w.shape[0] != dim1 or tuple(out.shape) != (n, dim2) or (logits is not None and tuple(logits.shape) != (n, dim2)):
+        raise ValueError(f"shape mismatch: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    kernel_launches[0] += 1 if n else 0
+    check(lib.mggb_dense_softmax_forward(_dev_ptr(out, torch.float32, "out"), _dev_ptr(logits, torch.float32, "logits"),
+                                         _dev_ptr(x, torch.float32, "x"), _dev_ptr(w, torch.float32, "w"),
+                                         n, dim1, dim2, _stream()))
+
+
+def dense_softmax_fits(dim1: int, dim2: int) -> bool:
+    """Whether ``dense_softmax_forward`` takes this shape (dim2 <= 256 and w plus the staging rows within 160 KiB)."""
+    j = (dim2 + 31) // 32
+    return j <= 8 and (dim1 * 32 * j + 64 * dim1) * 4 <= 160 * 1024
+
+
+def publish_rows(src: torch.Tensor, publish, elem_offset: int = 0):
+    """Copies the contiguous fp32 tensor ``src`` to ``base + elem_offset`` floats of every entry of
+    ``publish`` (tensors or device addresses, e.g. ``ReplicaBuffer.publish``): pushes rows that a kernel
+    wrote locally into the peers' replicas with full-width stores."""
+    if not publish or src.numel() == 0:
+        return
+    if not src.is_contiguous():
+        raise ValueError("publish_rows: src must be contiguous")
+    dst = [(p.data_ptr() if isinstance(p, torch.Tensor) else int(p)) + 4 * elem_offset for p in publish]
+    pub, npub = _publish_table(dst)
+    kernel_launches[0] += 1
+    check(lib.mggb_publish_rows(_dev_ptr(src, torch.float32, "src"), src.numel(), pub, npub, _stream()))
+
+
 def row_scale(out, inp, scale):
     n, dim = inp.shape
+    kernel_launches[0] += 1 if n else 0
     check(lib.mggb_row_scale(_dev_ptr(out, torch.float32, "out"), _dev_ptr(inp, torch.float32, "in"),
                              _dev_ptr(scale, torch.float32, "scale"), n, dim, _stream()))
 
@@ -286,6 +360,24 @@ def dense_beg_new_forward(dp: dense_param_new_beg):
 def dense_hidden_new_forward(dp: dense_param_new_hidden):
     """``include/gnn_layer.cuh:48-52``."""
     dp._forward()
+
+
+def dense_hidden_softmax_new_forward(dp: dense_param_new_hidden, smx: softmax_new_param, keep_logits: bool = False):
+    """``dense_hidden_new_forward(dp); softmax_new_forward(smx);`` (``src/mgg_np_div_mem.cu:220-226``) as one
+    kernel when smx reads what dp writes and the shape fits; the two separate calls otherwise.  Without
+    ``keep_logits`` the fused pass leaves dp.d_out untouched."""
+    fused = (smx.d_in.data_ptr() == dp.d_out.data_ptr() and smx.numNodes == dp.numNodes and smx.dim == dp.dim2
+             and dp.row_scale is None and not dp.publish and not dp.relu and not (dp.flags & _lib.DENSE_RELU)
+             and dense_softmax_fits(dp.dim1, dp.dim2))
+    if not fused:
+        dp._forward()
+        softmax_new_forward(smx)
+        return
+    n = dp.numNodes
+    x = dp.d_in.reshape(-1)[: n * dp.dim1].view(n, dp.dim1)
+    o = smx.d_out.reshape(-1)[: n * dp.dim2].view(n, dp.dim2)
+    lg = dp.d_out.reshape(-1)[: n * dp.dim2].view(n, dp.dim2) if keep_logits else None
+    dense_softmax_forward(o, x, dp.d_W, lg)
 
 
 def softmax_new_forward(smx: softmax_new_param):

@@ -16,6 +16,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libmggb200.so")
 BIN_DIR = os.path.join(PKG_DIR, "bin")
+OBJ_DIR = os.path.join(PKG_DIR, "_obj")
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
@@ -43,16 +44,35 @@ def _stale(target: str, deps) -> bool:
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
+    """Compiles every source to an object file under ``_obj/`` (only the stale ones, in parallel) and
+    links them into the shared library."""
+    from concurrent.futures import ThreadPoolExecutor
     srcs = _sources()
-    deps = srcs + glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(PKG_DIR, "..", "include", "*.h"))
-    if not force and not _stale(LIB_PATH, deps):
+    headers = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(PKG_DIR, "..", "include", "*.h"))
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    objs = [os.path.join(OBJ_DIR, os.path.basename(src) + ".o") for src in srcs]
+
+    def compile_one(pair):
+        src, obj = pair
+        if not force and not _stale(obj, [src] + headers):
+            return None
+        cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+        return src, subprocess.run(cmd, capture_output=True, text=True)
+
+    with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 4)) as pool:
+        results = [r for r in pool.map(compile_one, zip(srcs, objs)) if r is not None]
+    for src, r in results:
+        if verbose or r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed compiling {src}")
+    if not results and not _stale(LIB_PATH, objs):
         return LIB_PATH
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-shared"] + srcs + ["-o", LIB_PATH, "-lgomp", "-lcuda"]
-    r = subprocess.run(cmd, capture_output=True, text=True)
+    r = subprocess.run([_nvcc(), "-shared"] + objs + ["-o", LIB_PATH, "-lgomp", "-lcuda"], capture_output=True, text=True)
     if verbose or r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)
     if r.returncode != 0:
-        raise RuntimeError("nvcc failed building libmggb200.so")
+        raise RuntimeError("nvcc failed linking libmggb200.so")
     return LIB_PATH
 
 

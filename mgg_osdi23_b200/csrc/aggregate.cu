@@ -587,7 +587,8 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
               const int32_t* ci_l, const int32_t* rp_r, const int32_t* ci_r, int32_t lb, int32_t ub,
               int dim, int32_t node_per_pe, int pe, int ps, int wpb, int dist, const float* row_scale,
               int mode, float self_scale, float* const* publish_out, int num_publish, int flags, void* stream,
-              const HubScratch* caller_scratch = nullptr, int caller_scratch_cap = 0, const int32_t* row_order = nullptr) {
+              const HubScratch* caller_scratch = nullptr, int caller_scratch_cap = 0, const int32_t* row_order = nullptr,
+              int64_t row_count = -1) {
     MGGB_REQUIRE(num_publish >= 0 && num_publish <= MGGB_MAX_PES && (num_publish == 0 || publish_out),
                  "aggregate: num_publish must be in [0,%d] with a non-NULL table (got %d)", MGGB_MAX_PES, num_publish);
     for (int k = 0; k < num_publish; k++)
@@ -617,6 +618,11 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
     P.num_publish = num_publish;
     for (int k = 0; k < num_publish; k++) P.publish[k] = publish_out[k];
     P.lb = lb; P.num_rows = ub - lb; P.node_per_pe = node_per_pe;
+    if (row_count >= 0) {   // only the listed rows (ids relative to lb)
+        if (row_count == 0) return MGGB_OK;
+        MGGB_REQUIRE(row_order != nullptr && row_count <= ub - lb, "aggregate: row_count needs a row list of at most ub-lb rows (got %lld)", (long long)row_count);
+        P.num_rows = (int32_t)row_count;
+    }
     P.dim = dim; P.pe = pe; P.num_pes = num_pes;
     P.chunk = (int)std::min<long long>((long long)ps * dist, 1 << 24);  // larger than any useful chunk: same walk
     make_divider((uint32_t)node_per_pe, &P.div_magic, &P.div_shift);
@@ -774,6 +780,30 @@ int mggb_gin_np_div_ordered(float* output, const float* const* peer_input, int n
     return aggregate(output, peer_input, num_pes, row_ptr_l, col_idx_l, row_ptr_r, col_idx_r, lb, ub, dim,
                      node_per_pe, pe, part_size, warp_per_block, interleaved_dist, nullptr, MODE_GIN,
                      1.0f + eps, nullptr, 0, flags, stream, nullptr, 0, row_order);
+}
+
+int mggb_sag_np_div_rows(float* output, const float* const* peer_input, int num_pes,
+                         const int32_t* row_ptr_l, const int32_t* col_idx_l, const int32_t* row_ptr_r,
+                         const int32_t* col_idx_r, int32_t lb, int32_t ub, int dim, int32_t node_per_pe,
+                         int pe, int part_size, int warp_per_block, int interleaved_dist,
+                         const float* row_scale, int flags, float* const* publish_out, int num_publish,
+                         const int32_t* row_list, int64_t row_count, void* stream) {
+    MGGB_REQUIRE(row_count >= 0, "sag_np_div_rows: row_count must be >= 0 (got %lld)", (long long)row_count);
+    return aggregate(output, peer_input, num_pes, row_ptr_l, col_idx_l, row_ptr_r, col_idx_r, lb, ub, dim,
+                     node_per_pe, pe, part_size, warp_per_block, interleaved_dist, row_scale,
+                     (flags & MGGB_AGG_ACCUMULATE) ? MODE_ACCUMULATE : MODE_OVERWRITE, 0.f, publish_out,
+                     num_publish, flags, stream, nullptr, 0, row_list, row_count);
+}
+
+int mggb_gin_np_div_rows(float* output, const float* const* peer_input, int num_pes,
+                         const int32_t* row_ptr_l, const int32_t* col_idx_l, const int32_t* row_ptr_r,
+                         const int32_t* col_idx_r, int32_t lb, int32_t ub, int dim, int32_t node_per_pe,
+                         int pe, int part_size, int warp_per_block, int interleaved_dist, float eps,
+                         int flags, const int32_t* row_list, int64_t row_count, void* stream) {
+    MGGB_REQUIRE(row_count >= 0, "gin_np_div_rows: row_count must be >= 0 (got %lld)", (long long)row_count);
+    return aggregate(output, peer_input, num_pes, row_ptr_l, col_idx_l, row_ptr_r, col_idx_r, lb, ub, dim,
+                     node_per_pe, pe, part_size, warp_per_block, interleaved_dist, nullptr, MODE_GIN,
+                     1.0f + eps, nullptr, 0, flags, stream, nullptr, 0, row_list, row_count);
 }
 
 }  // extern "C"

@@ -39,8 +39,8 @@ int main(int argc, char* argv[]) {
                 MGG_COMPAT_CHECK(mggb_gin_np_div(d_agg[p.pe], table[k % 2].data(), G, p.rp_l, p.ci_l, p.rp_r, p.ci_r,
                                                  (int32_t)p.lb, (int32_t)p.ub, a.hiddenSize, (int32_t)p.nodesPerPE, p.pe,
                                                  a.partSize, a.warpPerBlock, a.interleaved_dist, eps, 0, p.stream));
-                dense_hidden_new_forward(dph[p.pe][k], p.stream);
-                if (k == layers - 1) softmax_new_forward(smx[p.pe], p.stream);
+                if (k == layers - 1) dense_hidden_softmax_new_forward(dph[p.pe][k], smx[p.pe], p.stream);
+                else dense_hidden_new_forward(dph[p.pe][k], p.stream);
             }
         }
         c.barrier();

@@ -41,8 +41,7 @@ int main(int argc, char* argv[]) {
             c.use(p);
             if (!p.rows()) continue;
             agg(p, d_agg[p.pe], tb);
-            dense_hidden_new_forward(dp2[p.pe], p.stream);
-            softmax_new_forward(smx[p.pe], p.stream);
+            dense_hidden_softmax_new_forward(dp2[p.pe], smx[p.pe], p.stream);
         }
         c.barrier();
     };

@@ -1,0 +1,192 @@
+// Last layer in one pass: out[n, M] = softmax_rows(x[n, K] * w[K, M]), optionally keeping the logits.
+//
+// Stands in for dense_hidden_new_forward followed by softmax_new_forward
+// (src/mgg_np_div_mem.cu:220-226, src/mgg_np_div_gin_mem.cu:220-222; include/gnn_layer.cuh:36-52).
+// Done as two kernels the [n, M] logits are written, read back and the probabilities written
+// (3 * n * M * 4 bytes); fused, only the probabilities leave the chip.  With a wide class count
+// and a narrow hidden width (172 classes from 16 features) the pass is bound by that traffic.
+//
+// A warp owns 8 rows at a time.  Lane l holds output columns l, l+32, ... (J of them) of each of
+// its rows in registers; w sits in shared memory once per block, zero-padded to 32*J columns; the
+// warp's 8 rows of x are staged in shared memory and read back as broadcasts.  Softmax is the
+// max-subtracted exp / sum of the separate kernel, reduced over the warp with shuffles, the 8 rows
+// side by side.
+#include <algorithm>
+#include <cfloat>
+#include <cstdint>
+#include "common.h"
+
+namespace {
+
+constexpr int FS_WARPS = 8;
+constexpr int FS_ROWS = 8;     // rows per warp step
+
+// e^d for d <= 0 as 2^(d * log2 e) on the special-function unit: relative error below 1e-6 * max(1, |d|/10)
+// down to d = -87, flushed to 0 below (the exact value is under 1e-37 there).  The kernel issues one
+// of these per output element, and it is bound by its instruction count.
+__device__ __forceinline__ float exp_neg(float d) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d * 1.4426950408889634f));
+    return r;
+}
+
+template <int J>
+__global__ void __launch_bounds__(FS_WARPS * 32)
+dense_softmax_kernel(float* __restrict__ out, float* __restrict__ logits, const float* __restrict__ x,
+                     const float* __restrict__ w, long long n, int K, int M, int vec_ok) {
+    extern __shared__ __align__(16) float fs_smem[];
+    constexpr int MP = 32 * J;
+    float* Ws = fs_smem;                                   // [K][MP]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* Xs = fs_smem + (size_t)K * MP + (size_t)warp * FS_ROWS * K;   // [FS_ROWS][K]
+    for (int idx = threadIdx.x; idx < K * MP; idx += FS_WARPS * 32) {
+        const int k = idx / MP, c = idx - k * MP;
+        Ws[idx] = c < M ? __ldg(w + (long long)k * M + c) : 0.f;
+    }
+    __syncthreads();
+
+    const long long groups = (n + FS_ROWS - 1) / FS_ROWS;
+    const long long stride = (long long)gridDim.x * FS_WARPS;
+    for (long long g = (long long)blockIdx.x * FS_WARPS + warp; g < groups; g += stride) {
+        const long long row0 = g * FS_ROWS;
+        const int rows = (int)min((long long)FS_ROWS, n - row0);
+        const int count = rows * K;
+        const float* src = x + row0 * K;
+        __syncwarp();                                      // the previous step's reads of Xs are done
+        if (vec_ok) {
+            for (int i = lane * 4; i < FS_ROWS * K; i += 128)
+                *reinterpret_cast<float4*>(Xs + i) = i < count ? __ldcs(reinterpret_cast<const float4*>(src + i))
+                                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+            for (int i = lane; i < FS_ROWS * K; i += 32) Xs[i] = i < count ? __ldcs(src + i) : 0.f;
+        }
+        __syncwarp();
+
+        float acc[FS_ROWS][J];
+#pragma unroll
+        for (int r = 0; r < FS_ROWS; r++)
+#pragma unroll
+            for (int j = 0; j < J; j++) acc[r][j] = 0.f;
+
+        if (vec_ok) {
+            for (int k = 0; k < K; k += 4) {
+                float4 xv[FS_ROWS];
+#pragma unroll
+                for (int r = 0; r < FS_ROWS; r++) xv[r] = *reinterpret_cast<const float4*>(Xs + r * K + k);
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++) {
+                    float wv[J];
+#pragma unroll
+                    for (int j = 0; j < J; j++) wv[j] = Ws[(k + kk) * MP + j * 32 + lane];
+#pragma unroll
+                    for (int r = 0; r < FS_ROWS; r++) {
+                        const float a = kk == 0 ? xv[r].x : kk == 1 ? xv[r].y : kk == 2 ? xv[r].z : xv[r].w;
+#pragma unroll
+                        for (int j = 0; j < J; j++) acc[r][j] = fmaf(a, wv[j], acc[r][j]);
+                    }
+                }
+            }
+        } else {
+            for (int k = 0; k < K; k++) {
+                float wv[J];
+#pragma unroll
+                for (int j = 0; j < J; j++) wv[j] = Ws[k * MP + j * 32 + lane];
+#pragma unroll
+                for (int r = 0; r < FS_ROWS; r++) {
+                    const float a = Xs[r * K + k];
+#pragma unroll
+                    for (int j = 0; j < J; j++) acc[r][j] = fmaf(a, wv[j], acc[r][j]);
+                }
+            }
+        }
+
+        // Softmax of the 8 rows side by side: the shuffle chains of different rows overlap.
+        const bool last_ok = lane < M - 32 * (J - 1);      // only the last column slot can run past M
+        if (logits) {
+#pragma unroll
+            for (int r = 0; r < FS_ROWS; r++)
+#pragma unroll
+                for (int j = 0; j < J; j++)
+                    if (r < rows && (j < J - 1 || last_ok)) __stcs(logits + (row0 + r) * M + j * 32 + lane, acc[r][j]);
+        }
+        float m[FS_ROWS], sum[FS_ROWS];
+#pragma unroll
+        for (int r = 0; r < FS_ROWS; r++) {
+            m[r] = -FLT_MAX;
+#pragma unroll
+            for (int j = 0; j < J; j++)
+                if (j < J - 1 || last_ok) m[r] = fmaxf(m[r], acc[r][j]);
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1)
+#pragma unroll
+            for (int r = 0; r < FS_ROWS; r++) m[r] = fmaxf(m[r], __shfl_xor_sync(0xffffffffu, m[r], off));
+#pragma unroll
+        for (int r = 0; r < FS_ROWS; r++) {
+            sum[r] = 0.f;
+#pragma unroll
+            for (int j = 0; j < J; j++) {
+                acc[r][j] = (j < J - 1 || last_ok) ? exp_neg(acc[r][j] - m[r]) : 0.f;
+                sum[r] += acc[r][j];
+            }
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1)
+#pragma unroll
+            for (int r = 0; r < FS_ROWS; r++) sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], off);
+#pragma unroll
+        for (int r = 0; r < FS_ROWS; r++) {
+            const float inv = 1.f / sum[r];
+            float* dst = out + (row0 + r) * M + lane;
+#pragma unroll
+            for (int j = 0; j < J; j++)
+                if (r < rows && (j < J - 1 || last_ok)) __stcs(dst + j * 32, acc[r][j] * inv);
+        }
+    }
+}
+
+template <int J>
+int launch_fused(float* out, float* logits, const float* x, const float* w, long long n, int K, int M,
+                 int vec_ok, size_t smem, int grid, cudaStream_t st) {
+    if (smem > 48 * 1024)
+        MGGB_CUDA(cudaFuncSetAttribute(dense_softmax_kernel<J>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dense_softmax_kernel<J><<<grid, FS_WARPS * 32, smem, st>>>(out, logits, x, w, n, K, M, vec_ok);
+    MGGB_CUDA(cudaGetLastError());
+    return MGGB_OK;
+}
+
+}  // namespace
+
+extern "C" int mggb_dense_softmax_forward(float* out, float* logits, const float* x, const float* w, int64_t n,
+                                          int dim1, int dim2, void* stream) {
+    MGGB_REQUIRE(out && x && w, "dense_softmax_forward: NULL argument");
+    MGGB_REQUIRE(n >= 0 && dim1 >= 1 && dim2 >= 1, "dense_softmax_forward: need n >= 0, dim1 >= 1, dim2 >= 1 (n=%lld dim1=%d dim2=%d)",
+                 (long long)n, dim1, dim2);
+    MGGB_REQUIRE(out != x && logits != x, "dense_softmax_forward: outputs must not alias x");
+    const int J = (dim2 + 31) / 32;
+    const size_t smem = ((size_t)dim1 * 32 * J + (size_t)FS_WARPS * FS_ROWS * dim1) * sizeof(float);
+    if (J > 8 || smem > 160 * 1024)
+        return mggb::fail(MGGB_ERR_UNSUPPORTED, "dense_softmax_forward: dim1=%d dim2=%d does not fit the fused kernel "
+                          "(dim2 <= 256 and %zu bytes of shared memory <= 160 KiB); call mggb_dense_forward then mggb_softmax_forward",
+                          dim1, dim2, smem);
+    if (n == 0) return MGGB_OK;
+    int dev = 0, sms = 148;
+    MGGB_CUDA(cudaGetDevice(&dev));
+    MGGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long groups = (n + FS_ROWS - 1) / FS_ROWS;
+    const long long blocks = (groups + FS_WARPS - 1) / FS_WARPS;
+    const int per_sm = smem > 64 * 1024 ? 1 : 2;
+    const int grid = (int)std::min<long long>(blocks, (long long)sms * per_sm);
+    const int vec_ok = (dim1 % 4 == 0 && ((uintptr_t)x % 16) == 0) ? 1 : 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (J) {
+        case 1: return launch_fused<1>(out, logits, x, w, n, dim1, dim2, vec_ok, smem, grid, st);
+        case 2: return launch_fused<2>(out, logits, x, w, n, dim1, dim2, vec_ok, smem, grid, st);
+        case 3: return launch_fused<3>(out, logits, x, w, n, dim1, dim2, vec_ok, smem, grid, st);
+        case 4: return launch_fused<4>(out, logits, x, w, n, dim1, dim2, vec_ok, smem, grid, st);
+        case 5: return launch_fused<5>(out, logits, x, w, n, dim1, dim2, vec_ok, smem, grid, st);
+        case 6: return launch_fused<6>(out, logits, x, w, n, dim1, dim2, vec_ok, smem, grid, st);
+        case 7: return launch_fused<7>(out, logits, x, w, n, dim1, dim2, vec_ok, smem, grid, st);
+        default: return launch_fused<8>(out, logits, x, w, n, dim1, dim2, vec_ok, smem, grid, st);
+    }
+}

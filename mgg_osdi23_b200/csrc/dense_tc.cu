@@ -402,17 +402,17 @@ __device__ void epilogue_role(const TcParams& P, float* out_stage, uint32_t tful
                     if (P.relu) v[j] = fmaxf(v[j], 0.f);
                 }
                 const long long o = row * P.M + c0;
-                if ((P.M & 3) == 0 && c0 + 16 <= P.M) {
+                if (out_stage != nullptr) {
+                    // park the row in shared memory; the warp stores its 32 rows coalesced below
+#pragma unroll
+                    for (int j = 0; j < 16; j++) out_stage[lane * (P.Npad + 1) + c0 + j] = v[j];   // odd pitch: no bank conflicts
+                } else if ((P.M & 3) == 0 && c0 + 16 <= P.M) {
 #pragma unroll
                     for (int j = 0; j < 16; j += 4) {
                         const float4 f = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                         *reinterpret_cast<float4*>(P.out + o + j) = f;
                         for (int q = 0; q < P.pub.n; q++) *reinterpret_cast<float4*>(P.pub.dst[q] + o + j) = f;
                     }
-                } else if (out_stage != nullptr) {
-                    // odd row widths: park the row in shared memory, the warp stores it coalesced below
-#pragma unroll
-                    for (int j = 0; j < 16; j++) out_stage[lane * (P.Npad + 1) + c0 + j] = v[j];   // odd pitch: no bank conflicts
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; j++)
@@ -425,18 +425,31 @@ __device__ void epilogue_role(const TcParams& P, float* out_stage, uint32_t tful
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         mbar_arrive(tempty0 + 8 * buf);   // the accumulator is in registers / shared memory: free it early
-        if (out_stage != nullptr && (P.M & 3) != 0) {
-            // the warp's 32 rows are one contiguous run of 32*M floats in the output
+        if (out_stage != nullptr) {
+            // The warp's 32 rows are one contiguous run of 32*M floats in the output (and in every
+            // replica it publishes to): consecutive lanes store consecutive addresses, so a peer
+            // receives full 128- to 512-byte writes instead of one 16-byte piece per row.
             __syncwarp();
             const long long first = tile * TILE_M + quarter * 32;
-            const int rows = (int)max(0LL, min(32LL, P.n - first));
+            const int total = (int)max(0LL, min(32LL, P.n - first)) * P.M;
             const long long o = first * P.M;
-            for (int r = 0; r < rows; r++)
-                for (int c = lane; c < P.M; c += 32) {
-                    const float f = out_stage[r * (P.Npad + 1) + c];
-                    P.out[o + r * P.M + c] = f;
-                    for (int q = 0; q < P.pub.n; q++) P.pub.dst[q][o + r * P.M + c] = f;
+            const float inv_m = 1.0f / (float)P.M;   // (i + 0.5) * inv_m truncates to i / M exactly for i < 2^13
+            if ((P.M & 3) == 0) {
+                for (int i = lane * 4; i < total; i += 128) {
+                    const int r = (int)(((float)i + 0.5f) * inv_m);
+                    const float* src = out_stage + r * (P.Npad + 1) + (i - r * P.M);
+                    const float4 f = make_float4(src[0], src[1], src[2], src[3]);
+                    *reinterpret_cast<float4*>(P.out + o + i) = f;
+                    for (int q = 0; q < P.pub.n; q++) *reinterpret_cast<float4*>(P.pub.dst[q] + o + i) = f;
                 }
+            } else {
+                for (int i = lane; i < total; i += 32) {
+                    const int r = (int)(((float)i + 0.5f) * inv_m);
+                    const float f = out_stage[r * (P.Npad + 1) + (i - r * P.M)];
+                    P.out[o + i] = f;
+                    for (int q = 0; q < P.pub.n; q++) P.pub.dst[q][o + i] = f;
+                }
+            }
             __syncwarp();
         }
     }
@@ -501,7 +514,7 @@ __global__ void __launch_bounds__(THREADS, 1) dense_tc_kernel(const TcParams P) 
     } else if (warp < 2 * LOADER_WARPS) {
         splitter_role<G>(P, ring, landed0, full0, &s_abort, blockIdx.x, gridDim.x, tiles);
     } else if (warp < 2 * LOADER_WARPS + 4) {
-        // staging rows for odd output widths: 32 rows x (Npad+1) floats per epilogue warp, after the barriers
+        // staging rows (odd output widths, publishing calls): 32 rows x (Npad+1) floats per epilogue warp, after the barriers
         float* out_stage = P.stage_out ? reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + 256) +
                                              (size_t)(warp - 2 * LOADER_WARPS) * 32 * (P.Npad + 1) : nullptr;
         epilogue_role(P, out_stage, tfull0, tempty0, tmem_base, &s_abort, blockIdx.x, gridDim.x, tiles);
@@ -535,7 +548,8 @@ int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, in
     if (nchunks < 2) return MGGB_OK;   // one slab per tile leaves the four epilogue warps as the limit: the CUDA-core kernel is faster
     const size_t w_bytes = 2 * (size_t)nchunks * Npad * 128;
     const size_t budget = 225 * 1024;                                      // of the 227 KiB a CTA may use
-    const size_t out_stage_bytes = (dim2 % 4 != 0) ? (size_t)4 * 32 * (Npad + 1) * sizeof(float) : 0;   // coalescing buffer for odd widths
+    // coalescing buffer: for odd widths, and whenever rows are also published to peers
+    const size_t out_stage_bytes = (dim2 % 4 != 0 || num_publish > 0) ? (size_t)4 * 32 * (Npad + 1) * sizeof(float) : 0;
     size_t fixed = w_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + out_stage_bytes;
     bool stage_out = out_stage_bytes != 0;
     if (stage_out && fixed + 2 * STAGE_BYTES > budget) { fixed -= out_stage_bytes; stage_out = false; }   // no room: strided stores

@@ -1,5 +1,7 @@
 // Row-wise helpers around the aggregation: softmax over classes, row scaling, 1/sqrt(degree).
+#include <algorithm>
 #include <cfloat>
+#include <cstdint>
 #include "common.h"
 
 namespace {
@@ -39,6 +41,23 @@ __global__ void inv_sqrt_degree_kernel(float* __restrict__ scale, const int32_t*
     }
 }
 
+// Destinations of a publishing copy (the peers' replicas).
+struct PublishTable {
+    float* dst[MGGB_MAX_PES];
+    int n;
+};
+
+// in[0, count) -> every destination, 16 bytes per thread per step, consecutive threads on consecutive
+// addresses: a peer receives whole 512-byte runs per warp instead of one row per store.
+template <typename T>
+__global__ void __launch_bounds__(256) publish_copy_kernel(const T* __restrict__ in, long long count, const PublishTable pub) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        const T v = in[i];
+        for (int q = 0; q < pub.n; q++) reinterpret_cast<T*>(pub.dst[q])[i] = v;
+    }
+}
+
 int grid_for(long long work_items, int block) {
     long long g = (work_items + block - 1) / block;
     const long long cap = 148LL * 16;
@@ -48,6 +67,33 @@ int grid_for(long long work_items, int block) {
 }  // namespace
 
 extern "C" {
+
+int mggb_publish_rows(const float* in, int64_t count, float* const* publish_out, int num_publish, void* stream) {
+    MGGB_REQUIRE(num_publish >= 0 && num_publish <= MGGB_MAX_PES && (num_publish == 0 || publish_out),
+                 "publish_rows: num_publish must be in [0,%d] with a non-NULL table (got %d)", MGGB_MAX_PES, num_publish);
+    MGGB_REQUIRE(count >= 0 && (count == 0 || in), "publish_rows: need count >= 0 and a non-NULL source");
+    if (count == 0 || num_publish == 0) return MGGB_OK;
+    PublishTable pub{};
+    pub.n = num_publish;
+    bool wide = ((uintptr_t)in % 16 == 0) && (count % 4 == 0);
+    for (int q = 0; q < num_publish; q++) {
+        MGGB_REQUIRE(publish_out[q] != nullptr && publish_out[q] != in, "publish_rows: publish_out[%d] is NULL or the source itself", q);
+        pub.dst[q] = publish_out[q];
+        wide = wide && ((uintptr_t)publish_out[q] % 16 == 0);
+    }
+    // One block per SM at most: enough stores in flight for the links, and room left on every SM for a
+    // kernel that runs beside this one on another stream.
+    int dev = 0, sms = 148;
+    MGGB_CUDA(cudaGetDevice(&dev));
+    MGGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (wide)
+        publish_copy_kernel<float4><<<std::min(grid_for(count / 4, 256), sms), 256, 0, (cudaStream_t)stream>>>(
+            reinterpret_cast<const float4*>(in), count / 4, pub);
+    else
+        publish_copy_kernel<float><<<std::min(grid_for(count, 256), sms), 256, 0, (cudaStream_t)stream>>>(in, count, pub);
+    MGGB_CUDA(cudaGetLastError());
+    return MGGB_OK;
+}
 
 int mggb_softmax_forward(float* out, const float* in, int64_t n, int dim, void* stream) {
     MGGB_REQUIRE(out && in, "softmax_forward: NULL argument");

@@ -28,6 +28,7 @@ How peers see a layer's output is chosen by what is passed as ``sym_a`` / ``sym_
 """
 from __future__ import annotations
 
+from contextlib import contextmanager
 from dataclasses import dataclass
 from typing import Callable, List, Optional, Sequence
 
@@ -71,16 +72,56 @@ class Shard:
         # never hand the kernel a NULL column array, even for an empty half
         self.ci_l = torch.from_numpy(lc if lc.size else np.zeros(1, np.int32)).to(dev)
         self.ci_r = torch.from_numpy(rc if rc.size else np.zeros(1, np.int32)).to(dev)
-        # block schedule: longest rows first, so that no high-degree row is left for the kernel's tail
-        # (measured on B200: 3-6 % faster on 2-8 PEs, where a shard has few blocks per SM; no gain on one PE)
+        # block schedule: rows by decreasing degree.  No high-degree row is left for the kernel's tail
+        # (3-6 % on 2-8 PEs with a block per node), and the nodes that share a warp in the
+        # group-per-node kernel have lists of the same length (2.3x on the skewed R-MAT shape,
+        # where a warp otherwise runs as long as the longest of its eight lists).
         if order_rows is None:
-            order_rows = num_pes > 1
-        self.row_order = torch.from_numpy(api.degree_order(lp, rp)).to(dev) if (order_rows and self.rows) else None
+            order_rows = True
+        self._order_host = api.degree_order(lp, rp) if (order_rows and self.rows) else None
+        self.row_order = torch.from_numpy(self._order_host).to(dev) if self._order_host is not None else None
+        self._blocks = {}
         self._dinv = None
         self.event_sink = None   # when a list: (start, end) CUDA events of every aggregation launch are appended
+        self._in_span = False
+
+    def row_blocks(self, count: int):
+        """The shard cut into ``count`` contiguous row ranges: a list of (r0, r1, rows) with ``rows`` the
+        int32 device list of the range's rows in the shard's block schedule (by decreasing degree, or in
+        id order).  Aggregating the ranges one after the other gives the same output as one call."""
+        if count not in self._blocks:
+            step = (self.rows + count - 1) // count
+            step = (step + 127) // 128 * 128        # whole tiles of the dense kernel
+            out = []
+            for r0 in range(0, self.rows, step):
+                r1 = min(self.rows, r0 + step)
+                if self._order_host is not None:
+                    o = self._order_host
+                    ids = o[(o >= r0) & (o < r1)]
+                else:
+                    ids = np.arange(r0, r1, dtype=np.int32)
+                out.append((r0, r1, torch.from_numpy(np.ascontiguousarray(ids, dtype=np.int32)).to(self.device)))
+            self._blocks[count] = out
+        return self._blocks[count]
+
+    @contextmanager
+    def timed_span(self):
+        """One (start, end) event pair around several aggregation launches on the current stream."""
+        if self.event_sink is None or self._in_span:
+            yield
+            return
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        self._in_span = True
+        try:
+            yield
+        finally:
+            self._in_span = False
+            b.record()
+            self.event_sink.append((a, b))
 
     def _timed(self, launch):
-        if self.event_sink is None:
+        if self.event_sink is None or self._in_span:
             return launch()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
@@ -100,16 +141,18 @@ class Shard:
                 api.inv_sqrt_degree(self._dinv, self.rp_l, self.rp_r)
         return self._dinv
 
-    def aggregate(self, out, sym, dim, knobs: Knobs, accumulate=False, row_scale_=None, publish=None):
+    def aggregate(self, out, sym, dim, knobs: Knobs, accumulate=False, row_scale_=None, publish=None, rows=None):
+        """``rows``: a row list from :meth:`row_blocks` (only those rows are computed); None = the whole shard."""
         self._timed(lambda: api.mgg_SAG_np_div(
             out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim, self.node_per_pe, self.pe,
             knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, accumulate=accumulate, row_scale_=row_scale_,
-            publish=publish, row_order=self.row_order, flags=knobs.flags))
+            publish=publish, row_order=self.row_order, rows=rows, flags=knobs.flags))
 
-    def aggregate_gin(self, out, sym, dim, knobs: Knobs, eps: float):
+    def aggregate_gin(self, out, sym, dim, knobs: Knobs, eps: float, rows=None):
         self._timed(lambda: api.mgg_GIN_np_div(
             out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim, self.node_per_pe, self.pe,
-            knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, eps, row_order=self.row_order, flags=knobs.flags))
+            knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, eps, row_order=self.row_order, rows=rows,
+            flags=knobs.flags))
 
 
 def nccl_stream_barrier(group=None) -> Callable[[], None]:
@@ -154,6 +197,45 @@ class _Forward:
         self._h_out = None
         self._copy_stream = None
         self.first_dense = None     # set by models whose stage 0 is exactly one row-local dense product
+        # True: the last dense layer's output (the logits) is stored as well as the probabilities, as the
+        # reference's separate dense and softmax calls do; False saves that write.
+        self.keep_logits = True
+        # Row blocks per aggregation whose output is pushed to peers: block b's consumer (the dense update
+        # that pushes, or the push itself) runs on a second, high-priority stream while block b+1 is
+        # aggregated, so the NVLink transfer hides behind the gather.  1 = one launch, no second stream.
+        self.overlap_blocks = 4 if (shard.num_pes > 1 and getattr(sym_a, "publish", None)) else 1
+        self.overlap_min_rows = 8192      # rows per block below which cutting the shard does not pay
+        self._side = None
+
+    # An aggregation pushes its rows from its own epilogue only while that is a small transfer: the
+    # epilogue writes one row per store, in the block schedule's (degree) order, and a peer then receives
+    # row-sized writes.  Above this many bytes per pass the rows are pushed by a copy kernel instead.
+    EPILOGUE_PUSH_MAX_BYTES = 16 << 20
+
+    def _blocked(self, aggregate_rows: Callable, consume: Callable[[int, int], None]):
+        """aggregate_rows(rows or None) launches the aggregation of a row list (None: the whole shard) on
+        the current stream; consume(r0, r1) launches whatever reads rows [r0, r1) of its output."""
+        sh = self.shard
+        nblk = self.overlap_blocks
+        if nblk <= 1 or sh.rows < self.overlap_min_rows * nblk:
+            with sh.timed_span():
+                aggregate_rows(None)
+            consume(0, sh.rows)
+            return
+        cur = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = torch.cuda.Stream(priority=-1)
+        side = self._side
+        side.wait_stream(cur)
+        with sh.timed_span():
+            for r0, r1, rows in sh.row_blocks(nblk):
+                aggregate_rows(rows)
+                done = torch.cuda.Event()
+                done.record(cur)
+                side.wait_event(done)
+                with torch.cuda.stream(side):
+                    consume(r0, r1)
+        cur.wait_stream(side)
 
     def _sym_view(self, sym, dim):
         """Where this PE writes its rows of the published matrix (its own buffer, or its slot of a replica)."""
@@ -245,17 +327,26 @@ class GCN2Forward(_Forward):
             api.dense_beg_new_forward(self.dp1)
 
     def _agg1(self):
-        if self.shard.rows:
-            self.shard.aggregate(self._sym_view(self.sym_b, self.hidden), self.sym_a, self.hidden, self.knobs,
-                                 row_scale_=self.scale1, publish=self.sym_b.publish)
+        if not self.shard.rows:
+            return
+        own = self._sym_view(self.sym_b, self.hidden)
+        pub = self.sym_b.publish
+        if not pub or self.shard.rows * self.hidden * 4 * len(pub) <= self.EPILOGUE_PUSH_MAX_BYTES:
+            self.shard.aggregate(own, self.sym_a, self.hidden, self.knobs, row_scale_=self.scale1, publish=pub)
+            return
+        self._blocked(
+            lambda rows: self.shard.aggregate(own, self.sym_a, self.hidden, self.knobs, row_scale_=self.scale1, rows=rows),
+            lambda r0, r1: api.publish_rows(own[r0:r1], pub, elem_offset=r0 * self.hidden))
 
     def _agg2_dense2_softmax(self):
         if self.shard.rows:
             self.shard.aggregate(self.d_agg, self.sym_b, self.hidden, self.knobs, row_scale_=self.scale2)
-            api.dense_hidden_new_forward(self.dp2)
-            api.softmax_new_forward(self.smx)
+            api.dense_hidden_softmax_new_forward(self.dp2, self.smx, self.keep_logits)
 
-    kernels_per_forward = 7   # dense, aggregate (+ its hub-row kernel), aggregate (+ hub), dense, softmax
+    @property
+    def kernels_per_forward(self):
+        # dense, aggregate (+ its hub-row kernel), aggregate (+ hub), then dense+softmax as one kernel or two
+        return 6 if api.dense_softmax_fits(self.hidden, self.out_dim) else 7
     aggregations_per_forward = 2
 
 
@@ -299,15 +390,24 @@ class GIN5Forward(_Forward):
         def stage():
             if not self.shard.rows:
                 return
-            self.shard.aggregate_gin(self.d_agg, self._syms[k % 2], self.hidden, self.knobs, self.eps)
-            api.dense_hidden_new_forward(self.dense[k + 1])
             if k == self.num_layers - 1:
-                api.softmax_new_forward(self.smx)
+                self.shard.aggregate_gin(self.d_agg, self._syms[k % 2], self.hidden, self.knobs, self.eps)
+                api.dense_hidden_softmax_new_forward(self.dense[k + 1], self.smx, self.keep_logits)
+            elif not self.dense[k + 1].publish:
+                self.shard.aggregate_gin(self.d_agg, self._syms[k % 2], self.hidden, self.knobs, self.eps)
+                api.dense_hidden_new_forward(self.dense[k + 1])
+            else:
+                self._blocked(
+                    lambda rows: self.shard.aggregate_gin(self.d_agg, self._syms[k % 2], self.hidden, self.knobs,
+                                                          self.eps, rows=rows),
+                    lambda r0, r1: self.dense[k + 1]._forward_rows(r0, r1))
         return stage
 
     @property
     def kernels_per_forward(self):
-        return 3 * self.num_layers + 2   # dense x (layers+1), aggregate + hub-row kernel per layer, softmax
+        # dense x layers, aggregate + hub-row kernel per layer, then dense+softmax as one kernel or two
+        fused = api.dense_softmax_fits(self.hidden, self.out_dim)
+        return 3 * self.num_layers + (1 if fused else 2)
 
     @property
     def aggregations_per_forward(self):
@@ -325,13 +425,21 @@ class SingleAggregation(_Forward):
         self.d_in = self._sym_view(sym_a, dim)   # in replica mode the caller also fills the peers' slots
         self.out = torch.zeros(rows, dim, dtype=torch.float32, device=shard.device)[: shard.rows]
         self.scale = shard.inv_sqrt_degree() if norm == "sym" else None
-        self.stages = [self._agg]
+        # push mode: the pass starts by pushing this PE's rows into the peers' replicas
+        self.stages = [self._push, self._agg] if getattr(sym_a, "publish", None) else [self._agg]
+
+    def _push(self):
+        if self.shard.rows:
+            api.publish_rows(self.d_in, self.sym_a.publish)
 
     def _agg(self):
         if self.shard.rows:
             self.shard.aggregate(self.out, self.sym_a, self.dim, self.knobs, row_scale_=self.scale)
 
-    kernels_per_forward = 2   # the aggregation and its hub-row kernel
+    @property
+    def kernels_per_forward(self):
+        return len(self.stages) + 1   # (the push,) the aggregation and its hub-row kernel
+
     aggregations_per_forward = 1
 
 
@@ -353,7 +461,8 @@ class LocalReplica:
     def __init__(self, tensors: Sequence[torch.Tensor], pe: int, slot_elems: int):
         self.tensor, self.pe, self.slot_elems = tensors[pe], pe, slot_elems
         self.peer_ptrs = [tensors[pe].data_ptr() + p * slot_elems * 4 for p in range(len(tensors))]
-        self.publish = [t.data_ptr() + pe * slot_elems * 4 for q, t in enumerate(tensors) if q != pe] or None
+        self.publish = [tensors[(pe + k) % len(tensors)].data_ptr() + pe * slot_elems * 4
+                        for k in range(1, len(tensors))] or None
 
     def own(self, rows: int, dim: int) -> torch.Tensor:
         off = self.pe * self.slot_elems

@@ -89,6 +89,34 @@ def _finish(src: torch.Tensor, dst: torch.Tensor, n: int, symmetric: bool, self_
     return torch.unique(keys, sorted=True)
 
 
+def _mix_bits(x: torch.Tensor, bits: int, seed: int) -> torch.Tensor:
+    """A bijection of [0, 2^bits): odd multiplications and xor-shifts, each invertible modulo 2^bits."""
+    mask = (1 << bits) - 1
+    h = max(1, bits // 2)
+    x = (x + (seed * 0x632BE5AB & mask)) & mask
+    x = (x * _GOLD) & mask
+    x = x ^ (x >> h)
+    x = (x * _C1) & mask
+    x = x ^ (x >> (h + 1 if h + 1 < bits else h))
+    x = (x * _C2) & mask
+    return x ^ (x >> h)
+
+
+def relabel_ids(ids: torch.Tensor, n: int, seed: int = 0) -> torch.Tensor:
+    """Pseudo-random permutation of [0, n) applied to ``ids`` (int64): the bit mixer above on the next
+    power of two, walked along its cycle until it lands below n again (cycle walking keeps it a
+    bijection).  Generators whose construction puts the heaviest nodes at the lowest ids (R-MAT) use it
+    so that a node-range partition sees shards of similar size, as with a dataset's arbitrary ids."""
+    bits = max(1, (n - 1).bit_length())
+    out = _mix_bits(ids, bits, seed)
+    bad = torch.nonzero(out >= n).flatten()
+    while bad.numel():
+        v = _mix_bits(out[bad], bits, seed)
+        out[bad] = v
+        bad = bad[v >= n]
+    return out
+
+
 def rmat_edges(scale: int, n_edges: int, a: float, b: float, c: float, seed: int, device="cpu",
                first: int = 0):
     """R-MAT endpoint pairs number [first, first+n_edges) on 2^scale ids (quadrant probabilities a, b, c, 1-a-b-c)."""
@@ -105,9 +133,10 @@ def rmat_edges(scale: int, n_edges: int, a: float, b: float, c: float, seed: int
 
 
 def rmat_graph(scale: int, n_edges: int, a=0.57, b=0.19, c=0.19, seed=0, symmetric=True, self_loops=True,
-               num_nodes: int | None = None, device="cpu") -> Graph:
+               num_nodes: int | None = None, device="cpu", relabel: bool = False) -> Graph:
     """R-MAT graph.  With num_nodes < 2^scale, sampled pairs with an endpoint >= num_nodes are dropped
-    and sampling continues until n_edges pairs are kept (before symmetrisation / deduplication)."""
+    and sampling continues until n_edges pairs are kept (before symmetrisation / deduplication).
+    relabel=True renumbers the nodes with ``relabel_ids`` (same graph up to isomorphism)."""
     n = num_nodes if num_nodes is not None else (1 << scale)
     if n == (1 << scale):
         src, dst = rmat_edges(scale, n_edges, a, b, c, seed, device)
@@ -123,9 +152,11 @@ def rmat_graph(scale: int, n_edges: int, a=0.57, b=0.19, c=0.19, seed=0, symmetr
             take = min(int(s.numel()), n_edges - have)
             kept_s.append(s[:take]); kept_d.append(d[:take]); have += take
         src, dst = torch.cat(kept_s), torch.cat(kept_d)
+    if relabel:
+        src, dst = relabel_ids(src, n, seed), relabel_ids(dst, n, seed)
     keys = _finish(src, dst, n, symmetric, self_loops)
     meta = dict(kind="rmat", scale=scale, sampled_edges=n_edges, a=a, b=b, c=c, d=round(1 - a - b - c, 6),
-                seed=seed, symmetric=symmetric, self_loops=self_loops)
+                seed=seed, symmetric=symmetric, self_loops=self_loops, relabelled=relabel)
     return _csr_from_keys(keys, n, meta)
 
 
@@ -210,25 +241,29 @@ def config2_graph(device="cpu", seed=0, scale: float = 1.0) -> Graph:
 
 
 def config3_graph(device="cpu", seed=0, scale: float = 1.0) -> Graph:
-    """ogbn-products-shaped: 2,449,029 nodes, ~123.7 M stored edges, power law 2.3."""
+    """ogbn-products-shaped: 2,449,029 nodes, ~123.7 M stored edges, power law 2.3.  The degree ranks are
+    dealt round-robin to 64 contiguous id blocks (no preference for edges inside a block), so every
+    node-range shard has the same degree profile and endpoints are spread over all shards."""
     n = max(64, int(2_449_029 * scale))
-    return chung_lu_graph(n, int(123_700_000 * scale), 2.3, seed=seed, communities=1, p_intra=0.0, device=device)
+    return chung_lu_graph(n, int(123_700_000 * scale), 2.3, seed=seed, communities=64, p_intra=0.0, device=device)
 
 
 def config4_graph(device="cpu", seed=0, scale_shift: int = 0) -> Graph:
-    """enwiki-shaped skewed directed R-MAT (a=.6 b=.15 c=.15 d=.1): 4,206,785 nodes, ~101.3 M edges, not symmetrised.
-    scale_shift > 0 halves ids and edges that many times for tests."""
+    """enwiki-shaped skewed directed R-MAT (a=.6 b=.15 c=.15 d=.1): 4,206,785 nodes, ~101.3 M edges, not
+    symmetrised, node ids relabelled pseudo-randomly.  scale_shift > 0 halves ids and edges that many
+    times for tests."""
     n = 4_206_785 >> scale_shift
     return rmat_graph(23 - scale_shift, 101_300_000 >> scale_shift, 0.6, 0.15, 0.15, seed=seed,
-                      symmetric=False, self_loops=False, num_nodes=n, device=device)
+                      symmetric=False, self_loops=False, num_nodes=n, device=device, relabel=True)
 
 
 def rmat_shard(scale: int, n_pairs: int, num_nodes: int, lb: int, ub: int, a=0.57, b=0.19, c=0.19, seed=0,
-               device="cpu", batch: int = 1 << 25) -> Graph:
+               device="cpu", batch: int = 1 << 25, relabel: bool = False) -> Graph:
     """The rows [lb, ub) of the symmetrised R-MAT graph on ``num_nodes`` ids, built WITHOUT
     materialising the whole graph: every rank walks the same ``n_pairs`` sampled pairs in batches
     (counter-based randomness, so all ranks see the same pairs) and keeps, in both directions, only
-    the edges whose source row it owns.  Pairs with an endpoint >= num_nodes are dropped.  Returns a
+    the edges whose source row it owns.  Pairs with an endpoint >= num_nodes are dropped; relabel=True
+    renumbers the endpoints with ``relabel_ids`` before the ownership test, as rmat_graph does.  Returns a
     Graph whose ``row_ptr`` (int64, ub-lb+1 entries, starting at 0) indexes the shard's rows and
     whose ``col_idx`` holds global ids; self-loops are added for the shard's own rows."""
     rows = ub - lb
@@ -238,6 +273,8 @@ def rmat_shard(scale: int, n_pairs: int, num_nodes: int, lb: int, ub: int, a=0.5
         s, d = rmat_edges(scale, cnt, a, b, c, seed, device, first)
         ok = (s < num_nodes) & (d < num_nodes)
         s, d = s[ok], d[ok]
+        if relabel:
+            s, d = relabel_ids(s, num_nodes, seed), relabel_ids(d, num_nodes, seed)
         fwd = (s >= lb) & (s < ub)
         bwd = (d >= lb) & (d < ub)
         kept.append(torch.cat([(s[fwd] - lb) * num_nodes + d[fwd], (d[bwd] - lb) * num_nodes + s[bwd]]))
@@ -250,15 +287,16 @@ def rmat_shard(scale: int, n_pairs: int, num_nodes: int, lb: int, ub: int, a=0.5
     col = (keys - src * num_nodes).to(torch.int32)
     row_ptr = torch.zeros(rows + 1, dtype=torch.int64, device=keys.device)
     torch.cumsum(torch.bincount(src, minlength=rows), 0, out=row_ptr[1:])
-    meta = dict(kind="rmat_shard", scale=scale, sampled_pairs=n_pairs, lb=lb, ub=ub, seed=seed)
+    meta = dict(kind="rmat_shard", scale=scale, sampled_pairs=n_pairs, lb=lb, ub=ub, seed=seed, relabelled=relabel)
     return Graph(num_nodes, row_ptr, col, meta)
 
 
 def config5_shard(pe: int, num_pes: int, device="cpu", seed=0, scale_shift: int = 0) -> Graph:
-    """paper100M-shaped: 111 M nodes, ~3.2 B stored edges (1.6 B sampled pairs), symmetric R-MAT; only
-    PE ``pe``'s rows are built (see rmat_shard).  scale_shift halves ids and pairs that many times."""
+    """paper100M-shaped: 111 M nodes, ~3.2 B stored edges (1.6 B sampled pairs), symmetric R-MAT with node
+    ids relabelled pseudo-randomly; only PE ``pe``'s rows are built (see rmat_shard).  scale_shift halves
+    ids and pairs that many times."""
     n = 111_000_000 >> scale_shift
     npp = (n + num_pes - 1) // num_pes
     lb = min(n, pe * npp)
     ub = min(n, lb + npp)
-    return rmat_shard(27 - scale_shift, 1_600_000_000 >> scale_shift, n, lb, ub, seed=seed, device=device)
+    return rmat_shard(27 - scale_shift, 1_600_000_000 >> scale_shift, n, lb, ub, seed=seed, device=device, relabel=True)

@@ -21,8 +21,8 @@ import sys
 
 import torch
 
-from . import drivers, graphgen as gg
-from .symmem import SymmetricBuffer
+from . import _lib, drivers, graphgen as gg
+from .symmem import ReplicaBuffer, SymmetricBuffer
 
 PS = (1, 2, 4, 8, 16, 32)
 WPB = (1, 2, 4, 8, 16)
@@ -50,6 +50,11 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--csv", default=None)
+    ap.add_argument("--fetch", default="peer", choices=["peer", "replica"],
+                    help="peer: remote rows are read from the owners' memory inside the kernel (the reference's scheme); "
+                         "replica: every PE holds a copy of the whole matrix and the kernel reads local memory only")
+    ap.add_argument("--group-per-node", action="store_true",
+                    help="also time the 4-lanes-per-node kernel (width 16 only; it ignores the three knobs)")
     args = ap.parse_args(argv)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -69,8 +74,18 @@ def main(argv=None):
     shard = drivers.Shard(g.row_ptr.cpu().numpy(), g.col_idx.cpu().numpy(), rank, world, device=dev)
     edges, nodes = g.num_edges, g.num_nodes
     del g
-    sym = SymmetricBuffer(shard.node_per_pe * args.dim, None, rank, world)
-    sym.view(shard.rows, args.dim).copy_(gg.features(shard.rows, args.dim, 1, device=dev, first_row=shard.lb))
+    if args.fetch == "replica" and world > 1:
+        # every PE fills its whole copy (the features depend only on seed, row and column)
+        sym = ReplicaBuffer(shard.node_per_pe, args.dim, None, rank, world)
+        for p in range(world):
+            lo = min(nodes, p * shard.node_per_pe)
+            hi = min(nodes, lo + shard.node_per_pe)
+            if hi > lo:
+                sym.tensor[p * sym.slot_elems: p * sym.slot_elems + (hi - lo) * args.dim].view(hi - lo, args.dim).copy_(
+                    gg.features(hi - lo, args.dim, 1, device=dev, first_row=lo))
+    else:
+        sym = SymmetricBuffer(shard.node_per_pe * args.dim, None, rank, world)
+        sym.view(shard.rows, args.dim).copy_(gg.features(shard.rows, args.dim, 1, device=dev, first_row=shard.lb))
     out = torch.zeros(max(shard.rows, 1), args.dim, device=dev)[: shard.rows]
 
     def sync():
@@ -79,8 +94,8 @@ def main(argv=None):
             dist_.barrier()
             torch.cuda.synchronize()
 
-    def time_point(ps, wpb, dist):
-        k = drivers.Knobs(ps, wpb, dist)
+    def time_point(ps, wpb, dist, flags=0):
+        k = drivers.Knobs(ps, wpb, dist, flags)
         for _ in range(args.warmup):
             if shard.rows:
                 shard.aggregate(out, sym, args.dim, k)
@@ -103,9 +118,14 @@ def main(argv=None):
             for dist in DIST:
                 results[(ps, wpb, dist)] = time_point(ps, wpb, dist)
 
+    group_ms = time_point(32, 1, 1, _lib.AGG_GROUP_PER_NODE) if (args.group_per_node and args.dim == 16) else None
+
     if rank == 0:
         sink = open(args.csv, "w") if args.csv else sys.stdout
-        print(f"# {args.config}: {nodes} nodes, {edges} edges, width {args.dim}, {world} GPU(s); ms per aggregation, max over ranks", file=sink)
+        print(f"# {args.config}: {nodes} nodes, {edges} edges, width {args.dim}, {world} GPU(s), fetch={args.fetch}; "
+              f"ms per aggregation, max over ranks", file=sink)
+        if group_ms is not None:
+            print(f"# group-per-node kernel: {group_ms:.4f} ms", file=sink)
         print("ps,wpb,dist,ms", file=sink)
         for (ps, wpb, dist), ms in results.items():
             print(f"{ps},{wpb},{dist},{ms:.4f}", file=sink)
@@ -116,6 +136,8 @@ def main(argv=None):
         print(f"\nbest  ps={best[0]} wpb={best[1]} dist={best[2]}: {results[best]:.4f} ms "
               f"({edges / results[best] / 1e6:.1f} G edges/s)")
         print(f"worst ps={worst[0]} wpb={worst[1]} dist={worst[2]}: {results[worst]:.4f} ms")
+        if group_ms is not None:
+            print(f"group-per-node kernel: {group_ms:.4f} ms ({edges / group_ms / 1e6:.1f} G edges/s)")
         print("\ndist \\ ps (wpb=4)   " + "".join(f"{ps:>9d}" for ps in PS))
         for dist in DIST:
             print(f"{dist:>18d}   " + "".join(f"{results[(ps, 4, dist)]:9.4f}" for ps in PS))

@@ -105,8 +105,11 @@ class ReplicaBuffer:
         self.tensor = self.sym.tensor
         # reading: every slot of the LOCAL copy
         self.peer_ptrs = [self.sym.ptr + p * self.slot_elems * 4 for p in range(num_pes)]
-        # writing: this PE's slot in every PEER's copy
-        self.publish = [self.sym.peer_ptrs[q] + pe * self.slot_elems * 4 for q in range(num_pes) if q != pe] or None
+        # writing: this PE's slot in every PEER's copy, nearest higher PE first.  Every kernel walks the
+        # table in order for each tile it stores, so with this rotation the PEs aim at different
+        # receivers at any one time instead of all at PE 0, then all at PE 1, ...
+        self.publish = [self.sym.peer_ptrs[(pe + k) % num_pes] + pe * self.slot_elems * 4
+                        for k in range(1, num_pes)] or None
 
     def own(self, rows: int, dim: int) -> torch.Tensor:
         off = self.pe * self.slot_elems

@@ -232,3 +232,50 @@ def test_group_per_node_kernel(oracle, G):
     x8 = np.ascontiguousarray(x[:, :8])
     import gpu_util
     np.testing.assert_allclose(gpu_util.emulated_aggregate(rp, col, x8, G, knobs=knobs, flags=flag), oracle.sag_f64(x8, rp, col), rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("dim,knobs,flags", [(16, (16, 2, 2), 0), (16, (32, 1, 1), 4), (64, (16, 1, 2), 0), (7, (4, 4, 1), 0)])
+def test_row_list_calls_cover_the_shard(dim, knobs, flags):
+    """Aggregating a shard in three row-list calls gives the bits of one whole-shard call (SAG and GIN)."""
+    from mgg_osdi23_b200 import drivers
+    g = gg.chung_lu_graph(3000, 60_000, 2.2, seed=11)
+    rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
+    dev = torch.device("cuda")
+    G, pe = 2, 1
+    sh = drivers.Shard(rp, col, pe, G, device=dev)
+    npp = sh.node_per_pe
+    x = gg.features(G * npp, dim, seed=5, device=dev)
+    table = [x[p * npp:(p + 1) * npp] for p in range(G)]
+    kn = drivers.Knobs(*knobs, flags)
+    whole = torch.zeros(sh.rows, dim, device=dev)
+    sh.aggregate(whole, table, dim, kn)
+    parts = torch.full((sh.rows, dim), 7.0, device=dev)
+    blocks = sh.row_blocks(3)
+    assert blocks[0][0] == 0 and blocks[-1][1] == sh.rows and sum(b[2].numel() for b in blocks) == sh.rows
+    for r0, r1, rows in blocks:
+        assert int(rows.min()) >= r0 and int(rows.max()) < r1
+        sh.aggregate(parts, table, dim, kn, rows=rows)
+    assert torch.equal(whole, parts)
+    gin_whole = torch.zeros(sh.rows, dim, device=dev)
+    gin_parts = torch.zeros(sh.rows, dim, device=dev)
+    sh.aggregate_gin(gin_whole, table, dim, kn, 0.25)
+    for _, _, rows in blocks:
+        sh.aggregate_gin(gin_parts, table, dim, kn, 0.25, rows=rows)
+    assert torch.equal(gin_whole, gin_parts)
+    # an empty list is a no-op; a list longer than the shard is refused
+    sh.aggregate(parts, table, dim, kn, rows=torch.zeros(0, dtype=torch.int32, device=dev))
+    assert torch.equal(whole, parts)
+    with pytest.raises(mgg.MggbError):
+        sh.aggregate(parts, table, dim, kn, rows=torch.zeros(sh.rows + 1, dtype=torch.int32, device=dev))
+
+
+def test_publish_rows_copies_to_every_destination():
+    dev = torch.device("cuda")
+    for count in (4096 * 16, 1001):
+        src = gg.features(count, 1, seed=2, device=dev).reshape(-1)
+        dst = [torch.zeros(count + 8, device=dev) for _ in range(3)]
+        mgg.publish_rows(src, dst, elem_offset=4)
+        for d in dst:
+            assert torch.equal(d[4:4 + count], src) and float(d[:4].abs().sum()) == 0 and float(d[-4:].abs().sum()) == 0
+    with pytest.raises(mgg.MggbError):
+        mgg.publish_rows(src, [src])

@@ -78,3 +78,44 @@ def test_tensor_core_kernel_reports_clean_status_and_matches_cuda_core_kernel(or
         np.testing.assert_allclose(a.cpu().numpy(), want, rtol=RTOL, atol=ATOL, err_msg=str((n, k, m)))
         np.testing.assert_allclose(b.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
         np.testing.assert_allclose(a.cpu().numpy(), b.cpu().numpy(), rtol=RTOL, atol=2e-5)
+
+
+@pytest.mark.parametrize("n,k,m", [(1003, 16, 172), (777, 16, 41), (301, 64, 47), (65, 7, 5), (1, 3, 1), (8, 4, 256),
+                                   (4099, 128, 33)])
+def test_fused_dense_softmax_matches_oracle(oracle, n, k, m):
+    dev = torch.device("cuda")
+    x = (gg.features(n, k, seed=n).numpy() * 4).astype(np.float32)
+    w = gg.glorot_uniform(k, m, seed=k).numpy()
+    xd, wd = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
+    out = torch.empty(n, m, device=dev)
+    logits = torch.empty(n, m, device=dev)
+    mgg.dense_softmax_forward(out, xd, wd, logits)
+    want_logits = oracle.dense(x, w)
+    np.testing.assert_allclose(logits.cpu().numpy(), want_logits, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(out.cpu().numpy(), oracle.softmax(want_logits.astype(np.float32)), rtol=2e-5, atol=1e-7)
+    # without the logits the probabilities are the same bits
+    out2 = torch.empty(n, m, device=dev)
+    mgg.dense_softmax_forward(out2, xd, wd)
+    assert torch.equal(out, out2)
+    # and the reference's two calls agree with the single one through the parameter structs
+    dp = mgg.dense_param_new_hidden("d-2", xd, torch.zeros(n, m, device=dev), n, k, m)
+    dp.set_weight(wd)
+    dp.flags = 4                                                        # CUDA-core dense: the same fp32 FMA chain
+    probs = torch.zeros(n, m, device=dev)
+    smx = mgg.softmax_new_param("smx", dp.d_out, probs, n, m)
+    mgg.dense_hidden_new_forward(dp)
+    mgg.softmax_new_forward(smx)
+    np.testing.assert_allclose(out.cpu().numpy(), probs.cpu().numpy(), rtol=2e-5, atol=1e-7)
+
+
+def test_fused_dense_softmax_refuses_what_it_cannot_hold():
+    dev = torch.device("cuda")
+    assert not mgg.dense_softmax_fits(16, 300) and not mgg.dense_softmax_fits(602, 172)
+    with pytest.raises(mgg.MggbError):
+        mgg.dense_softmax_forward(torch.empty(4, 300, device=dev), torch.ones(4, 16, device=dev), torch.ones(16, 300, device=dev))
+    # the struct-level call falls back to the two kernels for such a shape
+    d_in = torch.ones(4, 16, device=dev)
+    dp = mgg.dense_param_new_hidden("d", d_in, torch.zeros(4, 300, device=dev), 4, 16, 300)
+    probs = torch.zeros(4, 300, device=dev)
+    mgg.dense_hidden_softmax_new_forward(dp, mgg.softmax_new_param("s", dp.d_out, probs, 4, 300))
+    np.testing.assert_allclose(probs.cpu().numpy(), 1.0 / 300, rtol=1e-6)

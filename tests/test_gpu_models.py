@@ -173,3 +173,77 @@ def test_forward_host_overlapped_upload(oracle):
         assert torch.equal(chunked, plain)
     _, want = _oracle_gcn2(oracle, rp, col, x.numpy(), w1.numpy(), w2.numpy(), "sym")
     np.testing.assert_allclose(plain.numpy(), want, rtol=RTOL, atol=ATOL)
+
+
+def _force_overlap(m):
+    """Cut every pushed aggregation into row blocks with the consumer on the second stream, whatever the size."""
+    m.overlap_blocks, m.overlap_min_rows, m.EPILOGUE_PUSH_MAX_BYTES = 3, 1, 0
+    return m
+
+
+def test_overlapped_pushes_give_the_same_forward_pass(oracle):
+    """Push mode with the aggregation cut into row blocks (block b pushed while block b+1 is gathered)
+    matches the oracle and, bit for bit, the single-launch schedule."""
+    dev = torch.device("cuda")
+    G = 3
+    # GCN-2
+    g = gg.chung_lu_graph(1500, 40_000, 2.1, seed=2, communities=4, p_intra=0.7)
+    rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
+    n, din, hid, dout = g.num_nodes, 602, 16, 41
+    x = gg.features(n, din, seed=3).numpy()
+    w1, w2 = gg.glorot_uniform(din, hid, 1), gg.glorot_uniform(hid, dout, 2)
+    npp = (n + G - 1) // G
+    results = []
+    for overlap in (False, True):
+        sa, sb = _published(G, npp, hid, dev, "replica")
+
+        def make(pe):
+            sh = drivers.Shard(rp, col, pe, G, device=dev)
+            m = drivers.GCN2Forward(sh, din, hid, dout, sa[pe], sb[pe], drivers.Knobs(16, 4, 2),
+                                    w1=w1.to(dev), w2=w2.to(dev), norm="sym")
+            return _force_overlap(m) if overlap else m
+
+        results.append(_run_cluster(make, G, n, x))
+    assert np.array_equal(results[0][0], results[1][0]) and np.array_equal(results[0][1], results[1][1])
+    want_logits, want_probs = _oracle_gcn2(oracle, rp, col, x, w1.numpy(), w2.numpy(), "sym")
+    np.testing.assert_allclose(results[1][0], want_logits, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(results[1][1], want_probs, rtol=RTOL, atol=ATOL)
+    # GIN-5
+    g = gg.chung_lu_graph(1200, 12_000, 2.3, seed=5)
+    rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
+    n, din, hid, dout = g.num_nodes, 100, 64, 47
+    x = gg.features(n, din, seed=4).numpy()
+    ws = [gg.glorot_uniform(din, hid, 10) * 0.1] + [gg.glorot_uniform(hid, hid, 11 + k) * 0.1 for k in range(4)] \
+        + [gg.glorot_uniform(hid, dout, 20) * 0.1]
+    npp = (n + G - 1) // G
+    results = []
+    for overlap in (False, True):
+        sa, sb = _published(G, npp, hid, dev, "replica")
+
+        def make(pe):
+            sh = drivers.Shard(rp, col, pe, G, device=dev)
+            m = drivers.GIN5Forward(sh, din, hid, dout, sa[pe], sb[pe], drivers.Knobs(8, 2, 2), eps=0.0,
+                                    weights=[w.to(dev) for w in ws])
+            return _force_overlap(m) if overlap else m
+
+        results.append(_run_cluster(make, G, n, x))
+    assert np.array_equal(results[0][0], results[1][0]) and np.array_equal(results[0][1], results[1][1])
+
+
+def test_single_aggregation_in_push_mode(oracle):
+    g = gg.config4_graph(scale_shift=9)
+    rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
+    n, dim, G = g.num_nodes, 16, 4
+    x = gg.features(n, dim, seed=8).numpy()
+    dev = torch.device("cuda")
+    npp = (n + G - 1) // G
+    reps = drivers.local_replicas(G, npp, dim, dev)
+    models = [drivers.SingleAggregation(drivers.Shard(rp, col, pe, G, device=dev), dim, reps[pe],
+                                        drivers.Knobs(32, 1, 1, mgg._lib.AGG_GROUP_PER_NODE)) for pe in range(G)]
+    assert len(models[0].stages) == 2
+    for m in models:
+        m.d_in.copy_(torch.from_numpy(x[m.shard.lb:m.shard.ub]).to(dev))
+    drivers.run_stages(models)
+    torch.cuda.synchronize()
+    got = np.concatenate([m.out.cpu().numpy() for m in models])
+    np.testing.assert_allclose(got, oracle.sag_f64(x, rp, col), rtol=RTOL, atol=ATOL)

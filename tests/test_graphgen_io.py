@@ -90,3 +90,36 @@ def test_shard_local_generation_matches_whole_graph():
     # the shard feeds the 64-bit-row-pointer split directly (local ids are rebased by the caller)
     sh = gg.config5_shard(1, 4, scale_shift=17)
     assert sh.num_nodes == 111_000_000 >> 17 and sh.row_ptr.dtype == torch.int64
+
+
+def test_relabelling_is_a_permutation_and_balances_shards():
+    for n in (1, 2, 7, 1000, 16433):
+        p = gg.relabel_ids(torch.arange(n), n, seed=3)
+        assert sorted(p.tolist()) == list(range(n))
+    # relabelled shards assemble into the relabelled whole graph
+    scale, pairs, n = 10, 6000, 900
+    whole = gg.rmat_graph(scale, pairs, seed=4, num_nodes=None)
+    wr = np.repeat(np.arange(whole.num_nodes), np.diff(whole.row_ptr.numpy()))
+    wc = whole.col_idx.numpy().astype(np.int64)
+    keep = (wr < n) & (wc < n)
+    rr = gg.relabel_ids(torch.from_numpy(wr[keep]), n, seed=4).numpy()
+    cc = gg.relabel_ids(torch.from_numpy(wc[keep]), n, seed=4).numpy()
+    want = np.unique(rr * n + cc)
+    parts = []
+    for pe in range(3):
+        lb, ub = pe * 300, (pe + 1) * 300
+        sh = gg.rmat_shard(scale, pairs, n, lb, ub, seed=4, batch=1000, relabel=True)
+        rows = np.repeat(np.arange(lb, ub), np.diff(sh.row_ptr.numpy()))
+        parts.append(rows.astype(np.int64) * n + sh.col_idx.numpy())
+    assert np.array_equal(np.sort(np.concatenate(parts)), want)
+    # the skewed configurations give node-range shards of similar size
+    g = gg.config4_graph(scale_shift=6)
+    deg = np.diff(g.row_ptr.numpy())
+    npp = (g.num_nodes + 7) // 8
+    per = np.array([deg[i * npp:(i + 1) * npp].sum() for i in range(8)])
+    assert per.max() < 1.25 * per.mean()
+    g = gg.config3_graph(scale=0.02)
+    deg = np.diff(g.row_ptr.numpy())
+    npp = (g.num_nodes + 7) // 8
+    per = np.array([deg[i * npp:(i + 1) * npp].sum() for i in range(8)])
+    assert per.max() < 1.1 * per.mean()
