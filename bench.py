@@ -47,6 +47,9 @@ def parse_args():
                     help="how peers see a layer's output: 'peer' = rows pulled from the owner inside the aggregation "
                          "kernel; 'replica' = rows pushed into every PE's copy by the producing kernel; 'auto' = replica "
                          "when there are peers and the copy fits")
+    ap.add_argument("--overlap-blocks", type=int, default=-1,
+                    help="row blocks per pushed aggregation (block b is pushed to the peers while block b+1 is gathered); "
+                         "1 = no overlap, default = the driver's choice")
     ap.add_argument("--keep-logits", action="store_true",
                     help="also store the last dense layer's output (the fused dense+softmax kernel writes only the probabilities by default)")
     ap.add_argument("--row-order", default="auto", choices=["auto", "degree", "natural"],
@@ -377,6 +380,8 @@ def run_ours(args, rank, world, local_rank):
     else:
         model = drivers.SingleAggregation(shard, hid, sym_a, knobs, norm=norm)
     model.keep_logits = args.keep_logits
+    if args.overlap_blocks >= 1:
+        model.overlap_blocks = args.overlap_blocks
     x_dev = gg.features(shard.rows, din, seed=1, device=dev, first_row=shard.lb)
     if model_kind == "agg" and norm == "sym":
         x_dev = x_dev * shard.inv_sqrt_degree()[:, None]
@@ -424,7 +429,8 @@ def run_ours(args, rank, world, local_rank):
     e1.record()
     sync_all()
     shard.event_sink = None
-    launches = api.kernel_launches[0] - launches0      # this rank's kernels in the timed region
+    # kernels of all ranks in the timed region (a collective: every rank calls it, here)
+    launches = int(sum_over_ranks(api.kernel_launches[0] - launches0))
     step_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     agg_ms_local = sum(a.elapsed_time(b) for a, b in agg_events) / max(1, len(agg_events))
     agg_ms = max_over_ranks(agg_ms_local)
@@ -485,10 +491,11 @@ def run_ours(args, rank, world, local_rank):
                          "aggregation_roofline_ms": t_roof * 1e3, "aggregation_roofline_frac": t_roof * 1e3 / agg_ms,
                          "nvlink_gbs_assumed": NVLINK_GBS},
             "fetch": fetch, "dense_kernel": "cuda-core" if args.dense == "simt" else "tcgen05 where the shape fits",
+            "overlap_blocks": model.overlap_blocks,
             "last_layer": "dense + softmax in one kernel" + (", logits stored too" if args.keep_logits else ", logits not stored"),
             "per_gpu_edges": [{"local": el, "remote": er, "rows": r} for el, er, r in allstats],
             "remote_fraction": sum(er for _, er, _ in allstats) / max(1, total_edges),
-            "gpu_launches": int(sum_over_ranks(launches)),
+            "gpu_launches": launches,
             "pass_breakdown_ms": {"spans": "stage" + (", barrier, stage" * ((spans - 1) // 2) if world > 1 else ", stage" * (spans - 1)),
                                   "ms": breakdown},
             "preproc_ms": preproc_ms, "clocks": clocks,

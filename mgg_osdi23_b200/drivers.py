@@ -200,10 +200,12 @@ class _Forward:
         # True: the last dense layer's output (the logits) is stored as well as the probabilities, as the
         # reference's separate dense and softmax calls do; False saves that write.
         self.keep_logits = True
-        # Row blocks per aggregation whose output is pushed to peers: block b's consumer (the dense update
-        # that pushes, or the push itself) runs on a second, high-priority stream while block b+1 is
-        # aggregated, so the NVLink transfer hides behind the gather.  1 = one launch, no second stream.
-        self.overlap_blocks = 4 if (shard.num_pes > 1 and getattr(sym_a, "publish", None)) else 1
+        # Row blocks per aggregation whose output is pushed to peers: with N > 1, block b's consumer (the
+        # dense update that pushes, or the push itself) runs on a second, high-priority stream while block
+        # b+1 is aggregated.  1 (the default) = one launch, no second stream: on 4 B200s with the
+        # products-shaped GIN the cut gave no gain (11.7 ms per pass against 11.4 ms), because the
+        # persistent dense kernel and the gather compete for the same SMs.
+        self.overlap_blocks = 1
         self.overlap_min_rows = 8192      # rows per block below which cutting the shard does not pay
         self._side = None
 

@@ -56,3 +56,28 @@ def test_config5_shard_local_path_small():
     d = _run("--config", "cfg5", "--scale", "0.00006", "--steps", "3", "--warmup", "3")
     assert d["config"]["workload"].startswith("cfg5") and d["config"]["nodes"] == 111_000_000 >> 15
     assert d["config"]["classes"] == 172 and d["value"] > 0 and "cpu_baseline" not in d
+
+
+def test_no_collective_is_called_by_rank_zero_alone():
+    """A collective inside an ``if rank == 0:`` block deadlocks every multi-GPU run (the other ranks
+    never join it).  Checked on the source: bench.py's collective helpers and torch.distributed calls
+    must not appear under a rank test."""
+    import ast
+    src = open(os.path.join(ROOT, "bench.py")).read()
+    collectives = {"sum_over_ranks", "max_over_ranks", "sync_all", "all_reduce", "all_gather", "barrier", "broadcast",
+                   "all_gather_object", "forward", "forward_host"}
+
+    def mentions_rank(test):
+        return any(isinstance(n, ast.Name) and n.id in ("rank", "local_rank") for n in ast.walk(test))
+
+    bad = []
+    for node in ast.walk(ast.parse(src)):
+        if isinstance(node, ast.If) and mentions_rank(node.test):
+            for sub in node.body + node.orelse:
+                for call in ast.walk(sub):
+                    if isinstance(call, ast.Call):
+                        f = call.func
+                        name = f.id if isinstance(f, ast.Name) else f.attr if isinstance(f, ast.Attribute) else ""
+                        if name in collectives:
+                            bad.append((name, call.lineno))
+    assert not bad, f"collective under a rank test: {bad}"
