@@ -320,6 +320,11 @@ def build_weights(cfg, device):
 
 def run_ours(args, rank, world, local_rank):
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # only a one-element all-reduce goes through NCCL
+    # torch.distributed.run gives every rank OMP_NUM_THREADS=1 unless the user chose a value; the host
+    # partitioner (split_CSR) is OpenMP code, so share the host cores among the ranks instead.  Must be
+    # set before the library is loaded.
+    if world > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
+        os.environ["OMP_NUM_THREADS"] = str(max(1, (os.cpu_count() or 1) // world))
     import numpy as np
     import torch
     import torch.distributed as dist
