@@ -286,6 +286,14 @@ int mggb_inv_sqrt_degree(float* scale, const int32_t* row_ptr_l, const int32_t* 
 int mggb_graph_file_info(const char* beg_file, const char* csr_file, int64_t* num_nodes, int64_t* num_edges);
 int mggb_graph_file_load(const char* beg_file, const char* csr_file, int64_t num_nodes, int64_t num_edges,
                          int64_t* row_ptr64, int32_t* col_idx);
+/* A shard's rows only: _rows_info returns the position of row lb's first neighbor and the number of
+ * neighbors of rows [lb, ub); _load_rows fills row_ptr64 (ub-lb+1 entries, rebased to start at 0) and
+ * col_idx (that many int32 ids) by reading just those parts of the two files.  Feeds
+ * mggb_split_csr_*_i64 with shard-local pointers.  The reference loads the whole graph on every rank
+ * (src/mgg_np_div_mem.cu:54-56). */
+int mggb_graph_file_rows_info(const char* beg_file, int64_t lb, int64_t ub, int64_t* first_edge, int64_t* num_edges);
+int mggb_graph_file_load_rows(const char* beg_file, const char* csr_file, int64_t lb, int64_t ub,
+                              int64_t* row_ptr64, int32_t* col_idx);
 int mggb_graph_file_write(const char* beg_file, const char* csr_file, const char* weight_file,
                           const int64_t* row_ptr64, const int32_t* col_idx, int64_t num_nodes);
 

@@ -77,6 +77,8 @@ SIGNATURES = {
     "mggb_inv_sqrt_degree": [_vp, _vp, _vp, _i64, _vp],
     "mggb_graph_file_info": [C.c_char_p, C.c_char_p, _pi64, _pi64],
     "mggb_graph_file_load": [C.c_char_p, C.c_char_p, _i64, _i64, _vp, _vp],
+    "mggb_graph_file_rows_info": [C.c_char_p, _i64, _i64, _pi64, _pi64],
+    "mggb_graph_file_load_rows": [C.c_char_p, C.c_char_p, _i64, _i64, _vp, _vp],
     "mggb_graph_file_write": [C.c_char_p, C.c_char_p, C.c_char_p, _vp, _vp, _i64],
 }
 

@@ -35,3 +35,15 @@ def load_graph(beg_file: str, csr_file: str):
     check(lib.mggb_graph_file_load(beg_file.encode(), csr_file.encode(), n.value, e.value,
                                    row_ptr.ctypes.data_as(C.c_void_p), col.ctypes.data_as(C.c_void_p)))
     return row_ptr, col
+
+
+def load_graph_rows(beg_file: str, csr_file: str, lb: int, ub: int):
+    """Rows [lb, ub) only: (row_ptr int64 [ub-lb+1] starting at 0, col_idx int32), read from just those
+    parts of the files.  What ``drivers.Shard(..., shard_local=True)`` takes."""
+    first, e = C.c_int64(), C.c_int64()
+    check(lib.mggb_graph_file_rows_info(beg_file.encode(), lb, ub, C.byref(first), C.byref(e)))
+    row_ptr = np.empty(ub - lb + 1, np.int64)
+    col = np.empty(e.value, np.int32)
+    check(lib.mggb_graph_file_load_rows(beg_file.encode(), csr_file.encode(), lb, ub,
+                                        row_ptr.ctypes.data_as(C.c_void_p), col.ctypes.data_as(C.c_void_p)))
+    return row_ptr, col

@@ -5,6 +5,7 @@ import numpy as np
 import pytest
 import torch
 
+import mgg_osdi23_b200 as mgg
 from mgg_osdi23_b200 import graphgen as gg, graphio
 
 
@@ -123,3 +124,35 @@ def test_relabelling_is_a_permutation_and_balances_shards():
     npp = (g.num_nodes + 7) // 8
     per = np.array([deg[i * npp:(i + 1) * npp].sum() for i in range(8)])
     assert per.max() < 1.1 * per.mean()
+
+
+def test_shard_rows_are_read_from_their_part_of_the_files(tmp_path):
+    """load_graph_rows returns what slicing the whole graph gives, and feeds the shard-local split."""
+    g = gg.rmat_graph(9, 5000, seed=8)
+    rp, col = g.row_ptr.numpy(), g.col_idx.numpy()
+    beg, csr, _ = graphio.write_graph(str(tmp_path / "g"), rp, col)
+    n = g.num_nodes
+    for lb, ub in ((0, n), (0, 100), (100, 371), (n - 7, n), (50, 50), (n, n)):
+        srp, scol = graphio.load_graph_rows(beg, csr, lb, ub)
+        assert srp.dtype == np.int64 and scol.dtype == np.int32 and srp[0] == 0
+        assert np.array_equal(srp, rp[lb:ub + 1] - rp[lb])
+        assert np.array_equal(scol, col[rp[lb]:rp[ub]])
+    # the shard's rows go straight into the split with shard-local pointers
+    G, pe = 3, 1
+    npp, lb, ub = mgg.shard_range(n, G, pe)
+    srp, scol = graphio.load_graph_rows(beg, csr, lb, ub)
+    whole = mgg.split_CSR(rp.astype(np.int32), col, lb, ub)
+    part = mgg.split_CSR(srp, scol, lb, ub, first_row=lb)
+    assert all(np.array_equal(a, b) for a, b in zip(whole, part))
+    # bad ranges and damaged files are refused with a message
+    for lb, ub in ((-1, 5), (5, 4), (0, n + 1)):
+        with pytest.raises(mgg.MggbError):
+            graphio.load_graph_rows(beg, csr, lb, ub)
+    short = str(tmp_path / "short_csr.bin")
+    with open(csr, "rb") as f, open(short, "wb") as o:
+        o.write(f.read()[: 8 * int(rp[200]) - 8])
+    graphio.load_graph_rows(beg, short, 0, 100)                    # rows before the cut still load
+    with pytest.raises(mgg.MggbError):
+        graphio.load_graph_rows(beg, short, 150, 220)
+    with pytest.raises(mgg.MggbError):
+        graphio.load_graph_rows(str(tmp_path / "missing_beg_pos.bin"), csr, 0, 1)
