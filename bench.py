@@ -47,6 +47,9 @@ def parse_args():
                     help="how peers see a layer's output: 'peer' = rows pulled from the owner inside the aggregation "
                          "kernel; 'replica' = rows pushed into every PE's copy by the producing kernel; 'auto' = replica "
                          "when there are peers and the copy fits")
+    ap.add_argument("--cpu-threads", type=int, default=0,
+                    help="host threads of the CPU arm (--impl reference and cpu_baseline); 0 = all the cores this process may use, "
+                         "1 = the reference's host aggregation exactly as written (one thread)")
     ap.add_argument("--overlap-blocks", type=int, default=-1,
                     help="row blocks per pushed aggregation (block b is pushed to the peers while block b+1 is gathered); "
                          "1 = no overlap, default = the driver's choice")
@@ -203,20 +206,27 @@ class ClockSampler:
 # CPU arm: the reference's host aggregation (or the port) + oracle dense/softmax
 # -------------------------------------------------------------------------------------------------
 
-def cpu_forward_factory(cfg_name, g_cpu, x_np, weights_np, norm):
-    """Returns (step_fn, description dict).  step_fn() runs one forward pass on the host."""
+def cpu_forward_factory(cfg_name, g_cpu, x_np, weights_np, norm, threads=0):
+    """Returns (step_fn, description dict).  step_fn() runs one forward pass on the host with
+    ``threads`` host threads (0 = every core this process may use)."""
     import numpy as np
     from oracle.oracle import Oracle, Ref
     orc = Oracle()
     use_ref = Ref.available()
     ref = Ref() if use_ref else None
+    if threads <= 0:
+        threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        if g_cpu.num_edges < (1 << 21):     # a few milliseconds of work: handing out ranges costs more than it saves
+            threads = 1
     rp = g_cpu.row_ptr.numpy().astype(np.int32)
     col = g_cpu.col_idx.numpy()
     model = CONFIGS[cfg_name][0]
     dinv = orc.inv_sqrt_degree(rp) if norm == "sym" else None
 
     def sag(t):
-        return ref.sag_ref(t, rp, col) if use_ref else orc.sag_f32(t, rp, col)
+        if use_ref:
+            return ref.sag_ref(t, rp, col, threads=threads)
+        return orc.sag_omp(t, rp, col)[0] if threads > 1 else orc.sag_f32(t, rp, col)
 
     def agg(t):
         if dinv is None:
@@ -235,10 +245,11 @@ def cpu_forward_factory(cfg_name, g_cpu, x_np, weights_np, norm):
             h = orc.dense(sag(h) + h, weights_np[k + 1])
         return orc.softmax(h)
 
-    desc = {"kind": "reference" if use_ref else "port", "cores": 1,
+    desc = {"kind": "reference" if use_ref else "port", "cores": threads,
             "sample": ("whole workload, full forward pass per step: aggregations by "
-                       + ("SAG_ref compiled from the reference's include/utils.cuh (single thread, as written)" if use_ref
-                          else "the plain-C port of SAG_ref (single thread)")
+                       + (f"SAG_ref compiled from the reference's include/utils.cuh, called on {threads} node ranges at once "
+                          "(the function itself is one loop over the nodes; row sums are the same bits)" if use_ref
+                          else f"the plain-C port of SAG_ref ({'OpenMP over rows' if threads > 1 else 'single thread'})")
                        + "; dense/softmax by the CPU oracle (OpenMP, not reference code)")}
     return step, desc
 
@@ -248,6 +259,9 @@ def run_reference(args, rank, world):
     import torch
     if rank != 0:
         return
+    # torch.distributed.run hands every rank OMP_NUM_THREADS=1; rank 0 runs this arm alone
+    if world > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     if args.config == "cfg5":
         print(json.dumps({"impl": "reference", "unavailable": "config 5 is never materialised as one graph (built shard by shard); the host reference needs the whole CSR"}), flush=True)
         return
@@ -258,7 +272,7 @@ def run_reference(args, rank, world):
     x = gg.features(g.num_nodes, din, seed=1).numpy()
     weights = build_weights(args.config, "cpu")
     norm = "sym" if model in ("gcn2",) or args.config == "cfg1" else "none"
-    step, d = cpu_forward_factory(args.config, g, x, [w.numpy() for w in weights], norm)
+    step, d = cpu_forward_factory(args.config, g, x, [w.numpy() for w in weights], norm, args.cpu_threads)
     naggs = {"agg": 1, "gcn2": 2, "gin5": 5}[model]
     # bound the run: the driver's K and W are honoured up to ~150 s of CPU work
     t0 = time.perf_counter(); step(); one = time.perf_counter() - t0
@@ -527,7 +541,7 @@ def cpu_baseline(args, rp_host, col_host, n, din, weights, norm, naggs, total_ed
     from mgg_osdi23_b200 import graphgen as gg
     g_cpu = gg.Graph(n, torch.from_numpy(rp_host), torch.from_numpy(col_host), meta)
     x = gg.features(n, din, seed=1).numpy()
-    step, d = cpu_forward_factory(args.config, g_cpu, x, [w.cpu().numpy() for w in weights], norm)
+    step, d = cpu_forward_factory(args.config, g_cpu, x, [w.cpu().numpy() for w in weights], norm, args.cpu_threads)
     t0 = time.perf_counter(); step(); one = time.perf_counter() - t0
     reps = max(1, min(5, int(15.0 / max(one, 1e-3))))
     t0 = time.perf_counter()

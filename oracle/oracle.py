@@ -183,13 +183,29 @@ class Ref:
                                        C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)] + [C.c_void_p] * 4
         L.mggref_build_part.argtypes = [_I32P, C.c_int, C.c_int, C.POINTER(C.c_longlong)] + [C.c_void_p] * 3
 
-    def sag_ref(self, x, row_ptr, col, update=None):
+    def sag_ref(self, x, row_ptr, col, update=None, threads: int = 1):
+        """``SAG_ref`` (``include/utils.cuh:71-86``).  The function is a single loop over the nodes;
+        with ``threads`` > 1 it is CALLED on that many disjoint node ranges at once (pointers offset
+        to the range; column offsets stay absolute), which gives the same bits row for row."""
         x, row_ptr, col = _f32(x), _i32(row_ptr), _i32(col)
         n, dim = len(row_ptr) - 1, x.shape[1]
         out = np.zeros((n, dim), np.float32) if update is None else _f32(update).copy()
         if len(col) == 0:
             col = np.zeros(1, np.int32)
-        self.lib.mggref_sag_ref(out, x, row_ptr, col, n, int(row_ptr[-1]), dim)
+        if threads <= 1 or n < 4 * threads:
+            self.lib.mggref_sag_ref(out, x, row_ptr, col, n, int(row_ptr[-1]), dim)
+            return out
+        from concurrent.futures import ThreadPoolExecutor
+        # node ranges of about equal edge counts, four per thread
+        cuts = np.searchsorted(row_ptr, np.linspace(0, int(row_ptr[-1]), 4 * threads + 1)[1:-1]).astype(np.int64)
+        bounds = np.unique(np.concatenate([[0], np.clip(cuts, 0, n), [n]]))
+
+        def run(k):
+            r0, r1 = int(bounds[k]), int(bounds[k + 1])
+            self.lib.mggref_sag_ref(out[r0:r1], x, row_ptr[r0:r1 + 1], col, r1 - r0, int(row_ptr[-1]), dim)
+
+        with ThreadPoolExecutor(max_workers=threads) as pool:      # ctypes releases the GIL during the call
+            list(pool.map(run, range(len(bounds) - 1)))
         return out
 
     def split_csr(self, row_ptr, col, lb, ub):

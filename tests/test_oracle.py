@@ -128,3 +128,21 @@ def test_oracle_matches_reference_host_code(oracle, ref, seed):
                 for ptr in a[:2]:
                     for u, v in zip(oracle.build_part(ptr, ub - lb, ps), ref.build_part(ptr, ub - lb, ps)):
                         assert np.array_equal(u, v)
+
+
+def test_reference_aggregation_on_several_node_ranges_at_once_gives_the_same_bits():
+    """The CPU arm of the benchmark calls SAG_ref on disjoint node ranges from several threads."""
+    from oracle.oracle import Ref
+    if not Ref.available():
+        pytest.skip("the reference's host code was not compiled here")
+    import numpy as np
+    from mgg_osdi23_b200 import graphgen as gg
+    ref = Ref()
+    g = gg.chung_lu_graph(3000, 120_000, 2.1, seed=9)
+    rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
+    x = gg.features(g.num_nodes, 7, seed=1).numpy()
+    one = ref.sag_ref(x, rp, col)
+    for threads in (2, 3, 8):
+        assert np.array_equal(one, ref.sag_ref(x, rp, col, threads=threads))
+    start = gg.features(g.num_nodes, 7, seed=2).numpy()
+    assert np.array_equal(ref.sag_ref(x, rp, col, update=start), ref.sag_ref(x, rp, col, update=start, threads=4))
