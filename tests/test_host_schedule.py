@@ -68,3 +68,13 @@ def test_models_choose_their_last_layer_and_launch_counts():
     reps = drivers.local_replicas(2, (3000 + 1) // 2, 16, device="cpu")
     two = drivers.SingleAggregation(drivers.Shard(rp, col, 0, 2, device="cpu"), 16, reps[0], drivers.Knobs(16, 4, 2))
     assert len(two.stages) == 2 and two.kernels_per_forward == 3   # push, aggregation, hub rows
+
+
+def test_row_of_flat_index_trick_of_the_dense_epilogue_is_exact():
+    """dense_tc's staged epilogue finds the row of flat element i of a 32-row block of width M as
+    int((float(i) + 0.5f) * (1.0f / M)).  Brute force in float32 over every width the kernel takes."""
+    for m in range(1, 257):
+        inv = np.float32(1.0) / np.float32(m)
+        i = np.arange(32 * m, dtype=np.int64)
+        r = ((i.astype(np.float32) + np.float32(0.5)) * inv).astype(np.int32)
+        assert np.array_equal(r, i // m), m
