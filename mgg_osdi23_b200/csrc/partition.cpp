@@ -166,16 +166,30 @@ int mggb_build_part_fill(const int32_t* indptr, int32_t num_nodes, int32_t part_
 int mggb_degree_order(const int32_t* row_ptr_l, const int32_t* row_ptr_r, int32_t num_rows, int32_t* order) {
     MGGB_REQUIRE(row_ptr_l && order, "degree_order: NULL argument");
     MGGB_REQUIRE(num_rows >= 0, "degree_order: need num_rows >= 0");
-    std::vector<int64_t> key((size_t)num_rows);
-#pragma omp parallel for schedule(static)
+    if (num_rows == 0) return MGGB_OK;
+    // Counting sort on the degree (stable, so ties stay in row order): degrees are small integers
+    // with many repeats, and a comparison sort of 10^7 rows takes seconds.
+    std::vector<int32_t> deg((size_t)num_rows);
+    int64_t max_deg = 0;
+#pragma omp parallel for schedule(static) reduction(max : max_deg)
     for (int32_t i = 0; i < num_rows; i++) {
-        int64_t deg = (int64_t)row_ptr_l[i + 1] - row_ptr_l[i];
-        if (row_ptr_r) deg += (int64_t)row_ptr_r[i + 1] - row_ptr_r[i];
-        key[i] = deg;
-        order[i] = i;
+        int64_t d = (int64_t)row_ptr_l[i + 1] - row_ptr_l[i];
+        if (row_ptr_r) d += (int64_t)row_ptr_r[i + 1] - row_ptr_r[i];
+        if (d < 0) d = 0;
+        if (d > INT32_MAX) d = INT32_MAX;
+        deg[i] = (int32_t)d;
+        if (d > max_deg) max_deg = d;
     }
-    // longest rows first, ties in row order
-    std::stable_sort(order, order + num_rows, [&](int32_t a, int32_t b) { return key[a] > key[b]; });
+    if (max_deg > (int64_t)64 * num_rows + (1 << 20)) {
+        // a histogram that large would cost more than sorting: compare instead
+        for (int32_t i = 0; i < num_rows; i++) order[i] = i;
+        std::stable_sort(order, order + num_rows, [&](int32_t a, int32_t b) { return deg[a] > deg[b]; });
+        return MGGB_OK;
+    }
+    std::vector<int64_t> start((size_t)max_deg + 2, 0);
+    for (int32_t i = 0; i < num_rows; i++) start[(size_t)(max_deg - deg[i]) + 1]++;   // bucket 0 = longest rows
+    for (int64_t b = 0; b <= max_deg; b++) start[b + 1] += start[b];
+    for (int32_t i = 0; i < num_rows; i++) order[start[(size_t)(max_deg - deg[i])]++] = i;
     return MGGB_OK;
 }
 

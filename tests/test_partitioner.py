@@ -97,6 +97,14 @@ def test_degree_order():
     assert mgg.degree_order(lp, rp).tolist() == [2, 1, 0, 3, 4]      # totals 2 5 7 2 0; ties keep row order
     assert mgg.degree_order(lp).tolist() == [2, 0, 3, 1, 4]
     assert mgg.degree_order(np.zeros(1, np.int32)).size == 0
+    # against a stable sort, on a skewed degree sequence, and on one whose largest degree dwarfs the row count
+    rng = np.random.default_rng(3)
+    deg = np.minimum(rng.zipf(1.7, size=20_000), 50_000)
+    lp = np.zeros(deg.size + 1, np.int32); lp[1:] = np.cumsum(deg // 2)
+    rp = np.zeros(deg.size + 1, np.int32); rp[1:] = np.cumsum(deg - deg // 2)
+    assert np.array_equal(mgg.degree_order(lp, rp), np.argsort(-deg, kind="stable"))
+    sparse = np.array([0, 5, 200_000_005, 200_000_006, 200_000_011], np.int32)
+    assert mgg.degree_order(sparse).tolist() == [1, 0, 3, 2]
 
 
 def test_split_from_shard_local_rows(oracle):
