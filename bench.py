@@ -247,7 +247,7 @@ def cpu_forward_factory(cfg_name, g_cpu, x_np, weights_np, norm, threads=0):
 
     desc = {"kind": "reference" if use_ref else "port", "cores": threads,
             "sample": ("whole workload, full forward pass per step: aggregations by "
-                       + (f"SAG_ref compiled from the reference's include/utils.cuh, called on {threads} node ranges at once "
+                       + (f"SAG_ref compiled from the reference's include/utils.cuh, called from {threads} threads on disjoint node ranges "
                           "(the function itself is one loop over the nodes; row sums are the same bits)" if use_ref
                           else f"the plain-C port of SAG_ref ({'OpenMP over rows' if threads > 1 else 'single thread'})")
                        + "; dense/softmax by the CPU oracle (OpenMP, not reference code)")}
