@@ -24,7 +24,10 @@ How peers see a layer's output is chosen by what is passed as ``sym_a`` / ``sym_
   aggregation kernel PULLS every remote neighbor's row from the owner's memory (the reference's scheme);
 * a :class:`symmem.ReplicaBuffer` (or :class:`LocalReplica`): the producing kernel's epilogue PUSHES
   each output row into every peer's copy of the matrix, and the aggregation then reads local memory
-  only.  One pushed row per node and peer instead of one pulled row per remote edge.
+  only.  One pushed row per node and peer instead of one pulled row per remote edge.  A dense layer
+  pushes from its epilogue (contiguous runs of rows); an aggregation does so only for small outputs
+  and otherwise writes locally and pushes the finished rows with ``api.publish_rows``; a pass can be cut
+  into row blocks whose pushes overlap the next block's gather (``overlap_blocks``).
 """
 from __future__ import annotations
 
