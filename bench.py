@@ -25,11 +25,24 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# DRAM bytes (read + write) of one aggregation launch from the ncu capture summarised in
-# profiles/cfg2_gcn2_1gpu_aggregation_and_dense.txt; only that case has been captured.
-NCU_TRAFFIC_BYTES = {("cfg2", 1, 1.0): 494.4e6}
 NVLINK_GBS = 900.0          # per direction per GPU (nominal); 770 GB/s measured peer copy on this pool
 FALLBACK_HBM_GBS = 6650.0
+RTOL, ATOL = 1e-5, 1e-4     # fp32 embeddings / probabilities against the fp64-accumulating oracle
+TRAFFIC_TABLE = os.path.join(ROOT, "profiles", "ncu_dram_traffic.md")
+
+
+def ncu_traffic(config: str, gpus: int, scale: float, kernel: str):
+    """DRAM bytes (read + write) of one launch of ``kernel`` as an ncu capture measured them, from the
+    table of captures kept under profiles/ (rows: | config | gpus | scale | kernel | read | write | summary |).
+    None when that case was never captured."""
+    try:
+        for ln in open(TRAFFIC_TABLE):
+            f = [c.strip() for c in ln.strip().strip("|").split("|")]
+            if len(f) >= 6 and f[0] == config and f[1] == str(gpus) and abs(float(f[2]) - scale) < 1e-12 and f[3] == kernel:
+                return float(f[4]) + float(f[5])
+    except (OSError, ValueError):
+        pass
+    return None
 
 
 def parse_args():
@@ -43,10 +56,15 @@ def parse_args():
     ap.add_argument("--ps", type=int, default=None)
     ap.add_argument("--wpb", type=int, default=None)
     ap.add_argument("--dist", type=int, default=None)
-    ap.add_argument("--fetch", default="auto", choices=["auto", "peer", "replica"],
-                    help="how peers see a layer's output: 'peer' = rows pulled from the owner inside the aggregation "
-                         "kernel; 'replica' = rows pushed into every PE's copy by the producing kernel; 'auto' = replica "
-                         "when there are peers and the copy fits")
+    ap.add_argument("--fetch", default="auto", choices=["auto", "both", "peer", "replica"],
+                    help="how peers see a layer's output: 'peer' (pull) = rows fetched from the owner inside the aggregation "
+                         "kernel; 'replica' (push) = rows stored into every PE's copy by the producing kernel; 'both' / 'auto' = "
+                         "time the two one after the other (the line's headline is the faster, both are under \"modes\")")
+    ap.add_argument("--repeats", type=int, default=5, help="the K timed steps are run this many times; the median is reported")
+    ap.add_argument("--barrier", default="flag", choices=["flag", "nccl"],
+                    help="what separates the stages of a pass at N > 1: 'flag' = epoch flags in peer memory (one small kernel), "
+                         "'nccl' = a one-element all-reduce")
+    ap.add_argument("--no-check", action="store_true", help="skip the comparison of the outputs with the oracle")
     ap.add_argument("--cpu-threads", type=int, default=0,
                     help="host threads of the CPU arm (--impl reference and cpu_baseline); 0 = all the cores this process may use, "
                          "1 = the reference's host aggregation exactly as written (one thread)")
@@ -114,6 +132,7 @@ class ClockSampler:
         self.cuda_index, self.proc, self.lines = cuda_index, None, []
         self.sm, self.mask, self.max_mhz, self.handle, self.nvml = [], 0, None, None, None
         self._stop = threading.Event()
+        self._active = threading.Event()     # samples are kept only while a timed loop runs (resume / pause)
         self.thread = None
 
     def _nvml_handle(self):
@@ -134,6 +153,9 @@ class ClockSampler:
     def _poll(self):
         n = self.nvml
         while not self._stop.is_set():
+            if not self._active.is_set():
+                time.sleep(0.001)
+                continue
             try:
                 self.sm.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
                 try:
@@ -142,7 +164,7 @@ class ClockSampler:
                     self.mask |= int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
             except Exception:
                 break
-            time.sleep(0.004)
+            time.sleep(0.001)
 
     def start(self):
         try:
@@ -161,6 +183,12 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def resume(self):
+        self._active.set()
+
+    def pause(self):
+        self._active.clear()
+
     def _pump(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
@@ -174,7 +202,7 @@ class ClockSampler:
             sm = sorted(self.sm)
             reasons = sorted(name for bit, name in self.REASONS.items() if self.mask & bit)
             return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": self.max_mhz, "reasons": reasons,
-                    "samples": len(sm), "source": "nvml, 4 ms period, during the timed region"}
+                    "samples": len(sm), "source": "nvml, about 1 ms period, during the timed loops only"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["neither NVML nor nvidia-smi available"]}
         time.sleep(0.25)
@@ -203,8 +231,14 @@ class ClockSampler:
 
 
 # -------------------------------------------------------------------------------------------------
-# CPU arm: the reference's host aggregation (or the port) + oracle dense/softmax
+# CPU side: the reference's host aggregation (or the port) + oracle dense/softmax; the expected output
 # -------------------------------------------------------------------------------------------------
+
+def host_threads(requested: int = 0) -> int:
+    if requested > 0:
+        return requested
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
 
 def cpu_forward_factory(cfg_name, g_cpu, x_np, weights_np, norm, threads=0):
     """Returns (step_fn, description dict).  step_fn() runs one forward pass on the host with
@@ -214,10 +248,11 @@ def cpu_forward_factory(cfg_name, g_cpu, x_np, weights_np, norm, threads=0):
     orc = Oracle()
     use_ref = Ref.available()
     ref = Ref() if use_ref else None
-    if threads <= 0:
-        threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-        if g_cpu.num_edges < (1 << 21):     # a few milliseconds of work: handing out ranges costs more than it saves
-            threads = 1
+    threads = host_threads(threads)
+    omp_threads = orc.set_threads(threads)      # dense / softmax / the port's OpenMP loop: set at run time, then read back
+    sag_threads = threads
+    if g_cpu.num_edges < (1 << 21):             # a few milliseconds of work: handing out ranges costs more than it saves
+        sag_threads = 1
     rp = g_cpu.row_ptr.numpy().astype(np.int32)
     col = g_cpu.col_idx.numpy()
     model = CONFIGS[cfg_name][0]
@@ -225,8 +260,8 @@ def cpu_forward_factory(cfg_name, g_cpu, x_np, weights_np, norm, threads=0):
 
     def sag(t):
         if use_ref:
-            return ref.sag_ref(t, rp, col, threads=threads)
-        return orc.sag_omp(t, rp, col)[0] if threads > 1 else orc.sag_f32(t, rp, col)
+            return ref.sag_ref(t, rp, col, threads=sag_threads)
+        return orc.sag_omp(t, rp, col)[0] if sag_threads > 1 else orc.sag_f32(t, rp, col)
 
     def agg(t):
         if dinv is None:
@@ -245,13 +280,37 @@ def cpu_forward_factory(cfg_name, g_cpu, x_np, weights_np, norm, threads=0):
             h = orc.dense(sag(h) + h, weights_np[k + 1])
         return orc.softmax(h)
 
-    desc = {"kind": "reference" if use_ref else "port", "cores": threads,
+    desc = {"kind": "reference" if use_ref else "port", "cores": sag_threads, "omp_threads_dense_softmax": omp_threads,
             "sample": ("whole workload, full forward pass per step: aggregations by "
-                       + (f"SAG_ref compiled from the reference's include/utils.cuh, called from {threads} threads on disjoint node ranges "
+                       + (f"SAG_ref compiled from the reference's include/utils.cuh, called from {sag_threads} threads on disjoint node ranges "
                           "(the function itself is one loop over the nodes; row sums are the same bits)" if use_ref
-                          else f"the plain-C port of SAG_ref ({'OpenMP over rows' if threads > 1 else 'single thread'})")
-                       + "; dense/softmax by the CPU oracle (OpenMP, not reference code)")}
+                          else f"the plain-C port of SAG_ref ({'OpenMP over rows' if sag_threads > 1 else 'single thread'})")
+                       + f"; dense/softmax by the CPU oracle (OpenMP, {omp_threads} threads in effect, not reference code)")}
     return step, desc
+
+
+def oracle_expected(cfg_name, rp, col, x_np, weights_np, norm):
+    """The whole forward pass with double-precision accumulation in every sum (aggregation, dense,
+    softmax), rounded to fp32 between stages: what the GPU output is compared with.  Returns
+    (output, the last aggregation's result or None): the second lets the check see the embeddings
+    themselves, not only probabilities that a saturated softmax has pushed to 0 or 1."""
+    from oracle.oracle import Oracle
+    orc = Oracle()
+    orc.set_threads(host_threads())
+    model = CONFIGS[cfg_name][0]
+    dinv = orc.inv_sqrt_degree(rp) if norm == "sym" else None
+    sag = lambda t: orc.sag_f64_omp(t, rp, col)
+    agg = (lambda t: sag(t)) if dinv is None else (lambda t: orc.row_scale(sag(orc.row_scale(t, dinv)), dinv))
+    if model == "agg":
+        return agg(x_np), None
+    if model == "gcn2":
+        z = agg(agg(orc.dense(x_np, weights_np[0])))
+        return orc.softmax(orc.dense(z, weights_np[1])), z
+    h = orc.dense(x_np, weights_np[0])
+    for k in range(5):
+        z = sag(h) + h
+        h = orc.dense(z, weights_np[k + 1])
+    return orc.softmax(h), z
 
 
 def run_reference(args, rank, world):
@@ -259,9 +318,6 @@ def run_reference(args, rank, world):
     import torch
     if rank != 0:
         return
-    # torch.distributed.run hands every rank OMP_NUM_THREADS=1; rank 0 runs this arm alone
-    if world > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
-        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     if args.config == "cfg5":
         print(json.dumps({"impl": "reference", "unavailable": "config 5 is never materialised as one graph (built shard by shard); the host reference needs the whole CSR"}), flush=True)
         return
@@ -291,7 +347,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": metric_name(model), "value": value, "unit": "edges/s", "n_gpus": args.gpus,
         "steps": steps, "warmup": warm + 1, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args, g, model, din, hid, dout, None, 1),
+        "config": workload_config(args, g.num_nodes, g.num_edges, g.meta, din, hid, dout),
         "cpu_baseline": d,
         "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -304,13 +360,12 @@ def metric_name(model):
             "agg": "aggregation_edges_per_s"}[model]
 
 
-def workload_config(args, g, model, din, hid, dout, knobs, world):
-    c = {"workload": f"{args.config}: {CONFIGS[args.config][5]}", "nodes": g.num_nodes, "edges": g.num_edges,
-         "in_dim": din, "aggregated_width": hid, "classes": dout, "graph": g.meta,
-         "partition": f"node-range x{world}", "l2_policy": "inputs larger than L2 (features 561 MB, neighbor ids 458 MB per aggregation)"
+def workload_config(args, nodes, edges, meta, din, hid, dout):
+    """The workload, described identically by both arms (tuning knobs and the partition live elsewhere in the line)."""
+    c = {"workload": f"{args.config}: {CONFIGS[args.config][5]}", "nodes": nodes, "edges": edges,
+         "in_dim": din, "aggregated_width": hid, "classes": dout, "graph": meta, "partition": "node-range",
+         "l2_policy": "inputs larger than L2 (features 561 MB, neighbor ids 458 MB per aggregation)"
          if args.config == "cfg2" else "inputs larger than L2 where the graph is (see edges x 4 B of neighbor ids per aggregation)"}
-    if knobs is not None:
-        c.update({"ps": knobs.partSize, "wpb": knobs.warpPerBlock, "dist": knobs.interleaved_dist, "group_per_node": bool(knobs.flags & 4)})
     if args.scale != 1.0:
         c["scale"] = args.scale
     return c
@@ -332,13 +387,80 @@ def build_weights(cfg, device):
 # GPU arm
 # -------------------------------------------------------------------------------------------------
 
+def compare(got, want, rtol=RTOL, atol=ATOL):
+    """(max abs error, max relative error over |want| >= atol, worst |err| / (atol + rtol |want|)) of two device tensors."""
+    import torch
+    if got.numel() == 0:
+        return 0.0, 0.0, 0.0
+    g, w = got.double(), want.double()
+    err = (g - w).abs()
+    err = torch.where(torch.isfinite(err), err, torch.full_like(err, float("inf")))
+    big = w.abs() >= atol
+    rel = float((err[big] / w.abs()[big]).max()) if bool(big.any()) else 0.0
+    return float(err.max()), rel, float((err / (atol + rtol * w.abs())).max())
+
+
+def sample_rows(shard, count=48):
+    """Shard rows for the sampled checks: the longest and shortest neighbor lists, the median, the rows
+    with the most remote neighbors, and a seeded random handful."""
+    import numpy as np
+    import torch
+    rows = shard.rows
+    if rows == 0:
+        return []
+    deg_l = (shard.rp_l[1:] - shard.rp_l[:-1]).cpu().numpy()
+    deg_r = (shard.rp_r[1:] - shard.rp_r[:-1]).cpu().numpy()
+    order = np.argsort(deg_l + deg_r, kind="stable")
+    pick = set(order[-6:].tolist()) | set(order[:3].tolist()) | {int(order[rows // 2])} | set(np.argsort(deg_r, kind="stable")[-6:].tolist())
+    rng = np.random.default_rng(1234 + shard.pe)
+    pick |= set(rng.integers(0, rows, max(0, count - len(pick))).tolist())
+    return sorted(pick)
+
+
+def sampled_stage_check_gcn2(model, shard, x_dev, world, dist):
+    """Config 5 is never materialised on one host, so its check is stage by stage on sampled rows: each
+    stage's stored output is compared with a double-precision evaluation (torch, on the device, gathers
+    from an all-gathered copy of the published matrix) of that stage applied to the previous stage's
+    STORED output.  Returns (rows checked, max abs, max rel, worst tolerance ratio)."""
+    import torch
+    hid = model.hidden
+    npp, rows = shard.node_per_pe, shard.rows
+
+    def gathered(sym):
+        own = torch.zeros(npp, hid, dtype=torch.float32, device=shard.device)
+        own[:rows] = model._sym_view(sym, hid)
+        if world == 1:
+            return own
+        full = torch.empty(world * npp, hid, dtype=torch.float32, device=shard.device)
+        dist.all_gather_into_tensor(full, own)
+        return full
+
+    h1_all, z1_all = gathered(model.sym_a), gathered(model.sym_b)
+    picks = sample_rows(shard)
+    worst = [0.0, 0.0, 0.0]
+    if picks:
+        idx = torch.tensor(picks, dtype=torch.int64, device=shard.device)
+        dinv = shard.inv_sqrt_degree().double()
+        w1, w2 = model.dp1.d_W.double(), model.dp2.d_W.double()
+        lb = shard.lb
+
+        def nbr(i):
+            a, b = int(shard.rp_l[i]), int(shard.rp_l[i + 1])
+            c, d = int(shard.rp_r[i]), int(shard.rp_r[i + 1])
+            return torch.cat([shard.ci_l[a:b], shard.ci_r[c:d]]).long()
+
+        want_h1 = (x_dev[idx].double() @ w1) * dinv[idx, None]
+        want_z1 = torch.stack([h1_all[nbr(i)].double().sum(0) for i in picks]) * (dinv[idx] ** 2)[:, None]
+        want_z2 = torch.stack([z1_all[nbr(i)].double().sum(0) for i in picks]) * dinv[idx, None]
+        want_out = torch.softmax(model.d_agg[idx].double() @ w2, dim=1)
+        for got, want in ((h1_all[lb + idx], want_h1), (z1_all[lb + idx], want_z1), (model.d_agg[idx], want_z2), (model.out[idx], want_out)):
+            r = compare(got, want)
+            worst = [max(a, b) for a, b in zip(worst, r)]
+    return len(picks), worst
+
+
 def run_ours(args, rank, world, local_rank):
-    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # only a one-element all-reduce goes through NCCL
-    # torch.distributed.run gives every rank OMP_NUM_THREADS=1 unless the user chose a value; the host
-    # partitioner (split_CSR) is OpenMP code, so share the host cores among the ranks instead.  Must be
-    # set before the library is loaded.
-    if world > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
-        os.environ["OMP_NUM_THREADS"] = str(max(1, (os.cpu_count() or 1) // world))
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # NCCL only carries set-up traffic and (with --barrier nccl) one-element all-reduces
     import numpy as np
     import torch
     import torch.distributed as dist
@@ -356,6 +478,22 @@ def run_ours(args, rank, world, local_rank):
     group_kernel = (args.group_per_node or args.config in ("cfg4", "cfg5")) and not args.no_group_per_node
     knobs = drivers.Knobs(args.ps or dknobs[0], args.wpb or dknobs[1], args.dist or dknobs[2], flags=4 if group_kernel else 0)
 
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def reduce_over_ranks(v: float, op) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=op)
+        return float(t.item())
+
+    max_over_ranks = lambda v: reduce_over_ranks(v, dist.ReduceOp.MAX)
+    sum_over_ranks = lambda v: reduce_over_ranks(v, dist.ReduceOp.SUM)
+
     shard_local = args.config == "cfg5"          # too large to replicate: every rank builds only its rows
     if shard_local:
         shift = 0
@@ -372,118 +510,47 @@ def run_ours(args, rank, world, local_rank):
     preproc_ms = (time.perf_counter() - t0) * 1e3
     g_meta, g_edges = g.meta, g.num_edges
     if shard_local and world > 1:                 # stored edges of the whole graph = sum over the shards
-        t = torch.tensor([g_edges], dtype=torch.int64, device=dev)
-        dist.all_reduce(t)
-        g_edges = int(t.item())
+        g_edges = int(sum_over_ranks(float(g_edges)))
     del g
     torch.cuda.empty_cache()
 
     npp = shard.node_per_pe
-    fetch = args.fetch
-    if fetch == "auto":
-        fetch = "replica" if world > 1 and world * npp * hid * 4 < (8 << 30) else "peer"
-    if fetch == "replica":
-        sym_a = ReplicaBuffer(npp, hid, group, rank, world)
-        sym_b = ReplicaBuffer(npp, hid, group, rank, world)
-    else:
-        sym_a = SymmetricBuffer(npp * hid, group, rank, world)
-        sym_b = SymmetricBuffer(npp * hid, group, rank, world)
     weights = build_weights(args.config, dev)
     norm = "sym" if model_kind == "gcn2" or args.config == "cfg1" else "none"
-    if model_kind == "gcn2":
-        model = drivers.GCN2Forward(shard, din, hid, dout, sym_a, sym_b, knobs, w1=weights[0], w2=weights[1], norm=norm,
-                                    dense_flags=4 if args.dense == "simt" else 0)
-    elif model_kind == "gin5":
-        model = drivers.GIN5Forward(shard, din, hid, dout, sym_a, sym_b, knobs, eps=0.0, weights=weights,
-                                    dense_flags=4 if args.dense == "simt" else 0)
-    else:
-        model = drivers.SingleAggregation(shard, hid, sym_a, knobs, norm=norm)
-    model.keep_logits = args.keep_logits
-    if args.overlap_blocks >= 1:
-        model.overlap_blocks = args.overlap_blocks
     x_dev = gg.features(shard.rows, din, seed=1, device=dev, first_row=shard.lb)
     if model_kind == "agg" and norm == "sym":
         x_dev = x_dev * shard.inv_sqrt_degree()[:, None]
     x_host = torch.empty(x_dev.shape, dtype=torch.float32, pin_memory=True)
     x_host.copy_(x_dev)
-    model.d_in.copy_(x_dev)
-    del x_dev
-    barrier = drivers.nccl_stream_barrier(group) if world > 1 else None
-
-    def sync_all():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    def max_over_ranks(v: float) -> float:
-        if world == 1:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    def sum_over_ranks(v: float) -> float:
-        if world == 1:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
-
-    # ---- device-resident timing ---------------------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
-        model.forward(barrier)
-    sync_all()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    agg_events = []
-    shard.event_sink = agg_events
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    launches0 = api.kernel_launches[0]
-    e0.record()
-    for _ in range(args.steps):
-        model.forward(barrier)
-    e1.record()
-    sync_all()
-    shard.event_sink = None
-    # kernels of all ranks in the timed region (a collective: every rank calls it, here)
-    launches = int(sum_over_ranks(api.kernel_launches[0] - launches0))
-    step_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
-    agg_ms_local = sum(a.elapsed_time(b) for a, b in agg_events) / max(1, len(agg_events))
-    agg_ms = max_over_ranks(agg_ms_local)
-    nsite = model.aggregations_per_forward
-    agg_ms_by_site = [max_over_ranks(sum(a.elapsed_time(b) for a, b in agg_events[s::nsite]) / max(1, len(agg_events[s::nsite])))
-                      for s in range(nsite)]
-    clocks = sampler.stop() if rank == 0 else None
-
-    # ---- where the time of a pass goes (a few extra passes, outside the timed region) ---------------
-    marks = []
-    for _ in range(5):
-        model.forward(barrier, marks)
-    sync_all()
-    spans = len(marks[0]) - 1
-    breakdown = [max_over_ranks(sum(m[i].elapsed_time(m[i + 1]) for m in marks) / len(marks)) for i in range(spans)]
-
-    # ---- end to end through the host-buffer entry point ---------------------------------------
-    e2e = None
-    if not args.no_e2e:
-        for _ in range(2):
-            model.forward_host(x_host, barrier)
-        sync_all()
-        e_steps = max(3, min(args.steps, 10))
-        e0.record()
-        for _ in range(e_steps):
-            model.forward_host(x_host, barrier)
-        e1.record()
-        sync_all()
-        e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e_steps)
-    naggs = model.aggregations_per_forward
+    naggs = {"agg": 1, "gcn2": 2, "gin5": 5}[model_kind]
     total_edges = g_edges
-    value = naggs * total_edges / (step_ms * 1e-3)
 
-    # per-rank edge split, gathered for the roofline
+    # ---- what the outputs are compared with (outside every timed region) ------------------------------
+    expected, expected_agg, check_kind = None, None, None
+    # five chained layers of unnormalised sums: the fp32 rounding of every layer is carried through the rest
+    rtol = 1e-4 if model_kind == "gin5" else RTOL
+    if not args.no_check and not shard_local:
+        check_kind = ("whole output of every rank (probabilities, and the last aggregation's embeddings) vs the CPU oracle's "
+                      "forward pass (double-precision accumulation)")
+        out_w = dout if model_kind != "agg" else hid
+        expected = torch.empty(n, out_w, dtype=torch.float32, device=dev)
+        expected_agg = torch.empty(n, hid, dtype=torch.float32, device=dev) if model_kind != "agg" else None
+        if rank == 0:
+            x_all = gg.features(n, din, seed=1, device=dev).cpu().numpy()
+            want, want_agg = oracle_expected(args.config, rp_host.astype(np.int32), col_host, x_all, [w.cpu().numpy() for w in weights], norm)
+            expected.copy_(torch.from_numpy(want))
+            if expected_agg is not None:
+                expected_agg.copy_(torch.from_numpy(want_agg))
+            del x_all, want, want_agg
+        if world > 1:
+            dist.broadcast(expected, 0)
+            if expected_agg is not None:
+                dist.broadcast(expected_agg, 0)
+    elif not args.no_check:
+        check_kind = ("stage by stage on sampled rows of every rank (longest, shortest, most-remote, random): each stage's stored output "
+                      "vs a double-precision evaluation, on the device with torch, of that stage on the previous stage's stored output")
+
+    # ---- per-rank edge split, gathered for the roofline ------------------------------------------------
     stats = torch.tensor([shard.e_local, shard.e_remote, shard.rows], dtype=torch.int64, device=dev)
     if world > 1:
         allstats = [torch.zeros_like(stats) for _ in range(world)]
@@ -492,47 +559,229 @@ def run_ours(args, rank, world, local_rank):
         allstats = [stats]
     allstats = [s.tolist() for s in allstats]
 
+    fetch = "both" if args.fetch == "auto" else args.fetch
+    mode_names = ["single"] if world == 1 else {"both": ["pull", "push"], "peer": ["pull"], "replica": ["push"]}[fetch]
+    agg_events = []
+    results = {}
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
+    for mode in mode_names:
+        nbuf = 3 if model_kind == "gin5" else (2 if model_kind == "gcn2" else 1)
+        if mode == "push":
+            syms = [ReplicaBuffer(npp, hid, group, rank, world) for _ in range(nbuf)]
+        else:
+            syms = [SymmetricBuffer(npp * hid, group, rank, world) for _ in range(nbuf)]
+        if model_kind == "gcn2":
+            model = drivers.GCN2Forward(shard, din, hid, dout, syms[0], syms[1], knobs, w1=weights[0], w2=weights[1], norm=norm,
+                                        dense_flags=4 if args.dense == "simt" else 0)
+        elif model_kind == "gin5":
+            model = drivers.GIN5Forward(shard, din, hid, dout, syms[0], syms[1], knobs, eps=0.0, weights=weights,
+                                        dense_flags=4 if args.dense == "simt" else 0, sym_c=syms[2])
+        else:
+            model = drivers.SingleAggregation(shard, hid, syms[0], knobs, norm=norm)
+        model.keep_logits = args.keep_logits
+        if args.overlap_blocks >= 1:
+            model.overlap_blocks = args.overlap_blocks
+        model.d_in.copy_(x_dev)
+        barrier, barrier_obj = None, None
+        if world > 1:
+            if args.barrier == "flag":
+                barrier_obj = drivers.FlagBarrier(group, rank, world)
+                barrier = barrier_obj
+            else:
+                barrier = drivers.nccl_stream_barrier(group)
+
+        # device-resident timing: W warm-up passes, then `repeats` loops of exactly K passes each
+        for _ in range(max(args.warmup, 3)):
+            model.forward(barrier)
+        sync_all()
+        del agg_events[:]
+        shard.event_sink = agg_events
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        loop_ms, launches = [], 0
+        for rep in range(max(1, args.repeats)):
+            sync_all()
+            launches0 = api.kernel_launches[0]
+            sampler.resume()
+            e0.record()
+            for _ in range(args.steps):
+                model.forward(barrier)
+            e1.record()
+            sync_all()
+            sampler.pause()
+            launches = api.kernel_launches[0] - launches0
+            loop_ms.append(max_over_ranks(e0.elapsed_time(e1) / args.steps))
+        shard.event_sink = None
+        step_ms = sorted(loop_ms)[len(loop_ms) // 2]
+        launches = int(sum_over_ranks(launches))       # kernels of all ranks in one timed loop of K passes
+        nsite = model.aggregations_per_forward
+        agg_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in agg_events) / max(1, len(agg_events)))
+        agg_ms_by_site = [max_over_ranks(sum(a.elapsed_time(b) for a, b in agg_events[s::nsite]) / max(1, len(agg_events[s::nsite])))
+                          for s in range(nsite)]
+        barrier_status = int(max_over_ranks(float(barrier_obj.status()))) if barrier_obj is not None else 0
+
+        # where the time of a pass goes (a few extra passes, outside the timed region)
+        marks = []
+        for _ in range(5):
+            model.forward(barrier, marks)
+        sync_all()
+        spans = len(marks[0]) - 1
+        breakdown = [max_over_ranks(sum(m[i].elapsed_time(m[i + 1]) for m in marks) / len(marks)) for i in range(spans)]
+
+        # the outputs of the last pass against the oracle
+        check = None
+        if not args.no_check:
+            if expected is not None:
+                r = compare(model.out, expected[shard.lb:shard.ub], rtol)
+                if expected_agg is not None:     # the last aggregation's output (the final dense layer's input)
+                    r = [max(a, b) for a, b in zip(r, compare(model.d_agg, expected_agg[shard.lb:shard.ub], rtol))]
+                nrows = shard.rows
+            else:
+                nrows, r = sampled_stage_check_gcn2(model, shard, x_dev, world, dist)
+            r = [max_over_ranks(v) for v in r]
+            check = {"kind": check_kind, "rows": int(sum_over_ranks(float(nrows))), "max_abs": r[0], "max_rel": r[1],
+                     "tol": f"|got - want| <= {ATOL:g} + {rtol:g} |want|", "worst_over_tol": r[2], "pass": bool(r[2] <= 1.0)}
+
+        # end to end through the host-buffer entry point
+        e2e = None
+        if not args.no_e2e:
+            for _ in range(2):
+                model.forward_host(x_host, barrier)
+            sync_all()
+            e_steps = max(3, min(args.steps, 10))
+            e0.record()
+            for _ in range(e_steps):
+                model.forward_host(x_host, barrier)
+            e1.record()
+            sync_all()
+            e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e_steps)
+            hmarks = []
+            for _ in range(3):
+                model.forward_host(x_host, barrier, marks=hmarks)
+            sync_all()
+            e2e_parts = [max_over_ranks(sum(m[i].elapsed_time(m[i + 1]) for m in hmarks) / len(hmarks)) for i in range(2)]
+            e2e = {"ms": e2e_ms, "upload_and_forward_ms": e2e_parts[0], "download_ms": e2e_parts[1]}
+            if check is not None and expected is not None:      # forward_host must have reproduced the same output
+                r2 = [max_over_ranks(v) for v in compare(model.out, expected[shard.lb:shard.ub], rtol)]
+                check["e2e_worst_over_tol"] = r2[2]
+                check["pass"] = bool(check["pass"] and r2[2] <= 1.0)
+
+        results[mode] = {"step_ms": step_ms, "loop_ms": loop_ms, "launches": launches, "agg_ms": agg_ms, "agg_ms_by_site": agg_ms_by_site,
+                         "breakdown": breakdown, "spans": spans, "check": check, "e2e": e2e, "overlap_blocks": model.overlap_blocks,
+                         "barrier_status": barrier_status, "leading_barrier": bool(model.leading_barrier)}
+        sync_all()
+        del model
+        if barrier_obj is not None:
+            barrier_obj.close()
+        for s_ in syms:
+            s_.close()
+        torch.cuda.empty_cache()
+
+    clocks = sampler.stop() if rank == 0 else None
+    failed = any(r["check"] is not None and not r["check"]["pass"] for r in results.values())
+    failed = failed or any(r["barrier_status"] != 0 for r in results.values())
+
     if rank == 0:
         hbm, hbm_src = measured_peaks()
+        props = torch.cuda.get_device_properties(dev)
+        sms, l2_bytes = props.multi_processor_count, int(props.L2_cache_size)
+        sm_hz = (clocks.get("sm_max_mhz") or 1965.0) * 1e6 if clocks else 1965.0e6
         D = hid
-        t_roof = max(max(4.0 * D * el / (hbm * 1e9), 4.0 * D * er / (NVLINK_GBS * 1e9)) for el, er, _ in allstats)
-        alg_bytes = max(4.0 * D * (el + er) for el, er, _ in allstats)       # per launch, busiest GPU
-        achieved = alg_bytes / (agg_ms * 1e-3) / 1e9
+        best = min(results, key=lambda m: results[m]["step_ms"])
+
+        def roofline_of(mode):
+            r = results[mode]
+            # busiest GPU by gathered bytes
+            el, er, rows_g = max(allstats, key=lambda s: s[0] + s[1])
+            alg_bytes = 4.0 * D * (el + er)
+            pulled = mode == "pull"
+            # rows that must come out of this GPU's HBM at least once: its own shard when remote rows are pulled, else the whole matrix
+            table_bytes = 4.0 * D * (rows_g if pulled else n)
+            dram_min = 4.0 * (el + er) + 2 * 8.0 * (rows_g + 1) + table_bytes + 4.0 * D * rows_g
+            t_local = 4.0 * D * (el if pulled else el + er) / (hbm * 1e9)
+            t_remote = 4.0 * D * er / (NVLINK_GBS * 1e9) if pulled else 0.0
+            t = r["agg_ms"] * 1e-3
+            achieved = alg_bytes / t / 1e9
+            if pulled and t_remote > t_local:
+                kind, peak = "nvlink: remote rows fetched inside the kernel, one row per remote edge", NVLINK_GBS
+                achieved = 4.0 * D * er / t / 1e9
+                note = "achieved = remote gathered bytes / kernel time; peak = 900 GB/s per direction (nominal)"
+            elif table_bytes < 0.75 * l2_bytes:
+                wave = min(4.0 * D, 128.0)
+                kind, peak = "l1tex: the gathered matrix stays in L2, every gathered row costs one L1 data-pipe wavefront", sms * sm_hz * wave / 1e9
+                note = (f"peak = {sms} SMs x {sm_hz / 1e6:.0f} MHz x {wave:.0f} B per wavefront (one 128-byte line per cycle per SM); "
+                        f"matrix {table_bytes / 1e6:.1f} MB against {l2_bytes / 1e6:.0f} MB of L2")
+            else:
+                kind, peak = "hbm-gather: the gathered matrix exceeds L2", hbm
+                note = "achieved = algorithmic bytes (one full row per stored edge) / kernel time; peak = measured copy bandwidth"
+            t_roof = max(max(4.0 * D * (a if pulled else a + b) / (hbm * 1e9), (4.0 * D * b / (NVLINK_GBS * 1e9)) if pulled else 0.0)
+                         for a, b, _ in allstats)
+            kernel = "sag_group_per_node_kernel" if group_kernel and D == 16 else "sag_np_div_kernel"
+            return {"bound": "hbm" if kind.startswith("hbm") else kind.split(":")[0], "bound_kind": kind, "achieved": achieved, "peak": peak,
+                    "unit": "GB/s", "frac": achieved / peak, "note": note, "peak_source": f"HBM figure: of {hbm_src}",
+                    "traffic": ncu_traffic(args.config, world, args.scale, kernel), "kernel": kernel,
+                    "algorithmic_bytes_per_launch": alg_bytes, "frac_algorithmic": alg_bytes / t / 1e9 / hbm,
+                    "dram_bytes_min": dram_min, "frac_dram": dram_min / t / 1e9 / hbm,
+                    "kernel_ms": r["agg_ms"], "kernel_ms_by_call_site": r["agg_ms_by_site"],
+                    "aggregation_roofline_ms": t_roof * 1e3, "aggregation_roofline_frac": t_roof * 1e3 / r["agg_ms"],
+                    "nvlink_gbs_assumed": NVLINK_GBS}
+
+        def mode_summary(mode):
+            r = results[mode]
+            rf = roofline_of(mode)
+            out = {"ms_per_step": r["step_ms"], "ms_per_step_each_loop": r["loop_ms"], "value": naggs * total_edges / (r["step_ms"] * 1e-3),
+                   "kernel_ms": r["agg_ms"], "bound": rf["bound"], "frac": rf["frac"], "aggregation_roofline_frac": rf["aggregation_roofline_frac"],
+                   "check": r["check"], "barrier_status": r["barrier_status"], "starts_with_barrier": r["leading_barrier"],
+                   "pass_breakdown_ms": r["breakdown"]}
+            if r["e2e"]:
+                out["e2e_ms"] = r["e2e"]["ms"]
+            return out
+
+        r = results[best]
+        step_ms = r["step_ms"]
+        spans = r["spans"]
         line = {
-            "metric": metric_name(model_kind), "value": value, "unit": "edges/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(args, type("G", (), {"num_nodes": n, "num_edges": total_edges, "meta": g_meta})(),
-                                      model_kind, din, hid, dout, knobs, world),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                         "traffic": NCU_TRAFFIC_BYTES.get((args.config, world, args.scale)), "peak_source": f"of {hbm_src}", "kernel": "sag_np_div_kernel",
-                         "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": agg_ms, "kernel_ms_by_call_site": agg_ms_by_site,
-                         "aggregation_roofline_ms": t_roof * 1e3, "aggregation_roofline_frac": t_roof * 1e3 / agg_ms,
-                         "nvlink_gbs_assumed": NVLINK_GBS},
-            "fetch": fetch, "dense_kernel": "cuda-core" if args.dense == "simt" else "tcgen05 where the shape fits",
-            "overlap_blocks": model.overlap_blocks,
+            "metric": metric_name(model_kind), "value": naggs * total_edges / (step_ms * 1e-3), "unit": "edges/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "repeats": max(1, args.repeats), "ms_per_step": step_ms,
+            "timing": "median over `repeats` timed loops of exactly `steps` passes each; CUDA events, max over ranks",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, n, total_edges, g_meta, din, hid, dout),
+            "knobs": {"ps": knobs.partSize, "wpb": knobs.warpPerBlock, "dist": knobs.interleaved_dist, "group_per_node": bool(knobs.flags & 4),
+                      "partition": f"node-range x{world}"},
+            "roofline": roofline_of(best),
+            "check": r["check"],
+            "fetch": {"single": "single GPU, no peers", "pull": "peer (rows pulled inside the aggregation kernel)",
+                      "push": "replica (rows pushed by the producing kernel)"}[best],
+            "modes": {m: mode_summary(m) for m in results} if world > 1 else None,
+            "barrier": (args.barrier if world > 1 else None),
+            "dense_kernel": "cuda-core" if args.dense == "simt" else "tcgen05 where the shape fits",
+            "overlap_blocks": r["overlap_blocks"],
             "last_layer": "dense + softmax in one kernel" + (", logits stored too" if args.keep_logits else ", logits not stored"),
-            "per_gpu_edges": [{"local": el, "remote": er, "rows": r} for el, er, r in allstats],
+            "per_gpu_edges": [{"local": el, "remote": er, "rows": rr} for el, er, rr in allstats],
             "remote_fraction": sum(er for _, er, _ in allstats) / max(1, total_edges),
-            "gpu_launches": launches,
+            "gpu_launches": r["launches"],
             "pass_breakdown_ms": {"spans": "stage" + (", barrier, stage" * ((spans - 1) // 2) if world > 1 else ", stage" * (spans - 1)),
-                                  "ms": breakdown},
+                                  "ms": r["breakdown"]},
             "preproc_ms": preproc_ms, "clocks": clocks,
         }
-        if not args.no_e2e:
+        if r["e2e"]:
             h2d = int(n * din * 4)
             d2h = int(n * (dout if model_kind != "agg" else hid) * 4)
-            line["e2e"] = {"value": naggs * total_edges / (e2e_ms * 1e-3), "unit": "edges/s", "ms_per_step": e2e_ms,
+            line["e2e"] = {"value": naggs * total_edges / (r["e2e"]["ms"] * 1e-3), "unit": "edges/s", "ms_per_step": r["e2e"]["ms"],
                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                           "upload_and_forward_ms": r["e2e"]["upload_and_forward_ms"], "download_ms": r["e2e"]["download_ms"],
                            "note": "pinned host features -> device, forward, probabilities -> pinned host; graph structure resident"}
         if world == 1 and not args.no_cpu_baseline and not shard_local:
             line["cpu_baseline"] = cpu_baseline(args, rp_host, col_host, n, din, weights, norm, naggs, total_edges, g_meta)
         print(json.dumps(line), flush=True)
 
     sync_all()
-    sym_a.close(); sym_b.close()
     if world > 1:
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit("bench.py: an output check or a barrier wait failed (see the \"check\" / \"barrier_status\" keys of the line above)")
 
 
 def cpu_baseline(args, rp_host, col_host, n, din, weights, norm, naggs, total_edges, meta):
@@ -555,11 +804,21 @@ def cpu_baseline(args, rp_host, col_host, n, din, weights, norm, naggs, total_ed
     return d
 
 
+def fix_openmp_environment(args, rank, world):
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to every rank unless the user chose a value.  The
+    OpenMP runtime reads the variable once, when it is loaded, so this runs before anything imports it:
+    the reference arm (rank 0 works alone) gets every core, the GPU arm's host partitioner a fair share."""
+    if world > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
+        cores = host_threads()
+        os.environ["OMP_NUM_THREADS"] = str(cores if args.impl == "reference" else max(1, cores // world))
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    fix_openmp_environment(args, rank, world)
     if args.impl == "reference":
         run_reference(args, rank, world)
         return

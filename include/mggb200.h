@@ -7,7 +7,10 @@
  *   - every function returns an int status (MGGB_OK == 0); nothing exits or throws.  The reference
  *     instead prints and calls exit(-1) on a CUDA error (include/neighbor_utils.cuh:836-840) and
  *     validates nothing; mggb_last_error() returns the message of the calling thread's last failure;
- *   - the caller owns every buffer; the library keeps no pointer after a call returns;
+ *   - the caller owns every buffer it passes and the library keeps no pointer to one after a call
+ *     returns.  The library's own device memory is small and listed where it arises: the hub work
+ *     list of the aggregation (1 MiB per device and stream, allocated on first use and kept until the
+ *     process exits; mggb_sag_np_div_static allocates nothing) and the barrier's status word;
  *   - device work is enqueued on the given stream (a cudaStream_t passed as void*, NULL = default
  *     stream) of the CURRENT device and is NOT synchronised (the reference synchronises the device
  *     after every launch, include/neighbor_utils.cuh:835);
@@ -115,6 +118,21 @@ int mggb_sym_import(const unsigned char handle[64], void** peer_ptr); /* maps a 
 int mggb_sym_close(void* peer_ptr);                          /* unmaps an imported buffer */
 int mggb_enable_peer_access(int device, int peer_device);    /* MGGB_ERR_PEER if impossible */
 
+/* ---- barrier between PEs ---------------------------------------------------------------------------
+ * The reference's layers are not separated by anything (src/mgg_np_div_mem.cu:213-226); a pass that
+ * publishes in one stage and gathers in the next needs every PE to have finished the first.  Each
+ * PE owns MGGB_MAX_PES int32 epoch slots in a zero-filled symmetric buffer (mggb_sym_alloc, exported
+ * to / imported by its peers); peer_slots[p] is PE p's slot array as addressable from this device.
+ * The call enqueues one small kernel that stores `epoch` into slot [pe] of every PE's array and then
+ * waits until slot [p] of its own array holds `epoch` or a later value for every p.  Call it with
+ * epoch = 1, 2, 3, ... in the same order on every PE; each PE on its own GPU (kernels that wait on
+ * one another must not share a device).  The wait gives up after timeout_ns (at most 10 s) of wall
+ * clock: the kernel then returns, the stream carries on, and mggb_flag_barrier_status reports
+ * 1 + the first PE that never arrived (0 = no wait has expired since the last reset; the call
+ * synchronises the device).  Nothing here can hang a GPU. */
+int mggb_flag_barrier(int* const* peer_slots, int num_pes, int pe, int epoch, int64_t timeout_ns, void* stream);
+int mggb_flag_barrier_status(int* status, int reset);
+
 /* ---- neighbor aggregation ----------------------------------------------------------------------
  * Replaces mgg_SAG_np_div (launcher include/neighbor_utils.cuh:787-841, kernel :1351-1460).
  *   output      [ub-lb, dim] on this device (may itself be a symmetric buffer)
@@ -204,6 +222,13 @@ int mggb_publish_rows(const float* in, int64_t count, float* const* publish_out,
  * in row order).  row_ptr_r may be NULL.  No counterpart in the reference. */
 int mggb_degree_order(const int32_t* row_ptr_l, const int32_t* row_ptr_r, int32_t num_rows, int32_t* order);
 
+/* Neighbor count above which the aggregation entry points hand a row to the wide-block kernel at
+ * these knobs, dim and flags (MGGB_AGG_*); -1 when no row ever is.  A caller that knows its shard's
+ * largest neighbor count can pass MGGB_AGG_NO_HUB_SPLIT when nothing exceeds the threshold and save
+ * the second kernel's launch.  No counterpart in the reference. */
+int mggb_hub_threshold(int part_size, int warp_per_block, int interleaved_dist, int dim, int flags,
+                       int64_t* threshold);
+
 /* mggb_sag_np_div for callers that must not trigger a device allocation.  It has no counterpart in
  * the reference.
  *
@@ -222,7 +247,9 @@ int mggb_degree_order(const int32_t* row_ptr_l, const int32_t* row_ptr_r, int32_
  *                8192 times that many edges (134 M at the default knobs) can never overflow it.
  *                Larger shards are refused with MGGB_ERR_UNSUPPORTED and a message naming the limit.
  *   warp_per_block must be <= 8 (wider blocks do not use a hub list at all).
- *   Every other argument is as for mggb_sag_np_div; MGGB_AGG_NO_HUB_SPLIT is ignored.
+ *   Every other argument is as for mggb_sag_np_div; MGGB_AGG_NO_HUB_SPLIT and MGGB_AGG_GROUP_PER_NODE
+ *   are ignored (the latter's hub threshold of 1024 neighbors would shrink the edge bound sixteenfold).
+ *   Rows wider than 3200 floats keep every node on its own block, exactly as in mggb_sag_np_div.
  *
  * The first call on each device looks up the array's device address (one cudaGetSymbolAddress, done
  * with that device current, result cached); make that first call outside any stream capture.
@@ -242,8 +269,12 @@ int mggb_sag_np_div_static(float* output, const float* const* peer_input, int nu
  * parameter structs of include/layer_new.cuh:272-393: row-major out[n, dim2] = x[n, dim1] * w[dim1, dim2],
  * alpha = 1, beta = 0, no bias.  The reference's call passes d_out as the B operand and never reads
  * d_in; this function computes the intended product from x.  row_scale (NULL or [n]) multiplies
- * output row i; publish_out / num_publish as for mggb_sag_np_div.  Precision: fp32-equivalent by default (3-pass split on the tensor cores, or the
- * CUDA-core kernel); MGGB_DENSE_TF32 selects one TF32 pass. */
+ * output row i; publish_out / num_publish as for mggb_sag_np_div.  out and every publish_out[k] may
+ * have any 4-byte alignment (16-byte aligned buffers get 128-bit stores).  Precision: fp32-equivalent
+ * by default (each operand split into two TF32 terms on the tensor cores and the partial products
+ * accumulated in fp32, or the fp32 CUDA-core kernel: about 1e-6 relative to an fp64 product);
+ * MGGB_DENSE_TF32 selects a single TF32 pass (operands truncated to 10 mantissa bits: about 1e-3
+ * relative, as cublasSgemm gives under CUBLAS_TF32_TENSOR_OP_MATH). */
 int mggb_dense_forward(float* out, const float* x, const float* w,
                        int64_t n, int dim1, int dim2,
                        const float* row_scale, int flags,

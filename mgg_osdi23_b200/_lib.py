@@ -53,6 +53,8 @@ SIGNATURES = {
     "mggb_sym_import": [C.c_char_p, C.POINTER(_vp)],
     "mggb_sym_close": [_vp],
     "mggb_enable_peer_access": [_int, _int],
+    "mggb_flag_barrier": [C.POINTER(_vp), _int, _int, _int, _i64, _vp],
+    "mggb_flag_barrier_status": [C.POINTER(_int), _int],
     "mggb_sag_np_div": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
                         _int, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp],
     "mggb_sag_np_div_static": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _i64, _int, _i32, _int,
@@ -69,6 +71,7 @@ SIGNATURES = {
                              _int, _int, _int, _f, _int, _vp, _i64, _vp],
     "mggb_publish_rows": [_vp, _i64, C.POINTER(_vp), _int, _vp],
     "mggb_degree_order": [_vp, _vp, _i32, _vp],
+    "mggb_hub_threshold": [_int, _int, _int, _int, _int, _pi64],
     "mggb_dense_forward": [_vp, _vp, _vp, _i64, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp],
     "mggb_dense_device_status": [C.POINTER(_int), _int],
     "mggb_softmax_forward": [_vp, _vp, _i64, _int, _vp],

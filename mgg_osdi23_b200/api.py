@@ -32,7 +32,7 @@ __all__ = [
     "shard_range", "split_CSR", "build_part", "mgg_SAG_np_div", "mgg_GIN_np_div",
     "dense_param_new_beg", "dense_param_new_hidden", "softmax_new_param",
     "dense_beg_new_forward", "dense_hidden_new_forward", "softmax_new_forward", "dense_hidden_softmax_new_forward",
-    "dense_forward", "softmax_forward", "dense_softmax_forward", "dense_softmax_fits", "publish_rows", "row_scale", "inv_sqrt_degree", "degree_order",
+    "dense_forward", "softmax_forward", "dense_softmax_forward", "dense_softmax_fits", "publish_rows", "row_scale", "inv_sqrt_degree", "degree_order", "hub_threshold",
 ]
 
 
@@ -146,6 +146,14 @@ def build_part(name: str, indptr, num_nodes: int, partSize: int, exact_sentinel:
     check(lib.mggb_build_part_fill(_np_ptr(indptr), num_nodes, partSize, int(exact_sentinel),
                                    _np_ptr(part_ptr), _np_ptr(part2node), _np_ptr(node2part)))
     return [part_ptr, part2node, node2part]
+
+
+def hub_threshold(np_size: int, warpPerBlock: int, interleaved_dist: int, dim: int, flags: int = 0) -> int:
+    """Neighbor count above which the aggregations hand a row to their wide-block kernel at these knobs
+    (-1: never).  A shard whose longest list stays below it can pass ``_lib.AGG_NO_HUB_SPLIT``."""
+    t = C.c_int64()
+    check(lib.mggb_hub_threshold(np_size, warpPerBlock, interleaved_dist, dim, flags, C.byref(t)))
+    return t.value
 
 
 def degree_order(row_ptr_l, row_ptr_r=None):

@@ -19,6 +19,7 @@
 //     No atomics (:1456-1458 uses a spin on atomicExch), so the result is reproducible for fixed
 //     knobs, and the epilogue (accumulate / GIN combine / row scale) is applied exactly once.
 #include <algorithm>
+#include <climits>
 #include <map>
 #include <mutex>
 #include <utility>
@@ -27,28 +28,20 @@
 // Compile-time tuning, per row width (LPR = lanes that read one row).  Chosen by measurement on
 // B200: narrow rows (dim <= 16) are served mostly from L2 and want many resident warps, so registers
 // are capped (3 blocks of 512 threads -> 40 registers); wide rows stream from HBM, run one batch
-// per node on typical graphs, and do better without the cap.  Prefetching the next batch of ids
-// paid off only below that occupancy, so it is off by default.
+// per node on typical graphs, and do better without the cap.
 //   MGGB_AGG_MIN_BLOCKS_NARROW  second argument of __launch_bounds__(512, .) for LPR <= 4
 //   MGGB_AGG_MAX_ROUNDS         load rounds issued back to back (rows in flight = rounds * 32/LPR)
-//   MGGB_AGG_PREFETCH_NARROW    1: request the next batch of neighbor ids before gathering the rows
 #ifndef MGGB_AGG_MIN_BLOCKS_NARROW
 #define MGGB_AGG_MIN_BLOCKS_NARROW 3
 #endif
 #ifndef MGGB_AGG_MAX_ROUNDS
 #define MGGB_AGG_MAX_ROUNDS 4
 #endif
-#ifndef MGGB_AGG_ROW_LOAD
-#define MGGB_AGG_ROW_LOAD 0   // how a row is loaded: 0 read-only path (L1-cached), 1 L2 only, 2 read-only path without L1 allocation
-#endif
-#ifndef MGGB_AGG_PREFETCH_NARROW
-#define MGGB_AGG_PREFETCH_NARROW 0
-#endif
 
 namespace {
 
 constexpr int HUB_WARPS = 16;        // warps of a hub row's block
-constexpr int HUB_GRID = 148 * 2;    // blocks walking the hub list (two per SM)
+constexpr int HUB_BLOCKS_PER_SM = 2;  // blocks walking the hub list, per SM of the device
 constexpr int HUB_MIN_EDGES = 16384; // smallest neighbor count treated as a hub (a 4-warp block needs > 100 us for it)
 constexpr int HUB_CAP = 1 << 18;     // list entries: enough for every row above 16384 edges of a 2^32-edge shard
 
@@ -88,15 +81,7 @@ template <int VEC> struct Vec;
 template <> struct Vec<4> {
     float4 v;
     __device__ __forceinline__ void zero() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
-    __device__ __forceinline__ void load(const float* p) {
-#if MGGB_AGG_ROW_LOAD == 1
-        v = __ldcg(reinterpret_cast<const float4*>(p));
-#elif MGGB_AGG_ROW_LOAD == 2
-        asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-#else
-        v = __ldg(reinterpret_cast<const float4*>(p));
-#endif
-    }
+    __device__ __forceinline__ void load(const float* p) { v = __ldg(reinterpret_cast<const float4*>(p)); }
     __device__ __forceinline__ void add(const Vec& o) { v.x += o.v.x; v.y += o.v.y; v.z += o.v.z; v.w += o.v.w; }
     __device__ __forceinline__ void xor_reduce(int off) {
         v.x += __shfl_xor_sync(0xffffffffu, v.x, off);
@@ -474,6 +459,18 @@ __global__ void __launch_bounds__(512, 2) sag_hub_rows_kernel(const AggParams P)
     }
 }
 
+constexpr int GROUP_HUB_MIN_EDGES = 1024;   // group-per-node kernel: longer lists would leave one 4-lane group as the kernel's tail
+
+// Neighbor count above which a row is handed to the wide-block kernel, or -1 when these knobs use no
+// hub list at all.  One definition for the launch code, the allocation-free entry point's size
+// check and mggb_hub_threshold().
+long long hub_threshold(int ps, int wpb, int dist, int dim, int flags) {
+    if ((flags & MGGB_AGG_NO_HUB_SPLIT) || wpb > HUB_WARPS / 2 || (size_t)HUB_WARPS * dim * sizeof(float) > 200 * 1024) return -1;
+    if ((flags & MGGB_AGG_GROUP_PER_NODE) && dim == 16) return GROUP_HUB_MIN_EDGES;
+    const long long chunk = std::min<long long>((long long)ps * dist, 1 << 24);
+    return std::max<long long>(HUB_MIN_EDGES, 64 * chunk * wpb);
+}
+
 // Exact unsigned division by a runtime constant d for every 32-bit numerator:
 // q = (n * magic) >> shift with shift = 32 + ceil(log2 d), magic = ceil(2^shift / d) < 2^33.
 void make_divider(uint32_t d, unsigned long long* magic, int* shift) {
@@ -521,7 +518,7 @@ int launch_walk(const AggParams& P, int wpb, cudaStream_t st) {
         const size_t hub_smem = (size_t)HUB_WARPS * P.dim * sizeof(float);
         if (hub_smem > 48 * 1024)
             MGGB_CUDA(cudaFuncSetAttribute(sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE, (WALK == 2 ? 2 : 1)>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem));
-        sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE, (WALK == 2 ? 2 : 1)><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
+        sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE, (WALK == 2 ? 2 : 1)><<<HUB_BLOCKS_PER_SM * mggb::sm_count(), HUB_WARPS * 32, hub_smem, st>>>(P);
         MGGB_CUDA(cudaGetLastError());
     }
     return MGGB_OK;
@@ -531,7 +528,7 @@ int launch_walk(const AggParams& P, int wpb, cudaStream_t st) {
 template <int LPR, int VEC, bool EXACT, int REMOTE_MODE>
 int launch_kernel(const AggParams& P, int wpb, cudaStream_t st) {
     if (P.chunk < 32) return launch_walk<LPR, VEC, EXACT, REMOTE_MODE, 2>(P, wpb, st);
-    return launch_walk<LPR, VEC, EXACT, REMOTE_MODE, ((LPR <= 4) && MGGB_AGG_PREFETCH_NARROW) ? 1 : 0>(P, wpb, st);
+    return launch_walk<LPR, VEC, EXACT, REMOTE_MODE, 0>(P, wpb, st);
 }
 
 // Hub work list: per (device, stream) so that calls ordered on one stream reuse it safely and calls
@@ -555,8 +552,6 @@ int hub_scratch(cudaStream_t st, HubScratch* out) {
     return MGGB_OK;
 }
 
-constexpr int GROUP_HUB_MIN_EDGES = 1024;   // longer lists would leave one 4-lane group as the kernel's tail
-
 // The group-per-node kernel, then the hub kernel for whatever it deferred.
 int launch_group_per_node(const AggParams& P, cudaStream_t st) {
     int mode = 1;
@@ -575,9 +570,9 @@ int launch_group_per_node(const AggParams& P, cudaStream_t st) {
     else sag_group_per_node_kernel<2><<<grid, GROUP_BLOCK, 0, st>>>(P);
     MGGB_CUDA(cudaGetLastError());
     if (P.hub_count != nullptr) {
-        if (mode == 0) sag_hub_rows_kernel<4, 4, true, 0, 1><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
-        else if (mode == 1) sag_hub_rows_kernel<4, 4, true, 1, 1><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
-        else sag_hub_rows_kernel<4, 4, true, 2, 1><<<HUB_GRID, HUB_WARPS * 32, hub_smem, st>>>(P);
+        if (mode == 0) sag_hub_rows_kernel<4, 4, true, 0, 1><<<HUB_BLOCKS_PER_SM * mggb::sm_count(), HUB_WARPS * 32, hub_smem, st>>>(P);
+        else if (mode == 1) sag_hub_rows_kernel<4, 4, true, 1, 1><<<HUB_BLOCKS_PER_SM * mggb::sm_count(), HUB_WARPS * 32, hub_smem, st>>>(P);
+        else sag_hub_rows_kernel<4, 4, true, 2, 1><<<HUB_BLOCKS_PER_SM * mggb::sm_count(), HUB_WARPS * 32, hub_smem, st>>>(P);
         MGGB_CUDA(cudaGetLastError());
     }
     return MGGB_OK;
@@ -627,12 +622,14 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
     P.chunk = (int)std::min<long long>((long long)ps * dist, 1 << 24);  // larger than any useful chunk: same walk
     make_divider((uint32_t)node_per_pe, &P.div_magic, &P.div_shift);
     P.mode = mode; P.self_scale = self_scale;
-    // Hub rows get wide blocks unless the caller asked for none or already runs wide blocks.
+    // Hub rows get wide blocks unless the caller asked for none, already runs wide blocks, or the wide
+    // block's partial rows would not fit in shared memory (then every node stays on its own block).
     P.hub_count = nullptr; P.hub_list = nullptr; P.hub_cap = 0;
-    P.hub_min_edges = std::max(HUB_MIN_EDGES, 64 * P.chunk * wpb);
-    if (caller_scratch != nullptr) {
+    const long long hub_min = hub_threshold(ps, wpb, dist, dim, caller_scratch ? (flags & ~MGGB_AGG_GROUP_PER_NODE) : flags);
+    P.hub_min_edges = (int)std::min<long long>(std::max<long long>(hub_min, 0), INT_MAX);
+    if (hub_min >= 0 && caller_scratch != nullptr) {
         P.hub_count = caller_scratch->count; P.hub_list = caller_scratch->list; P.hub_cap = caller_scratch_cap;
-    } else if (!(flags & MGGB_AGG_NO_HUB_SPLIT) && wpb <= HUB_WARPS / 2 && (size_t)HUB_WARPS * dim * sizeof(float) <= 200 * 1024) {
+    } else if (hub_min >= 0) {
         HubScratch hs;
         int st_ = hub_scratch((cudaStream_t)stream, &hs);
         if (st_ != MGGB_OK) return st_;
@@ -644,9 +641,10 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
         bool aligned = ((uintptr_t)output % 16 == 0);
         for (int p = 0; p < num_pes; p++) aligned = aligned && ((uintptr_t)peer_input[p] % 16 == 0);
         for (int k = 0; k < num_publish; k++) aligned = aligned && ((uintptr_t)publish_out[k] % 16 == 0);
-        if (aligned) {
-            if (P.hub_count != nullptr) P.hub_min_edges = GROUP_HUB_MIN_EDGES;   // 4 lanes are slow on long lists
+        if (aligned)   // hub_threshold() already gave this kernel its own, lower threshold
             return launch_group_per_node(P, st);
+        if (P.hub_count != nullptr) {   // not taken after all: back to the wide-row threshold
+            P.hub_min_edges = (int)std::min<long long>(hub_threshold(ps, wpb, dist, dim, flags & ~MGGB_AGG_GROUP_PER_NODE), INT_MAX);
         }
     }
     bool vec4 = (dim % 4 == 0);
@@ -721,10 +719,11 @@ int mggb_sag_np_div_static(float* output, const float* const* peer_input, int nu
     MGGB_REQUIRE(part_size >= 1 && interleaved_dist >= 1 && warp_per_block >= 1 && warp_per_block <= HUB_WARPS / 2,
                  "sag_np_div_static: need part_size >= 1, interleaved_dist >= 1 and 1 <= warp_per_block <= %d", HUB_WARPS / 2);
     // Every listed row has more than hub_min neighbors, so at most shard_edges / (hub_min + 1) rows
-    // can be listed; refuse shards for which that bound does not fit the fixed list.
-    const long long chunk = std::min<long long>((long long)part_size * interleaved_dist, 1 << 24);
-    const long long hub_min = std::max<long long>(HUB_MIN_EDGES, 64 * chunk * warp_per_block);
-    const long long max_edges = (long long)STATIC_HUB_CAP * (hub_min + 1);
+    // can be listed; refuse shards for which that bound does not fit the fixed list.  (The group-per-node
+    // kernel is not offered here: its threshold of 1024 neighbors would shrink that bound sixteenfold.)
+    const int eff_flags = flags & ~(MGGB_AGG_NO_HUB_SPLIT | MGGB_AGG_GROUP_PER_NODE);
+    const long long hub_min = hub_threshold(part_size, warp_per_block, interleaved_dist, dim, eff_flags);
+    const long long max_edges = hub_min < 0 ? LLONG_MAX : (long long)STATIC_HUB_CAP * (hub_min + 1);
     if (shard_edges > max_edges)
         return mggb::fail(MGGB_ERR_UNSUPPORTED,
                           "sag_np_div_static: a shard of %lld edges may hold more than %d hub rows (limit %lld edges at these knobs); "
@@ -735,7 +734,14 @@ int mggb_sag_np_div_static(float* output, const float* const* peer_input, int nu
     return aggregate(output, peer_input, num_pes, row_ptr_l, col_idx_l, row_ptr_r, col_idx_r, lb, ub, dim,
                      node_per_pe, pe, part_size, warp_per_block, interleaved_dist, row_scale,
                      (flags & MGGB_AGG_ACCUMULATE) ? MODE_ACCUMULATE : MODE_OVERWRITE, 0.f, publish_out,
-                     num_publish, flags & ~MGGB_AGG_NO_HUB_SPLIT, stream, &hs, STATIC_HUB_CAP);
+                     num_publish, eff_flags, stream, &hs, STATIC_HUB_CAP);
+}
+
+int mggb_hub_threshold(int part_size, int warp_per_block, int interleaved_dist, int dim, int flags, int64_t* threshold) {
+    MGGB_REQUIRE(threshold, "hub_threshold: NULL output");
+    MGGB_REQUIRE(part_size >= 1 && interleaved_dist >= 1 && warp_per_block >= 1 && dim >= 1, "hub_threshold: knobs and dim must be >= 1");
+    *threshold = hub_threshold(part_size, warp_per_block, interleaved_dist, dim, flags);
+    return MGGB_OK;
 }
 
 int mggb_sag_np_div(float* output, const float* const* peer_input, int num_pes,

@@ -28,4 +28,20 @@ void clear_error();
             return mggb::fail(MGGB_ERR_CUDA, "%s failed: %s (%s:%d)", #call,              \
                               cudaGetErrorString(e__), __FILE__, __LINE__);               \
     } while (0)
+
+namespace mggb {
+// Multiprocessors of the current device (asked once per device; 1 if the query fails, which only
+// makes a grid smaller).  Grids are sized from this, never from a typed-in count.
+inline int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) return 1;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+}  // namespace mggb
 #endif

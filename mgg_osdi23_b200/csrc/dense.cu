@@ -110,9 +110,7 @@ int dense_simt(float* out, const float* x, const float* w, int64_t n, int dim1, 
     const size_t smem = ((size_t)BM * (BK + 1) + (size_t)BK * CT * TN) * sizeof(float);
     if (smem > 48 * 1024)
         MGGB_CUDA(cudaFuncSetAttribute(dense_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    int dev = 0, sms = 148;
-    MGGB_CUDA(cudaGetDevice(&dev));
-    MGGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int sms = mggb::sm_count();
     const long long tiles = (n + BM - 1) / BM;
     const int grid = (int)(tiles < (long long)sms * 4 ? tiles : (long long)sms * 4);
     dense_simt_kernel<<<grid, THREADS, smem, st>>>(out, x, w, n, dim1, dim2, row_scale,

@@ -170,9 +170,7 @@ extern "C" int mggb_dense_softmax_forward(float* out, float* logits, const float
                           "(dim2 <= 256 and %zu bytes of shared memory <= 160 KiB); call mggb_dense_forward then mggb_softmax_forward",
                           dim1, dim2, smem);
     if (n == 0) return MGGB_OK;
-    int dev = 0, sms = 148;
-    MGGB_CUDA(cudaGetDevice(&dev));
-    MGGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int sms = mggb::sm_count();
     const long long groups = (n + FS_ROWS - 1) / FS_ROWS;
     const long long blocks = (groups + FS_WARPS - 1) / FS_WARPS;
     const int per_sm = smem > 64 * 1024 ? 1 : 2;

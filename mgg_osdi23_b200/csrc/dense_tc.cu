@@ -68,6 +68,7 @@ struct TcParams {
     const float* row_scale;
     long long n;
     int K, M, Npad, nchunks, stages, relu, stage_out;
+    int vec_store;   // 1: dim2 % 4 == 0 and out and every publish destination are 16-byte aligned (128-bit stores)
     unsigned tmem_cols;
     Publish pub;
 };
@@ -89,22 +90,10 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, unsigned parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-#ifdef MGGB_DENSE_PROFILE
-// Build-time diagnostic: cycles CTA 0 spent inside each kind of wait (index = wait code) and in total
-// per role (index 8 + role).  Read with mggb_dense_profile().
-__device__ unsigned long long g_dense_cycles[16];
-#define MGGB_PROF_ADD(idx, start) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_dense_cycles[idx], (unsigned long long)(clock64() - (start))); } while (0)
-#else
-#define MGGB_PROF_ADD(idx, start) do { } while (0)
-#endif
-
 // Bounded wait: false when the limit ran out or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, unsigned parity, volatile int* abort_flag, int code) {
-#ifdef MGGB_DENSE_PROFILE
-    const long long t0 = clock64();
-#endif
     for (unsigned i = 0; i < SPIN_LIMIT; i++) {
-        if (mbar_try(bar, parity)) { MGGB_PROF_ADD(code, t0); return true; }
+        if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
         if (i > 32) __nanosleep(64);
     }
@@ -406,7 +395,7 @@ __device__ void epilogue_role(const TcParams& P, float* out_stage, uint32_t tful
                     // park the row in shared memory; the warp stores its 32 rows coalesced below
 #pragma unroll
                     for (int j = 0; j < 16; j++) out_stage[lane * (P.Npad + 1) + c0 + j] = v[j];   // odd pitch: no bank conflicts
-                } else if ((P.M & 3) == 0 && c0 + 16 <= P.M) {
+                } else if (P.vec_store && c0 + 16 <= P.M) {
 #pragma unroll
                     for (int j = 0; j < 16; j += 4) {
                         const float4 f = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -434,7 +423,7 @@ __device__ void epilogue_role(const TcParams& P, float* out_stage, uint32_t tful
             const int total = (int)max(0LL, min(32LL, P.n - first)) * P.M;
             const long long o = first * P.M;
             const float inv_m = 1.0f / (float)P.M;   // (i + 0.5) * inv_m truncates to i / M exactly for i < 2^13
-            if ((P.M & 3) == 0) {
+            if (P.vec_store) {
                 for (int i = lane * 4; i < total; i += 128) {
                     const int r = (int)(((float)i + 0.5f) * inv_m);
                     const float* src = out_stage + r * (P.Npad + 1) + (i - r * P.M);
@@ -504,9 +493,6 @@ __global__ void __launch_bounds__(THREADS, 1) dense_tc_kernel(const TcParams P) 
     const uint32_t tmem_base = s_tmem_base;
 
     const long long tiles = (P.n + TILE_M - 1) / TILE_M;
-#ifdef MGGB_DENSE_PROFILE
-    const long long role_t0 = clock64();
-#endif
     if (UseProducer<G>::value && warp < 2 * LOADER_WARPS) {
         producer_role<G>(P, ring, full0, empty0, &s_abort, blockIdx.x, gridDim.x, tiles);
     } else if (warp < LOADER_WARPS) {
@@ -522,7 +508,6 @@ __global__ void __launch_bounds__(THREADS, 1) dense_tc_kernel(const TcParams P) 
         mma_role(P, smem_u32(ring), smem_u32(w_hi), smem_u32(w_lo), full0, empty0, tfull0, tempty0, tmem_base,
                  &s_abort, blockIdx.x, gridDim.x, tiles);
     }
-    MGGB_PROF_ADD(8 + (warp < LOADER_WARPS ? 0 : warp < 2 * LOADER_WARPS ? 1 : warp < 2 * LOADER_WARPS + 4 ? 2 : 3), role_t0);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 2 * LOADER_WARPS + 4) {
@@ -564,14 +549,17 @@ int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, in
     P.K = dim1; P.M = dim2; P.Npad = Npad; P.nchunks = nchunks; P.stages = stages;
     P.relu = (flags & MGGB_DENSE_RELU) ? 1 : 0;
     P.stage_out = stage_out ? 1 : 0;
+    // 128-bit stores need 16-byte aligned destinations (a view that starts at an odd float offset is
+    // not); otherwise the epilogue stores float by float.
+    bool vec_store = (dim2 % 4 == 0) && ((uintptr_t)out % 16 == 0);
+    for (int q = 0; q < num_publish; q++) vec_store = vec_store && ((uintptr_t)publish_out[q] % 16 == 0);
+    P.vec_store = vec_store ? 1 : 0;
     P.tmem_cols = tmem_cols;
     P.pub.n = num_publish;
     for (int q = 0; q < num_publish; q++) P.pub.dst[q] = publish_out[q];
 
     const size_t smem = fixed + (size_t)stages * STAGE_BYTES;
-    int dev = 0, sms = 148;
-    MGGB_CUDA(cudaGetDevice(&dev));
-    MGGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int sms = mggb::sm_count();
     const long long tiles = (n + TILE_M - 1) / TILE_M;
     const int grid = (int)std::min<long long>(tiles, sms);
     const bool wide = (dim1 % 4 == 0) && ((uintptr_t)x % 16 == 0);
@@ -598,14 +586,3 @@ extern "C" int mggb_dense_device_status(int* status, int reset) {
     }
     return MGGB_OK;
 }
-
-#ifdef MGGB_DENSE_PROFILE
-extern "C" int mggb_dense_profile(unsigned long long* cycles16, int reset) {
-    MGGB_CUDA(cudaMemcpyFromSymbol(cycles16, g_dense_cycles, sizeof(unsigned long long) * 16));
-    if (reset) {
-        unsigned long long zero[16] = {0};
-        MGGB_CUDA(cudaMemcpyToSymbol(g_dense_cycles, zero, sizeof(zero)));
-    }
-    return MGGB_OK;
-}
-#endif

@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(256) publish_copy_kernel(const T* __restrict__
 
 int grid_for(long long work_items, int block) {
     long long g = (work_items + block - 1) / block;
-    const long long cap = 148LL * 16;
+    const long long cap = 16LL * mggb::sm_count();
     return (int)(g < 1 ? 1 : (g > cap ? cap : g));
 }
 
@@ -83,9 +83,7 @@ int mggb_publish_rows(const float* in, int64_t count, float* const* publish_out,
     }
     // One block per SM at most: enough stores in flight for the links, and room left on every SM for a
     // kernel that runs beside this one on another stream.
-    int dev = 0, sms = 148;
-    MGGB_CUDA(cudaGetDevice(&dev));
-    MGGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int sms = mggb::sm_count();
     if (wide)
         publish_copy_kernel<float4><<<std::min(grid_for(count / 4, 256), sms), 256, 0, (cudaStream_t)stream>>>(
             reinterpret_cast<const float4*>(in), count / 4, pub);

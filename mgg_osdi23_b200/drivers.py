@@ -16,8 +16,10 @@ Differences from the reference's drivers that are deliberate:
 * the dense step computes ``X*W`` from its input (the reference multiplies its output buffer in place);
 * both GCN aggregations run at the hidden width, as in the reference (``:214-215, :221-222``), which is
   legitimate because layer 2 is evaluated as ``(A*H)*W2``;
-* publishing alternates between two symmetric buffers so that no PE overwrites a buffer a slower
-  peer may still be reading.
+* publishing alternates between symmetric buffers so that no PE overwrites a buffer a slower peer may
+  still be reading, within a pass AND from one pass to the next: the buffer a pass writes first is
+  never the one its last stage reads (the 5-layer GIN needs a third buffer for that; a model that
+  cannot arrange it starts every pass with a barrier, ``leading_barrier``).
 
 How peers see a layer's output is chosen by what is passed as ``sym_a`` / ``sym_b``:
 * a :class:`symmem.SymmetricBuffer` (or :class:`LocalSym`): each PE keeps only its own rows and the
@@ -31,6 +33,7 @@ How peers see a layer's output is chosen by what is passed as ``sym_a`` / ``sym_
 """
 from __future__ import annotations
 
+import ctypes as C
 from contextlib import contextmanager
 from dataclasses import dataclass
 from typing import Callable, List, Optional, Sequence
@@ -38,7 +41,7 @@ from typing import Callable, List, Optional, Sequence
 import numpy as np
 import torch
 
-from . import api
+from . import api, _lib
 from .symmem import SymmetricBuffer
 
 
@@ -81,9 +84,14 @@ class Shard:
         # where a warp otherwise runs as long as the longest of its eight lists).
         if order_rows is None:
             order_rows = True
+        # longest neighbor list of the shard: when no row reaches the hub threshold the aggregation is
+        # told so (NO_HUB_SPLIT) and the second kernel, which would find an empty list, is not launched
+        deg = (lp[1:] - lp[:-1]) + (rp[1:] - rp[:-1])
+        self.max_degree = int(deg.max()) if self.rows else 0
         self._order_host = api.degree_order(lp, rp) if (order_rows and self.rows) else None
         self.row_order = torch.from_numpy(self._order_host).to(dev) if self._order_host is not None else None
         self._blocks = {}
+        self._flag_cache = {}
         self._dinv = None
         self.event_sink = None   # when a list: (start, end) CUDA events of every aggregation launch are appended
         self._in_span = False
@@ -144,18 +152,26 @@ class Shard:
                 api.inv_sqrt_degree(self._dinv, self.rp_l, self.rp_r)
         return self._dinv
 
+    def agg_flags(self, knobs: Knobs, dim: int) -> int:
+        """The knobs' flags, plus NO_HUB_SPLIT when no row of this shard exceeds the hub threshold."""
+        key = (knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, knobs.flags, dim)
+        if key not in self._flag_cache:
+            thr = api.hub_threshold(knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, dim, knobs.flags)
+            self._flag_cache[key] = knobs.flags | (_lib.AGG_NO_HUB_SPLIT if (thr < 0 or self.max_degree <= thr) else 0)
+        return self._flag_cache[key]
+
     def aggregate(self, out, sym, dim, knobs: Knobs, accumulate=False, row_scale_=None, publish=None, rows=None):
         """``rows``: a row list from :meth:`row_blocks` (only those rows are computed); None = the whole shard."""
         self._timed(lambda: api.mgg_SAG_np_div(
             out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim, self.node_per_pe, self.pe,
             knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, accumulate=accumulate, row_scale_=row_scale_,
-            publish=publish, row_order=self.row_order, rows=rows, flags=knobs.flags))
+            publish=publish, row_order=self.row_order, rows=rows, flags=self.agg_flags(knobs, dim)))
 
     def aggregate_gin(self, out, sym, dim, knobs: Knobs, eps: float, rows=None):
         self._timed(lambda: api.mgg_GIN_np_div(
             out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim, self.node_per_pe, self.pe,
             knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, eps, row_order=self.row_order, rows=rows,
-            flags=knobs.flags))
+            flags=self.agg_flags(knobs, dim)))
 
 
 def nccl_stream_barrier(group=None) -> Callable[[], None]:
@@ -168,6 +184,34 @@ def nccl_stream_barrier(group=None) -> Callable[[], None]:
     return barrier
 
 
+class FlagBarrier:
+    """Barrier for one-process-per-GPU runs without NCCL on the path: epoch flags in peer-mapped memory
+    (``mggb_flag_barrier``).  Calling the object enqueues one small kernel on the current stream; the
+    host never blocks.  The kernel's wait is bounded (``timeout_s``); ``status()`` synchronises and
+    returns 0, or 1 + the PE that never arrived at some barrier since the last ``reset``."""
+
+    def __init__(self, group, pe: int, num_pes: int, timeout_s: float = 2.0):
+        self.pe, self.num_pes = pe, num_pes
+        self.slots = SymmetricBuffer(_lib.MAX_PES, group, pe, num_pes)     # zero-filled 4-byte slots: epoch 0
+        self.table = (C.c_void_p * num_pes)(*self.slots.peer_ptrs)
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.epoch = 0
+
+    def __call__(self):
+        self.epoch += 1
+        api.kernel_launches[0] += 1
+        _lib.check(_lib.lib.mggb_flag_barrier(self.table, self.num_pes, self.pe, self.epoch, self.timeout_ns,
+                                              C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def status(self, reset: bool = False) -> int:
+        st = C.c_int(0)
+        _lib.check(_lib.lib.mggb_flag_barrier_status(C.byref(st), int(reset)))
+        return st.value
+
+    def close(self):
+        self.slots.close()
+
+
 def run_stages(models: Sequence, barrier: Optional[Callable[[], None]] = None, marks: Optional[list] = None):
     """Runs every model's stage s (all PEs held by this process), then the barrier, for each s.
     ``marks``: when a list, a CUDA event is recorded before the first stage and after every stage and
@@ -177,6 +221,11 @@ def run_stages(models: Sequence, barrier: Optional[Callable[[], None]] = None, m
     if marks is not None:
         ev = [torch.cuda.Event(enable_timing=True)]
         ev[0].record()
+    if barrier is not None and any(getattr(m, "leading_barrier", False) for m in models):
+        # stage 0 overwrites a buffer that a slower peer may still be reading in its previous pass
+        barrier()
+        if ev is not None:
+            ev.append(torch.cuda.Event(enable_timing=True)); ev[-1].record()
     for s in range(n):
         for m in models:
             m.stages[s]()
@@ -211,6 +260,9 @@ class _Forward:
         self.overlap_blocks = 1
         self.overlap_min_rows = 8192      # rows per block below which cutting the shard does not pay
         self._side = None
+        # True: a pass starts with a barrier, because its first stage overwrites the published buffer
+        # that the previous pass's LAST stage reads (a slower peer may still be gathering from it).
+        self.leading_barrier = False
 
     # An aggregation pushes its rows from its own epilogue only while that is a small transfer: the
     # epilogue writes one row per store, in the block schedule's (degree) order, and a peer then receives
@@ -250,7 +302,7 @@ class _Forward:
         run_stages([self], barrier, marks)
         return self.out
 
-    def forward_host(self, x_host: torch.Tensor, barrier=None, chunks: int = 8) -> torch.Tensor:
+    def forward_host(self, x_host: torch.Tensor, barrier=None, chunks: int = 8, marks: Optional[list] = None) -> torch.Tensor:
         """The call a user with HOST data makes: uploads this PE's feature rows (pinned ``x_host``
         [rows, in_dim]), runs the forward pass and returns the class probabilities in pinned host
         memory.  Synchronises the stream before returning.
@@ -267,6 +319,8 @@ class _Forward:
             cur = torch.cuda.current_stream()
             if self._copy_stream is None:
                 self._copy_stream = torch.cuda.Stream()
+            if barrier is not None and self.leading_barrier:
+                barrier()
             cs = self._copy_stream
             cs.wait_stream(cur)                 # the previous pass no longer reads d_in
             step = (rows + chunks - 1) // chunks
@@ -284,7 +338,12 @@ class _Forward:
                 self.stages[s]()
         if self._h_out is None:
             self._h_out = torch.empty(self.out.shape, dtype=torch.float32, pin_memory=True)
+        if ev is not None:
+            ev[1].record()
         self._h_out.copy_(self.out, non_blocking=True)
+        if ev is not None:
+            ev[2].record()
+            marks.append(ev)
         torch.cuda.current_stream().synchronize()
         return self._h_out
 
@@ -361,7 +420,7 @@ class GIN5Forward(_Forward):
 
     def __init__(self, shard: Shard, in_dim: int, hidden: int, out_dim: int, sym_a, sym_b, knobs: Knobs,
                  eps: float = 0.5, weights: Optional[Sequence[torch.Tensor]] = None, num_layers: int = 5,
-                 dense_flags: int = 0):
+                 dense_flags: int = 0, sym_c=None):
         super().__init__(shard, sym_a, sym_b, knobs)
         dev, rows = shard.device, max(shard.rows, 1)
         self.in_dim, self.hidden, self.out_dim, self.eps, self.num_layers = in_dim, hidden, out_dim, eps, num_layers
@@ -369,21 +428,31 @@ class GIN5Forward(_Forward):
         self.d_agg = torch.zeros(rows, hidden, dtype=torch.float32, device=dev)[: shard.rows]
         self.logits = torch.zeros(rows, out_dim, dtype=torch.float32, device=dev)[: shard.rows]
         self.out = torch.zeros(rows, out_dim, dtype=torch.float32, device=dev)[: shard.rows]
-        syms = [sym_a, sym_b]
-        self.dense = [api.dense_param_new_beg("d-1", self.d_in, self._sym_view(sym_a, hidden), shard.rows, in_dim, hidden)]
+        # Layer k reads what dense[k] published.  Consecutive layers must use different buffers, and so
+        # must the first and the last of a pass (the next pass's first dense product may start while a
+        # slower peer still gathers for the last layer): A B A B ... with the LAST one on the third
+        # buffer when the count is odd.  Without a third buffer such a pass starts with a barrier.
+        syms = [sym_a, sym_b][: 2 if sym_b is not None else 1]
+        seq = [syms[k % len(syms)] for k in range(num_layers)]
+        if seq[-1] is seq[0]:
+            if sym_c is not None and num_layers > 1:
+                seq[-1] = sym_c
+            else:
+                self.leading_barrier = True
+        self.dense = [api.dense_param_new_beg("d-1", self.d_in, self._sym_view(seq[0], hidden), shard.rows, in_dim, hidden)]
         for k in range(1, num_layers):
-            self.dense.append(api.dense_param_new_hidden(f"d-{k + 1}", self.d_agg, self._sym_view(syms[k % 2], hidden),
+            self.dense.append(api.dense_param_new_hidden(f"d-{k + 1}", self.d_agg, self._sym_view(seq[k], hidden),
                                                          shard.rows, hidden, hidden))
         self.dense.append(api.dense_param_new_hidden(f"d-{num_layers + 1}", self.d_agg, self.logits, shard.rows, hidden, out_dim))
         for k, dp in enumerate(self.dense):
             dp.flags = dense_flags
             if k < num_layers:
-                dp.publish = syms[k % 2].publish
+                dp.publish = seq[k].publish
         if weights is not None:
             for dp, w in zip(self.dense, weights):
                 dp.set_weight(w)
         self.smx = api.softmax_new_param("smx", self.logits, self.out, shard.rows, out_dim)
-        self._syms = syms
+        self._seq = seq
         self.stages = [self._first] + [self._layer(k) for k in range(num_layers)]
         self.first_dense = self.dense[0]
 
@@ -396,14 +465,14 @@ class GIN5Forward(_Forward):
             if not self.shard.rows:
                 return
             if k == self.num_layers - 1:
-                self.shard.aggregate_gin(self.d_agg, self._syms[k % 2], self.hidden, self.knobs, self.eps)
+                self.shard.aggregate_gin(self.d_agg, self._seq[k], self.hidden, self.knobs, self.eps)
                 api.dense_hidden_softmax_new_forward(self.dense[k + 1], self.smx, self.keep_logits)
             elif not self.dense[k + 1].publish:
-                self.shard.aggregate_gin(self.d_agg, self._syms[k % 2], self.hidden, self.knobs, self.eps)
+                self.shard.aggregate_gin(self.d_agg, self._seq[k], self.hidden, self.knobs, self.eps)
                 api.dense_hidden_new_forward(self.dense[k + 1])
             else:
                 self._blocked(
-                    lambda rows: self.shard.aggregate_gin(self.d_agg, self._syms[k % 2], self.hidden, self.knobs,
+                    lambda rows: self.shard.aggregate_gin(self.d_agg, self._seq[k], self.hidden, self.knobs,
                                                           self.eps, rows=rows),
                     lambda r0, r1: self.dense[k + 1]._forward_rows(r0, r1))
         return stage
@@ -432,6 +501,8 @@ class SingleAggregation(_Forward):
         self.scale = shard.inv_sqrt_degree() if norm == "sym" else None
         # push mode: the pass starts by pushing this PE's rows into the peers' replicas
         self.stages = [self._push, self._agg] if getattr(sym_a, "publish", None) else [self._agg]
+        # the next pass's push lands in the replicas that slower peers are still aggregating from
+        self.leading_barrier = len(self.stages) == 2
 
     def _push(self):
         if self.shard.rows:

@@ -21,9 +21,18 @@ _I32P = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
 _F32P = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 
 
-def build(verbose: bool = False) -> None:
+def reference_root() -> str | None:
+    """Where the reference project's sources lie: $MGG_REFERENCE_ROOT, else a directory named
+    ``reference`` beside this repository.  None when neither exists."""
+    cand = os.environ.get("MGG_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "include")) else None
+
+
+def build(verbose: bool = False, ref_root: str | None = None) -> None:
     """Run the Makefile (gcc for the restatement; nvcc for the reference shim when its sources are present)."""
-    r = subprocess.run(["make", "-C", _HERE], capture_output=True, text=True)
+    ref_root = ref_root or reference_root()
+    cmd = ["make", "-C", _HERE] + ([f"REF_ROOT={ref_root}"] if ref_root else [])
+    r = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or r.returncode != 0:
         print(r.stdout, r.stderr)
     if r.returncode != 0:
@@ -57,6 +66,9 @@ class Oracle:
         L.orc_sag_f64.argtypes = [_F32P, _F32P, _I32P, _I32P, C.c_int64, C.c_int]
         L.orc_sag_omp.argtypes = [_F32P, _F32P, _I32P, _I32P, C.c_int64, C.c_int]
         L.orc_sag_omp.restype = C.c_int
+        L.orc_sag_f64_omp.argtypes = [_F32P, _F32P, _I32P, _I32P, C.c_int64, C.c_int]
+        L.orc_set_threads.argtypes = [C.c_int]
+        L.orc_get_threads.restype = C.c_int
         L.orc_shard_aggregate.argtypes = [_F32P, C.POINTER(C.c_void_p), C.c_int, C.c_int, _I32P, C.c_void_p,
                                           _I32P, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int64,
                                           C.c_int, C.c_int, C.c_float, C.c_void_p]
@@ -84,6 +96,23 @@ class Oracle:
         out = np.zeros((n, dim), np.float32)
         self.lib.orc_sag_f64(out, x, row_ptr, col, n, dim)
         return out
+
+    def sag_f64_omp(self, x, row_ptr, col):
+        """``sag_f64`` with the rows dealt to OpenMP threads (same values)."""
+        x, row_ptr, col = _f32(x), _i32(row_ptr), _i32(col)
+        n, dim = len(row_ptr) - 1, x.shape[1]
+        out = np.zeros((n, dim), np.float32)
+        self.lib.orc_sag_f64_omp(out, x, row_ptr, col, n, dim)
+        return out
+
+    def set_threads(self, threads: int) -> int:
+        """Sets the thread count of the OpenMP routines (dense, softmax, sag_omp, sag_f64_omp) at run
+        time, whatever OMP_NUM_THREADS said when the runtime was loaded; returns the count in effect."""
+        self.lib.orc_set_threads(int(threads))
+        return int(self.lib.orc_get_threads())
+
+    def get_threads(self) -> int:
+        return int(self.lib.orc_get_threads())
 
     def sag_omp(self, x, row_ptr, col, out=None):
         x, row_ptr, col = _f32(x), _i32(row_ptr), _i32(col)

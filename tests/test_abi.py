@@ -58,3 +58,30 @@ def test_missing_library_fails_loudly(tmp_path, monkeypatch):
         assert "no fallback" in str(e)
     else:
         raise AssertionError("expected ImportError")
+
+
+def test_hub_threshold_follows_the_documented_rule():
+    """max(16384, 64*ps*dist*wpb) for the block-per-node kernels, 1024 for the group-per-node kernel at
+    dim 16, -1 (no hub list) for wide blocks, the no-split flag, or rows too wide for the 16-warp block."""
+    from mgg_osdi23_b200 import api, _lib
+    assert api.hub_threshold(16, 4, 1, 16) == 16384
+    assert api.hub_threshold(32, 4, 2, 16) == 64 * 64 * 4
+    assert api.hub_threshold(32, 8, 16, 64) == 64 * 512 * 8
+    assert api.hub_threshold(16, 16, 1, 16) == -1
+    assert api.hub_threshold(16, 4, 1, 16, _lib.AGG_NO_HUB_SPLIT) == -1
+    assert api.hub_threshold(16, 4, 1, 16, _lib.AGG_GROUP_PER_NODE) == 1024
+    assert api.hub_threshold(16, 4, 1, 64, _lib.AGG_GROUP_PER_NODE) == 16384
+    assert api.hub_threshold(16, 4, 1, 4000) == -1
+    assert api.hub_threshold(1 << 20, 8, 1 << 10, 16) == 64 * (1 << 24) * 8          # computed in 64 bits
+
+
+def test_shard_tells_the_aggregation_when_it_has_no_hub_rows():
+    import numpy as np
+    from mgg_osdi23_b200 import drivers, _lib
+    rp = np.array([0, 3, 5, 40000], np.int32)
+    col = np.zeros(40000, np.int32)
+    sh = drivers.Shard(rp, col, 0, 1, device="cpu")
+    assert sh.max_degree == 39995
+    assert sh.agg_flags(drivers.Knobs(16, 4, 1), 16) == 0                                 # a row above 16384: keep the hub kernel
+    assert sh.agg_flags(drivers.Knobs(32, 8, 8), 16) == _lib.AGG_NO_HUB_SPLIT             # threshold 131072: nothing reaches it
+    assert sh.agg_flags(drivers.Knobs(16, 4, 1, _lib.AGG_GROUP_PER_NODE), 16) == _lib.AGG_GROUP_PER_NODE

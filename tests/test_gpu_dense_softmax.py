@@ -119,3 +119,28 @@ def test_fused_dense_softmax_refuses_what_it_cannot_hold():
     probs = torch.zeros(4, 300, device=dev)
     mgg.dense_hidden_softmax_new_forward(dp, mgg.softmax_new_param("s", dp.d_out, probs, 4, 300))
     np.testing.assert_allclose(probs.cpu().numpy(), 1.0 / 300, rtol=1e-6)
+
+
+@pytest.mark.parametrize("n,k,m", [(700, 64, 64), (600, 602, 16), (300, 100, 47)])
+def test_dense_output_and_publish_views_at_odd_float_offsets(oracle, n, k, m):
+    """out and the publish destinations only have to be 4-byte aligned: a view that starts one float
+    into an allocation takes the element-wise store path instead of 128-bit stores (which would fault)."""
+    dev = torch.device("cuda")
+    x = gg.features(n, k, seed=n).numpy()
+    w = gg.glorot_uniform(k, m, seed=k).numpy()
+    want = oracle.dense(x, w)
+    xd, wd = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
+    for off_out, off_pub in ((1, 0), (0, 3), (2, 1), (0, 0)):
+        raw_o = torch.zeros(n * m + 8, device=dev)
+        raw_p = torch.zeros(n * m + 8, device=dev)
+        out = raw_o[off_out:off_out + n * m].view(n, m)
+        pub = raw_p[off_pub:off_pub + n * m].view(n, m)
+        assert out.data_ptr() % 16 == (4 * off_out) % 16
+        mgg.dense_forward(out, xd, wd, publish=[pub])
+        torch.cuda.synchronize()
+        np.testing.assert_allclose(out.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+        assert torch.equal(out, pub)
+        assert float(raw_o[:off_out].abs().sum()) == 0.0 and float(raw_o[off_out + n * m:].abs().sum()) == 0.0
+    st = mgg._lib.C.c_int(-1)
+    mgg._lib.check(mgg._lib.lib.mggb_dense_device_status(mgg._lib.C.byref(st), 0))
+    assert st.value == 0

@@ -247,3 +247,59 @@ def test_single_aggregation_in_push_mode(oracle):
     torch.cuda.synchronize()
     got = np.concatenate([m.out.cpu().numpy() for m in models])
     np.testing.assert_allclose(got, oracle.sag_f64(x, rp, col), rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("fetch", ["peer", "replica"])
+def test_back_to_back_passes_never_overwrite_what_a_slow_peer_still_reads(oracle, fetch):
+    """Two passes with DIFFERENT inputs, the PEs run in the worst order a barrier-separated schedule
+    allows: PE 0 finishes pass 1 and runs the first stage of pass 2 (which publishes into its peers'
+    view) BEFORE PE 1 runs the last stage of pass 1.  PE 1's pass-1 result must still be the oracle's:
+    the first stage of a pass may not write the buffer the last stage reads.  The 5-layer GIN needs its
+    third published buffer for that; without one the model asks for a barrier at the start of a pass."""
+    g = gg.chung_lu_graph(1200, 12_000, 2.3, seed=5)
+    rp, col = g.row_ptr.numpy().astype(np.int32), g.col_idx.numpy()
+    n, din, hid, dout, G = g.num_nodes, 100, 64, 47, 2
+    xs = [gg.features(n, din, seed=4).numpy(), gg.features(n, din, seed=44).numpy()]
+    ws = [gg.glorot_uniform(din, hid, 10) * 0.1] + [gg.glorot_uniform(hid, hid, 11 + k) * 0.1 for k in range(4)] \
+        + [gg.glorot_uniform(hid, dout, 20) * 0.1]
+    dev = torch.device("cuda")
+    npp = (n + G - 1) // G
+    sa, sb = _published(G, npp, hid, dev, fetch)
+    sc, _ = _published(G, npp, hid, dev, fetch)
+
+    def want(x):
+        h = oracle.dense(x, ws[0].numpy())
+        for k in range(5):
+            h = oracle.dense((oracle.sag_f64(h, rp, col).astype(np.float64) + h).astype(np.float32), ws[k + 1].numpy())
+        return h
+
+    models = [drivers.GIN5Forward(drivers.Shard(rp, col, pe, G, device=dev), din, hid, dout, sa[pe], sb[pe],
+                                  drivers.Knobs(8, 2, 2), eps=0.0, weights=[w.to(dev) for w in ws], sym_c=sc[pe]) for pe in range(G)]
+    assert not any(m.leading_barrier for m in models)
+    for m in models:
+        m.keep_logits = True
+    load = lambda m, x: m.d_in.copy_(torch.from_numpy(x[m.shard.lb:m.shard.ub]).to(dev))
+    last = len(models[0].stages) - 1
+    for m in models:
+        load(m, xs[0])
+    for s in range(last):                       # pass 1 up to the last barrier
+        for m in models:
+            m.stages[s]()
+    models[0].stages[last]()                    # PE 0 finishes pass 1 ...
+    first = models[0].logits.clone()
+    load(models[0], xs[1])
+    models[0].stages[0]()                       # ... and starts pass 2 while PE 1 is still in pass 1
+    models[1].stages[last]()
+    torch.cuda.synchronize()
+    h = want(xs[0])
+    scale = max(1.0, float(np.abs(h).max()))
+    got = np.concatenate([first.cpu().numpy(), models[1].logits.cpu().numpy()])
+    np.testing.assert_allclose(got / scale, h / scale, rtol=1e-4, atol=ATOL)
+    # without the third buffer the model says so instead of racing
+    two = drivers.GIN5Forward(drivers.Shard(rp, col, 0, G, device=dev), din, hid, dout, sa[0], sb[0], drivers.Knobs(8, 2, 2))
+    assert two.leading_barrier
+    # a single aggregation that pushes starts its pass with a barrier too; the 2-layer GCN needs none
+    reps = drivers.local_replicas(G, npp, 16, dev)
+    assert drivers.SingleAggregation(drivers.Shard(rp, col, 0, G, device=dev), 16, reps[0], drivers.Knobs()).leading_barrier
+    ga, gb = _published(G, npp, 16, dev, fetch)
+    assert not drivers.GCN2Forward(drivers.Shard(rp, col, 0, G, device=dev), din, 16, dout, ga[0], gb[0], drivers.Knobs()).leading_barrier

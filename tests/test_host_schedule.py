@@ -78,3 +78,19 @@ def test_row_of_flat_index_trick_of_the_dense_epilogue_is_exact():
         i = np.arange(32 * m, dtype=np.int64)
         r = ((i.astype(np.float32) + np.float32(0.5)) * inv).astype(np.int32)
         assert np.array_equal(r, i // m), m
+
+
+def test_leading_barrier_is_issued_before_stage_zero():
+    """run_stages calls the barrier once more, first, for a model that asks for it (host logic only)."""
+    calls = []
+
+    class M:
+        leading_barrier = True
+        stages = [lambda: calls.append("s0"), lambda: calls.append("s1")]
+
+    drivers.run_stages([M()], barrier=lambda: calls.append("b"))
+    assert calls == ["b", "s0", "b", "s1"]
+    del calls[:]
+    M.leading_barrier = False
+    drivers.run_stages([M()], barrier=lambda: calls.append("b"))
+    assert calls == ["s0", "b", "s1"]

@@ -80,3 +80,69 @@ def test_static_scratch_variant_refuses_oversized_shards():
     assert _call(lib.mggb_sag_np_div_static, out, x, sh, 16, (16, 4, 1), extra_edges=too_many - 1) == _lib.OK
     assert _call(lib.mggb_sag_np_div_static, out, x, sh, 16, (16, 16, 1), extra_edges=10) == _lib.ERR_INVALID_ARG
     torch.cuda.synchronize()
+
+
+def test_static_scratch_variant_allocates_no_device_memory():
+    """The point of the variant: after its first call on a device (which loads the kernels and looks the
+    array's address up), further calls leave the device's free memory exactly as it was, hub rows
+    included.  Run in a fresh process, where the regular entry point has never been called and so its
+    heap work list does not exist: a variant that fell back to it would have to allocate it here."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = r'''
+import ctypes as C, sys
+import numpy as np, torch
+sys.path.insert(0, %r); sys.path.insert(0, %r)
+from mgg_osdi23_b200 import _lib, drivers
+from gpu_util import random_graph
+dev = torch.device("cuda")
+rp, col = random_graph(600, 30, seed=21, hubs=[(3, 40000), (250, 17000)])
+sh = drivers.Shard(rp, col, 0, 1, device=dev)
+x = torch.rand(600, 16, device=dev) * 0.01
+out = torch.zeros(600, 16, device=dev)
+table = (C.c_void_p * 1)(x.data_ptr())
+def call():
+    _lib.check(_lib.lib.mggb_sag_np_div_static(out.data_ptr(), table, 1, sh.rp_l.data_ptr(), sh.ci_l.data_ptr(), sh.rp_r.data_ptr(),
+                                               sh.ci_r.data_ptr(), sh.lb, sh.ub, sh.edges, 16, sh.node_per_pe, 0, 16, 4, 1, None, 0, None, 0, None))
+call(); torch.cuda.synchronize()
+free0 = torch.cuda.mem_get_info()[0]
+for _ in range(4):
+    call()
+torch.cuda.synchronize()
+free1 = torch.cuda.mem_get_info()[0]
+assert free0 == free1, (free0, free1)
+want = float(x[torch.from_numpy(col[rp[3]:rp[4]]).long().to(dev)].double().sum())
+assert abs(float(out[3].double().sum()) - want) < 1e-4 * abs(want) + 1e-3
+print("unchanged", free0)
+''' % (root, os.path.join(root, "tests"))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "unchanged" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_static_scratch_variant_with_peers_and_a_publish_table(oracle):
+    """Two PEs emulated on one device (separate symmetric buffers, so remote rows go through the owner
+    lookup) and an extra destination for every output row: same bits as the regular entry point."""
+    dev = torch.device("cuda")
+    n, dim, G = 500, 16, 2
+    rp, col = random_graph(n, 20, seed=5, hubs=[(7, 20000), (400, 18000)])
+    x_np = np.random.default_rng(3).uniform(-0.02, 0.02, (n, dim)).astype(np.float32)
+    npp = (n + G - 1) // G
+    sym = [torch.from_numpy(np.ascontiguousarray(x_np[p * npp:(p + 1) * npp])).to(dev) for p in range(G)]
+    table = (C.c_void_p * G)(*[s.data_ptr() for s in sym])
+    want = oracle.sag_f64(x_np, rp, col)
+    lib = _lib.lib
+    for pe in range(G):
+        sh = drivers.Shard(rp, col, pe, G, device=dev)
+        outs, copies = [], []
+        for fn, extra in ((lib.mggb_sag_np_div, []), (lib.mggb_sag_np_div_static, [sh.edges])):
+            out = torch.zeros(sh.rows, dim, device=dev)
+            copy = torch.zeros(sh.rows, dim, device=dev)
+            pub = (C.c_void_p * 1)(copy.data_ptr())
+            _lib.check(fn(out.data_ptr(), table, G, sh.rp_l.data_ptr(), sh.ci_l.data_ptr(), sh.rp_r.data_ptr(), sh.ci_r.data_ptr(),
+                          sh.lb, sh.ub, *extra, dim, sh.node_per_pe, pe, 16, 4, 1, None, 0, pub, 1, None))
+            outs.append(out); copies.append(copy)
+        torch.cuda.synchronize()
+        assert torch.equal(outs[0], outs[1]) and torch.equal(copies[1], outs[1]) and torch.equal(copies[0], outs[0])
+        np.testing.assert_allclose(outs[1].cpu().numpy(), want[sh.lb:sh.ub], rtol=RTOL, atol=ATOL)
