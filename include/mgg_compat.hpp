@@ -9,6 +9,9 @@
 //   dense_param_new_beg / _hidden          include/layer_new.cuh:272-393
 //   softmax_new_param                      include/layer_new.cuh:59-103
 //   dense_beg_new_forward, dense_hidden_new_forward, softmax_new_forward   include/gnn_layer.cuh:36-52
+//   dense_param_beg / dense_param_hidden / softmax_param (the older structs, which OWN their output
+//       buffer; the dense ones own a SYMMETRIC one)                        include/layer_new.cuh:13-55, 210-269, 396-451
+//   dense_beg_forward, dense_hidden_forward, softmax_forward               include/gnn_layer.cuh:15-32
 //   mgg_symmetric_malloc                   stands in for nvshmem_malloc (src/mgg_np_div_mem.cu:139)
 //
 // Behaviour kept from the reference: the aggregation ADDS into `output`; both launchers synchronise
@@ -21,6 +24,12 @@
 // copy.  Here the process registers, per device, the table of all PEs' base pointers for a symmetric
 // buffer (mgg_register_symmetric); mgg_SAG_np_div looks its `input` argument up in that registry and
 // falls back to a one-PE table when it is not registered.
+// nvshmem_malloc is a collective: every PE calls it in the same order and the k-th call of each PE
+// names one symmetric buffer.  A program that drives several PEs from one process gets the same rule
+// from mgg_set_pe(pe, num_pes) + mgg_symmetric_malloc: the k-th allocation made while PE p is current
+// is PE p's part of symmetric buffer k, and as soon as all num_pes parts of a buffer exist their table
+// is registered for every one of them.  The older dense structs allocate their d_out this way, so a
+// driver that builds `new dense_param_beg(...)` once per PE needs no further call.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -95,17 +104,49 @@ inline bool lookup(const float* local, std::vector<const float*>& table) {
 
 }  // namespace mgg_compat
 
-// Allocates a zero-filled symmetric buffer on the current device.
-inline void* mgg_symmetric_malloc(size_t bytes) {
-    void* p = nullptr;
-    MGG_COMPAT_CHECK(mggb_sym_alloc(bytes, &p));
-    return p;
-}
-
 // Declares that `local` (this PE's buffer) is the entry `pe` of the given table of all PEs' buffers.
 inline void mgg_register_symmetric(const float* local, const float* const* table, int num_pes) {
     std::lock_guard<std::mutex> g(mgg_compat::registry_mutex());
     mgg_compat::registry()[local] = mgg_compat::SymEntry{std::vector<const float*>(table, table + num_pes)};
+}
+
+namespace mgg_compat {
+// The emulated symmetric heap of a one-process, several-PE program (see the header comment).
+struct Heap {
+    int pe = 0, num_pes = 1;
+    std::vector<std::vector<float*>> parts;   // parts[k][p] = PE p's part of symmetric buffer k (nullptr until allocated)
+    std::vector<int> next;                    // next[p] = index of PE p's next allocation
+};
+inline Heap& heap() { static Heap h; return h; }
+}  // namespace mgg_compat
+
+// Makes `pe` (of `num_pes`) the PE on whose behalf the following mgg_symmetric_malloc calls are made.
+// The caller selects the PE's device itself (cudaSetDevice), as the reference's drivers do.
+inline void mgg_set_pe(int pe, int num_pes) {
+    auto& h = mgg_compat::heap();
+    if (num_pes < 1 || num_pes > MGGB_MAX_PES || pe < 0 || pe >= num_pes) { printf("mgg_set_pe: bad pe %d of %d\n", pe, num_pes); exit(-1); }
+    if (h.num_pes != num_pes) { h.parts.clear(); h.next.assign(num_pes, 0); }
+    if ((int)h.next.size() != num_pes) h.next.assign(num_pes, 0);
+    h.pe = pe; h.num_pes = num_pes;
+}
+
+// Allocates a zero-filled symmetric buffer on the current device for the current PE (mgg_set_pe; one
+// PE by default).  Stands in for nvshmem_malloc.
+inline void* mgg_symmetric_malloc(size_t bytes) {
+    void* p = nullptr;
+    MGG_COMPAT_CHECK(mggb_sym_alloc(bytes, &p));
+    auto& h = mgg_compat::heap();
+    if ((int)h.next.size() != h.num_pes) h.next.assign(h.num_pes, 0);
+    const int k = h.next[h.pe]++;
+    if ((int)h.parts.size() <= k) h.parts.resize(k + 1, std::vector<float*>(h.num_pes, nullptr));
+    h.parts[k][h.pe] = (float*)p;
+    bool complete = true;
+    for (float* q : h.parts[k]) complete = complete && q != nullptr;
+    if (complete) {
+        std::vector<const float*> table(h.parts[k].begin(), h.parts[k].end());
+        for (float* q : h.parts[k]) mgg_register_symmetric(q, table.data(), h.num_pes);
+    }
+    return p;
 }
 
 // ---- aggregation ----------------------------------------------------------------------------------
@@ -217,4 +258,58 @@ inline void dense_hidden_softmax_new_forward(dense_param_new_hidden* dp, softmax
         return;
     dense_hidden_new_forward(dp, stream);
     softmax_new_forward(smx, stream);
+}
+
+// ---- the older structs and forwards (src/mgg_np_div_kernel.cu:127, src/mgg_np_div.cu:130-132) -------------
+// They differ from the _new ones in who owns the output: dense_param_beg / dense_param_hidden take only
+// their input and allocate d_out themselves, in symmetric memory (include/layer_new.cuh:250-252, :436),
+// zero-filled; softmax_param allocates a private d_out (:40-43).
+
+class dense_param_beg : public mgg_dense_param_base {
+public:
+    dense_param_beg(const char* name_in, float* d_in_ext, int numNodes_in, int dim1_in, int dim2_in)
+        : mgg_dense_param_base(name_in, d_in_ext, (float*)mgg_symmetric_malloc(sizeof(float) * (size_t)numNodes_in * dim2_in),
+                               numNodes_in, dim1_in, dim2_in) {}
+};
+
+class dense_param_hidden : public mgg_dense_param_base {
+public:
+    dense_param_hidden(const char* name_in, float* d_in_input, int numNodes_in, int dim1_in, int dim2_in)
+        : mgg_dense_param_base(name_in, d_in_input, (float*)mgg_symmetric_malloc(sizeof(float) * (size_t)numNodes_in * dim2_in),
+                               numNodes_in, dim1_in, dim2_in) {}
+};
+
+class softmax_param {
+public:
+    softmax_param(const char* name_in, float* d_in_input, int numNodes_in, int dim_in) {
+        strncpy(name, name_in, 7);
+        name[7] = '\0';
+        numNodes = numNodes_in; dim = dim_in; d_in = d_in_input;
+        alpha = 1.0f; beta = 0.0f;
+        if (cudaMalloc((void**)&d_out, sizeof(float) * (size_t)numNodes * dim) != cudaSuccess ||
+            cudaMemset(d_out, 0, sizeof(float) * (size_t)numNodes * dim) != cudaSuccess) {
+            printf("CUDA error @softmax_param: cannot allocate the %dx%d output\n", numNodes, dim);
+            exit(-1);
+        }
+    }
+    ~softmax_param() { cudaFree(d_out); }
+    softmax_param(const softmax_param&) = delete;
+    softmax_param& operator=(const softmax_param&) = delete;
+    int numNodes, dim;
+    float *d_out = nullptr, *d_in = nullptr;
+    float alpha, beta;
+    char name[8];
+};
+
+// d_out = d_in * d_W (the reference's calls, include/gnn_layer.cuh:22-32, multiply d_out in place and
+// never read d_in).  softmax_forward synchronises the device like the reference's (:19).
+inline void dense_beg_forward(dense_param_beg* dp, cudaStream_t stream = nullptr) {
+    MGG_COMPAT_CHECK(mggb_dense_forward(dp->d_out, dp->d_in, dp->d_W, dp->numNodes, dp->dim1, dp->dim2, nullptr, 0, nullptr, 0, stream));
+}
+inline void dense_hidden_forward(dense_param_hidden* dp, cudaStream_t stream = nullptr) {
+    MGG_COMPAT_CHECK(mggb_dense_forward(dp->d_out, dp->d_in, dp->d_W, dp->numNodes, dp->dim1, dp->dim2, nullptr, 0, nullptr, 0, stream));
+}
+inline void softmax_forward(softmax_param* smx, cudaStream_t stream = nullptr) {
+    MGG_COMPAT_CHECK(mggb_softmax_forward(smx->d_out, smx->d_in, smx->numNodes, smx->dim, stream));
+    cudaDeviceSynchronize();
 }

@@ -44,6 +44,12 @@ enum {
                                  By default a node with more than max(16384, 64*ps*dist*wpb) neighbors is passed,
                                  through a work list in library-owned device memory (allocated once per device
                                  and stream, on first use), to a second kernel that gives it a 16-warp block */
+    MGGB_AGG_STAGE_LOCAL = 8, /* also bring the rows of THIS PE's memory (the local list, or a local replica) into shared
+                                 memory with bulk copies before they are added up, as is always done for rows pulled
+                                 from peers' buffers.  For wide rows (dim >= 64), where registers limit how many bytes
+                                 a warp keeps in flight.  dim must be 4, 8, ..., 128 (a power of two); ignored otherwise */
+    MGGB_AGG_NO_STAGING = 16, /* never stage rows through shared memory: remote rows are loaded into registers like
+                                 local ones (the first design; kept for comparison) */
     MGGB_AGG_GROUP_PER_NODE = 4 /* dim 16 only (ignored otherwise): a node is aggregated by one group of 4 lanes,
                                  8 nodes per warp, instead of by warp_per_block warps; part_size and
                                  interleaved_dist then do not apply, and nodes above 1024 neighbors take the
@@ -279,6 +285,12 @@ int mggb_dense_forward(float* out, const float* x, const float* w,
                        int64_t n, int dim1, int dim2,
                        const float* row_scale, int flags,
                        float* const* publish_out, int num_publish, void* stream);
+
+/* Reads (and with reset != 0 clears) the status word of the aggregation kernels that stage rows through
+ * shared memory; synchronises the device.  0 = every launch so far ran to completion; 1 = a bounded wait
+ * for staged rows expired in some block, whose output row is then incomplete.  The reference has no
+ * counterpart (its blocking gets cannot time out). */
+int mggb_agg_device_status(int* status, int reset);
 
 /* Reads (and with reset != 0 clears) the status word of the tensor-core dense kernel on the current
  * device; synchronises the device.  0 = every launch so far ran to completion; 1..4 = a bounded wait

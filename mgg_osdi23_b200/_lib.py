@@ -12,7 +12,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libmggb200.so")
 
 OK, ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_PEER, ERR_IO = range(6)
-AGG_ACCUMULATE, AGG_NO_HUB_SPLIT, AGG_GROUP_PER_NODE = 1, 2, 4
+AGG_ACCUMULATE, AGG_NO_HUB_SPLIT, AGG_GROUP_PER_NODE, AGG_STAGE_LOCAL, AGG_NO_STAGING = 1, 2, 4, 8, 16
 DENSE_RELU, DENSE_TF32, DENSE_SIMT = 1, 2, 4
 MAX_PES = 16
 
@@ -74,6 +74,7 @@ SIGNATURES = {
     "mggb_hub_threshold": [_int, _int, _int, _int, _int, _pi64],
     "mggb_dense_forward": [_vp, _vp, _vp, _i64, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp],
     "mggb_dense_device_status": [C.POINTER(_int), _int],
+    "mggb_agg_device_status": [C.POINTER(_int), _int],
     "mggb_softmax_forward": [_vp, _vp, _i64, _int, _vp],
     "mggb_dense_softmax_forward": [_vp, _vp, _vp, _vp, _i64, _int, _int, _vp],
     "mggb_row_scale": [_vp, _vp, _vp, _i64, _int, _vp],

@@ -23,206 +23,22 @@
 #include <map>
 #include <mutex>
 #include <utility>
-#include "common.h"
+#include "aggregate_core.cuh"
 
 // Compile-time tuning, per row width (LPR = lanes that read one row).  Chosen by measurement on
 // B200: narrow rows (dim <= 16) are served mostly from L2 and want many resident warps, so registers
 // are capped (3 blocks of 512 threads -> 40 registers); wide rows stream from HBM, run one batch
 // per node on typical graphs, and do better without the cap.
 //   MGGB_AGG_MIN_BLOCKS_NARROW  second argument of __launch_bounds__(512, .) for LPR <= 4
-//   MGGB_AGG_MAX_ROUNDS         load rounds issued back to back (rows in flight = rounds * 32/LPR)
 #ifndef MGGB_AGG_MIN_BLOCKS_NARROW
 #define MGGB_AGG_MIN_BLOCKS_NARROW 3
 #endif
-#ifndef MGGB_AGG_MAX_ROUNDS
-#define MGGB_AGG_MAX_ROUNDS 4
-#endif
+
+namespace mggb {
+int aggregate_staged(const void* params, int wpb, int remote_mode, int stage, void* stream, bool* launched);
+}
 
 namespace {
-
-constexpr int HUB_WARPS = 16;        // warps of a hub row's block
-constexpr int HUB_BLOCKS_PER_SM = 2;  // blocks walking the hub list, per SM of the device
-constexpr int HUB_MIN_EDGES = 16384; // smallest neighbor count treated as a hub (a 4-warp block needs > 100 us for it)
-constexpr int HUB_CAP = 1 << 18;     // list entries: enough for every row above 16384 edges of a 2^32-edge shard
-
-struct AggParams {
-    float* out;
-    const float* peer[MGGB_MAX_PES];
-    const int32_t* rp_l;
-    const int32_t* ci_l;
-    const int32_t* rp_r;
-    const int32_t* ci_r;
-    const float* row_scale;
-    const int32_t* row_order;       // NULL, or the row each block takes (a permutation of 0..num_rows-1)
-    float* publish[MGGB_MAX_PES];   // extra destinations of every output row (peers' replicas)
-    int num_publish;
-    int32_t lb;
-    int32_t num_rows;
-    int32_t node_per_pe;
-    int dim;
-    int pe;
-    int num_pes;
-    int chunk;             // dist * ps: neighbors a warp takes per turn
-    unsigned long long div_magic;  // owner = (id * div_magic) >> div_shift
-    int div_shift;
-    int mode;              // 0 overwrite, 1 accumulate, 2 GIN combine
-    float self_scale;      // 1 + eps (GIN)
-    // Hub rows (more than hub_min_edges neighbors) are not aggregated by their one-node block: that
-    // block appends the row to hub_list and a second kernel gives each listed row a 16-warp block.
-    int* hub_count;        // number of rows appended (may exceed hub_cap); NULL = no hub handling
-    int* hub_list;
-    int hub_cap;
-    int hub_min_edges;
-};
-
-enum { MODE_OVERWRITE = 0, MODE_ACCUMULATE = 1, MODE_GIN = 2 };
-
-template <int VEC> struct Vec;
-template <> struct Vec<4> {
-    float4 v;
-    __device__ __forceinline__ void zero() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
-    __device__ __forceinline__ void load(const float* p) { v = __ldg(reinterpret_cast<const float4*>(p)); }
-    __device__ __forceinline__ void add(const Vec& o) { v.x += o.v.x; v.y += o.v.y; v.z += o.v.z; v.w += o.v.w; }
-    __device__ __forceinline__ void xor_reduce(int off) {
-        v.x += __shfl_xor_sync(0xffffffffu, v.x, off);
-        v.y += __shfl_xor_sync(0xffffffffu, v.y, off);
-        v.z += __shfl_xor_sync(0xffffffffu, v.z, off);
-        v.w += __shfl_xor_sync(0xffffffffu, v.w, off);
-    }
-    __device__ __forceinline__ void store_smem(float* p) const { *reinterpret_cast<float4*>(p) = v; }
-};
-template <> struct Vec<1> {
-    float v;
-    __device__ __forceinline__ void zero() { v = 0.f; }
-    __device__ __forceinline__ void load(const float* p) { v = __ldg(p); }
-    __device__ __forceinline__ void add(const Vec& o) { v += o.v; }
-    __device__ __forceinline__ void xor_reduce(int off) { v += __shfl_xor_sync(0xffffffffu, v, off); }
-    __device__ __forceinline__ void store_smem(float* p) const { *p = v; }
-};
-
-// Adds the rows of up to 32 neighbors (ids held one per lane in `my`, -1 = none) into acc.
-// FULL: all 32 ids are valid, so no per-row predicate is needed.
-template <int LPR, int VEC, bool REMOTE, bool FULL>
-__device__ __forceinline__ void gather_batch(Vec<VEC>& acc, const AggParams& P, const float* const* s_peer,
-                                             const char* lbase, unsigned row_bytes, int my, int cnt,
-                                             int g, int col, bool col_ok) {
-    constexpr int G = 32 / LPR;             // neighbor rows per load round
-    constexpr int U = LPR < MGGB_AGG_MAX_ROUNDS ? LPR : MGGB_AGG_MAX_ROUNDS;  // rounds issued back to back
-#pragma unroll 1
-    for (int r0 = 0; r0 < LPR; r0 += U) {
-        if (!FULL && r0 * G >= cnt) break;
-        Vec<VEC> v[U];
-        bool ok[U];
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int got = __shfl_sync(0xffffffffu, my, (r0 + u) * G + g);
-            ok[u] = col_ok && (FULL || got >= 0);
-            const int nid = FULL ? got : max(got, 0);   // absent lanes hold -1: keep every address and the owner index in range
-            const float* src;
-            if (REMOTE) {
-                const unsigned owner = (unsigned)(((unsigned long long)(unsigned)nid * P.div_magic) >> P.div_shift);
-                const int row = nid - (int)owner * P.node_per_pe;
-                src = s_peer[owner] + (long long)row * P.dim + col;
-            } else {
-                src = reinterpret_cast<const float*>(lbase + (long long)nid * row_bytes);
-            }
-            if (ok[u]) v[u].load(src);
-        }
-#pragma unroll
-        for (int u = 0; u < U; u++)
-            if (ok[u]) acc.add(v[u]);
-    }
-}
-
-// Gathers the edges [beg, end) of one neighbor list that belong to this warp and adds their rows
-// (columns [col, col+VEC) of each) into acc.  REMOTE selects the owner lookup.
-// The warp's share is walked as a sequence of batches of up to 32 ids: chunk q of the warp starts
-// at beg + (q*nwarps + warp)*chunk.  The ids of batch t+1 are requested before the rows of batch t
-// are gathered, so the id fetch (from HBM) overlaps the row fetch (mostly from L2).
-// WALK: 0 chunk by chunk; 1 the same with the next batch of ids requested early; 2 chunks shorter than a batch
-template <int LPR, int VEC, bool REMOTE, int WALK>
-__device__ __forceinline__ void gather_list(Vec<VEC>& acc, const AggParams& P, const float* const* s_peer,
-                                            const int32_t* __restrict__ ci, int beg, int end, const char* lbase,
-                                            int warp, int nwarps, int lane, int col, bool col_ok) {
-    const int g = lane / LPR;
-    const unsigned row_bytes = (unsigned)P.dim * 4u;
-    // directly addressed rows (REMOTE == false): address = lbase + id * row_bytes
-    // Edge positions fit 32 bits (a shard half has < 2^31 edges and the chunk is clamped to 2^24),
-    // so the walk uses unsigned arithmetic.
-    const unsigned uend = (unsigned)end, chunk = (unsigned)P.chunk;
-    const unsigned block_stride = chunk * (unsigned)nwarps;
-    if (WALK == 2) {
-        // Chunks shorter than a batch: the warp's edges, chunk after chunk, form one virtual sequence
-        // and every batch takes its next 32 of them (lane k's edge sits in the warp's chunk k / chunk),
-        // so that small part_size * interleaved_dist settings still gather 32 rows per batch.
-        for (unsigned k0 = 0;; k0 += 32) {
-            const unsigned k = k0 + (unsigned)lane, q = k / chunk;
-            const unsigned pos = (unsigned)beg + (q * (unsigned)nwarps + (unsigned)warp) * chunk + (k - q * chunk);
-            const unsigned valid = __ballot_sync(0xffffffffu, pos < uend);   // positions grow with k: a prefix of the lanes
-            if (valid == 0u) break;
-            const int cnt = __popc(valid);
-            const int my = pos < uend ? __ldcs(ci + pos) : -1;
-            if (cnt == 32) gather_batch<LPR, VEC, REMOTE, true>(acc, P, s_peer, lbase, row_bytes, my, cnt, g, col, col_ok);
-            else           gather_batch<LPR, VEC, REMOTE, false>(acc, P, s_peer, lbase, row_bytes, my, cnt, g, col, col_ok);
-            if (cnt < 32) break;
-        }
-        return;
-    }
-    unsigned cstart = (unsigned)beg + (unsigned)warp * chunk;         // start of the current chunk
-    if (cstart >= uend) return;
-    unsigned r = 0;                                                   // offset of the batch in its chunk
-    int cnt = (int)min(32u, min(chunk, uend - cstart));
-    int my = (lane < cnt) ? __ldcs(ci + cstart + lane) : -1;
-    while (true) {
-        unsigned ncs = cstart, nr = r + 32;
-        if (nr >= chunk || ncs + nr >= uend) { ncs += block_stride; nr = 0; }
-        const bool more = ncs < uend;
-        int ncnt = 0, nxt = -1;
-        if (more) {
-            ncnt = (int)min(32u, min(chunk - nr, uend - (ncs + nr)));
-            if (WALK == 1 && lane < ncnt) nxt = __ldcs(ci + ncs + nr + lane);
-        }
-        if (cnt == 32) gather_batch<LPR, VEC, REMOTE, true>(acc, P, s_peer, lbase, row_bytes, my, cnt, g, col, col_ok);
-        else           gather_batch<LPR, VEC, REMOTE, false>(acc, P, s_peer, lbase, row_bytes, my, cnt, g, col, col_ok);
-        if (!more) break;
-        if (WALK != 1 && lane < ncnt) nxt = __ldcs(ci + ncs + nr + lane);
-        cstart = ncs; r = nr; cnt = ncnt; my = nxt;
-    }
-}
-
-// REMOTE_MODE: 0 = one PE, no remote half; 1 = remote rows found through the owner lookup (peers'
-// buffers anywhere); 2 = the PEs' buffers are the consecutive slots of ONE matrix indexed by global id
-// (a local replica), so remote rows are addressed like local ones.
-//
-// Adds into acc this warp's share (warp `warp` of `nwarps`) of one node's neighbor rows, columns
-// [col, col+VEC).
-template <int LPR, int VEC, int REMOTE_MODE, int WALK>
-__device__ __forceinline__ void accumulate_row(Vec<VEC>& acc, const AggParams& P, const float* const* s_peer,
-                                               int lbeg, int lend, int rbeg, int rend,
-                                               int warp, int nwarps, int lane, int col, bool col_ok) {
-    const unsigned row_bytes = (unsigned)P.dim * 4u;
-    // the shard's first id, lb, is folded into the base of the local rows
-    const char* lbase = reinterpret_cast<const char*>(P.peer[P.pe] + col) - (long long)P.lb * row_bytes;
-    // The remote list's chunks are dealt to the warps starting where the local list's chunks
-    // stopped, so a short remote list does not always land on warp 0 (the reference restarts at
-    // warp 0, include/neighbor_utils.cuh:1432-1437; only the fp32 summation order differs).
-    const int rwarp = (warp + nwarps - (int)(((unsigned)(lend - lbeg) + P.chunk - 1) / P.chunk % nwarps)) % nwarps;
-    if (REMOTE_MODE == 1) {
-        gather_list<LPR, VEC, false, WALK>(acc, P, s_peer, P.ci_l, lbeg, lend, lbase, warp, nwarps, lane, col, col_ok);
-        if (rend > rbeg)
-            gather_list<LPR, VEC, true, WALK>(acc, P, s_peer, P.ci_r, rbeg, rend, nullptr, rwarp, nwarps, lane, col, col_ok);
-    } else {
-        // both halves are directly addressed: one copy of the gather code walks them in turn
-#pragma unroll 1
-        for (int half = 0; half < (REMOTE_MODE == 2 ? 2 : 1); half++) {
-            const int32_t* ci = half ? P.ci_r : P.ci_l;
-            const int beg = half ? rbeg : lbeg, end = half ? rend : lend;
-            const char* base = half ? reinterpret_cast<const char*>(P.peer[0] + col) : lbase;
-            if (end > beg)
-                gather_list<LPR, VEC, false, WALK>(acc, P, s_peer, ci, beg, end, base, half ? rwarp : warp, nwarps, lane, col, col_ok);
-        }
-    }
-}
 
 // Aggregates one node with all warps of the block and stores its output row.  s_part: nwarps * dim
 // floats of shared memory.  Ends with the block's threads past a __syncthreads() only on entry, so a
@@ -250,19 +66,7 @@ __device__ __forceinline__ void aggregate_row(const AggParams& P, const int row,
     }
     __syncthreads();
 
-    // Single writer per output element: sum the warps' partials in warp order, then the epilogue.
-    const long long obase = (long long)row * P.dim;
-    for (int c = threadIdx.x; c < P.dim; c += blockDim.x) {
-        float s = 0.f;
-        for (int w = 0; w < nwarps; w++) s += s_part[w * P.dim + c];
-        if (P.row_scale) s *= P.row_scale[row];
-        if (P.mode == MODE_GIN) s += P.self_scale * P.peer[P.pe][obase + c];
-        else if (P.mode == MODE_ACCUMULATE) s += P.out[obase + c];
-        P.out[obase + c] = s;
-        for (int k = 0; k < P.num_publish; k++) P.publish[k][obase + c] = s;
-    }
-    // No fence here: the pushed rows only have to be visible to kernels that peers launch after the
-    // next barrier, and a kernel's stores are complete, system-wide, when the kernel has finished.
+    store_row(P, row, s_part, nwarps);
 }
 
 // One block per node.  Dynamic shared memory: nwarps * dim floats (the warps' partial rows).
@@ -483,6 +287,50 @@ void make_divider(uint32_t d, unsigned long long* magic, int* shift) {
 
 template <int LPR, int VEC, bool EXACT>
 int launch_exact(const AggParams& P, int wpb, cudaStream_t st);
+
+// The wide-block kernel over whatever the first kernel appended to the hub list.
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE, int WALK>
+int launch_hub(const AggParams& P, cudaStream_t st) {
+    const size_t hub_smem = (size_t)HUB_WARPS * P.dim * sizeof(float);
+    if (hub_smem > 48 * 1024)
+        MGGB_CUDA(cudaFuncSetAttribute(sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE, WALK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem));
+    sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE, WALK><<<HUB_BLOCKS_PER_SM * mggb::sm_count(), HUB_WARPS * 32, hub_smem, st>>>(P);
+    MGGB_CUDA(cudaGetLastError());
+    return MGGB_OK;
+}
+
+// The same for the staged kernels (dim == 4 * LPR, 128-bit loads), by run-time row width and mode.
+template <int LPR>
+int launch_hub_mode(const AggParams& P, int remote_mode, cudaStream_t st) {
+    if (P.chunk < 32) {
+        if (remote_mode == 0) return launch_hub<LPR, 4, true, 0, 2>(P, st);
+        if (remote_mode == 1) return launch_hub<LPR, 4, true, 1, 2>(P, st);
+        return launch_hub<LPR, 4, true, 2, 2>(P, st);
+    }
+    if (remote_mode == 0) return launch_hub<LPR, 4, true, 0, 1>(P, st);
+    if (remote_mode == 1) return launch_hub<LPR, 4, true, 1, 1>(P, st);
+    return launch_hub<LPR, 4, true, 2, 1>(P, st);
+}
+
+int launch_hub_for(const AggParams& P, int remote_mode, cudaStream_t st) {
+    switch (P.dim / 4) {
+        case 1: return launch_hub_mode<1>(P, remote_mode, st);
+        case 2: return launch_hub_mode<2>(P, remote_mode, st);
+        case 4: return launch_hub_mode<4>(P, remote_mode, st);
+        case 8: return launch_hub_mode<8>(P, remote_mode, st);
+        case 16: return launch_hub_mode<16>(P, remote_mode, st);
+        default: return launch_hub_mode<32>(P, remote_mode, st);
+    }
+}
+
+// 0 = one PE; 2 = the PEs' buffers are consecutive slots of one matrix (a local replica); 1 = buffers anywhere.
+int remote_mode_of(const AggParams& P) {
+    if (P.num_pes == 1) return 0;
+    bool one_matrix = true;   // peer[p] == peer[0] + p * node_per_pe * dim for every p
+    for (int p = 1; p < P.num_pes; p++)
+        one_matrix = one_matrix && (P.peer[p] == P.peer[0] + (long long)p * P.node_per_pe * P.dim);
+    return one_matrix ? 2 : 1;
+}
 template <int LPR, int VEC, bool EXACT, int REMOTE_MODE>
 int launch_kernel(const AggParams& P, int wpb, cudaStream_t st);
 
@@ -495,11 +343,9 @@ int launch(const AggParams& P, int wpb, cudaStream_t st) {
 // A single PE has no remote half: that instantiation drops the owner lookup altogether.
 template <int LPR, int VEC, bool EXACT>
 int launch_exact(const AggParams& P, int wpb, cudaStream_t st) {
-    if (P.num_pes == 1) return launch_kernel<LPR, VEC, EXACT, 0>(P, wpb, st);
-    bool one_matrix = true;   // peer[p] == peer[0] + p * node_per_pe * dim for every p
-    for (int p = 1; p < P.num_pes; p++)
-        one_matrix = one_matrix && (P.peer[p] == P.peer[0] + (long long)p * P.node_per_pe * P.dim);
-    if (one_matrix) return launch_kernel<LPR, VEC, EXACT, 2>(P, wpb, st);
+    const int mode = remote_mode_of(P);
+    if (mode == 0) return launch_kernel<LPR, VEC, EXACT, 0>(P, wpb, st);
+    if (mode == 2) return launch_kernel<LPR, VEC, EXACT, 2>(P, wpb, st);
     return launch_kernel<LPR, VEC, EXACT, 1>(P, wpb, st);
 }
 
@@ -514,13 +360,7 @@ int launch_walk(const AggParams& P, int wpb, cudaStream_t st) {
     else
         sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE, WALK><<<P.num_rows, wpb * 32, smem, st>>>(P);
     MGGB_CUDA(cudaGetLastError());
-    if (P.hub_count != nullptr) {
-        const size_t hub_smem = (size_t)HUB_WARPS * P.dim * sizeof(float);
-        if (hub_smem > 48 * 1024)
-            MGGB_CUDA(cudaFuncSetAttribute(sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE, (WALK == 2 ? 2 : 1)>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem));
-        sag_hub_rows_kernel<LPR, VEC, EXACT, REMOTE_MODE, (WALK == 2 ? 2 : 1)><<<HUB_BLOCKS_PER_SM * mggb::sm_count(), HUB_WARPS * 32, hub_smem, st>>>(P);
-        MGGB_CUDA(cudaGetLastError());
-    }
+    if (P.hub_count != nullptr) return launch_hub<LPR, VEC, EXACT, REMOTE_MODE, (WALK == 2 ? 2 : 1)>(P, st);
     return MGGB_OK;
 }
 
@@ -554,14 +394,7 @@ int hub_scratch(cudaStream_t st, HubScratch* out) {
 
 // The group-per-node kernel, then the hub kernel for whatever it deferred.
 int launch_group_per_node(const AggParams& P, cudaStream_t st) {
-    int mode = 1;
-    if (P.num_pes == 1) mode = 0;
-    else {
-        bool one_matrix = true;
-        for (int p = 1; p < P.num_pes; p++)
-            one_matrix = one_matrix && (P.peer[p] == P.peer[0] + (long long)p * P.node_per_pe * P.dim);
-        if (one_matrix) mode = 2;
-    }
+    const int mode = remote_mode_of(P);
     if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, sizeof(int), st));
     const int grid = (P.num_rows + GROUP_ROWS_PER_BLOCK - 1) / GROUP_ROWS_PER_BLOCK;
     const size_t hub_smem = (size_t)HUB_WARPS * P.dim * sizeof(float);
@@ -649,6 +482,17 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
     }
     bool vec4 = (dim % 4 == 0);
     for (int p = 0; p < num_pes && vec4; p++) vec4 = ((uintptr_t)peer_input[p] % 16 == 0);
+    // Rows staged through shared memory by bulk copies: the remote list whenever remote rows are
+    // fetched from the owners' buffers (they are in flight for microseconds), every list when asked to.
+    const int remote_mode = remote_mode_of(P);
+    const int stage_bits = (remote_mode == 1 ? 1 : 0) | ((flags & MGGB_AGG_STAGE_LOCAL) ? 2 : 0);
+    if (vec4 && stage_bits != 0 && !(flags & MGGB_AGG_NO_STAGING)) {
+        if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, sizeof(int), st));
+        bool launched = false;
+        int rc = mggb::aggregate_staged(&P, wpb, remote_mode, stage_bits, st, &launched);
+        if (rc != MGGB_OK) return rc;
+        if (launched) return P.hub_count != nullptr ? launch_hub_for(P, remote_mode, st) : MGGB_OK;
+    }
     if (vec4) {
         const int q = dim / 4;
         if (q <= 1) return launch<1, 4>(P, wpb, st);

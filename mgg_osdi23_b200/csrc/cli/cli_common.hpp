@@ -12,6 +12,7 @@
 
 #include <algorithm>
 #include <chrono>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <ctime>
@@ -179,6 +180,40 @@ double time_loop(Cluster& c, int num_profiles, int warmup, F body) {
     for (auto& p : c.pes) printf("PE-%d, Total (ms): %.3f\n", p.pe, cpu_ms);
     printf("MPI time (ms) %.3f\n", wall_ms);
     return wall_ms;
+}
+
+// MGG_VALIDATE=1 in the environment: with the reference's all-ones inputs and weights every column of a
+// layer's output holds the same number per node, which the host can follow through the layers in double
+// precision from the graph alone.  Compares `width` columns of each PE's rows in d_buf with want[node]
+// (exactly when rel == 0, as the reference's check_equal does, include/utils.cuh:130-138) and prints the
+// reference's "Validation status" line.
+inline bool validate_enabled() { const char* v = getenv("MGG_VALIDATE"); return v && atoi(v); }
+
+inline bool validate_rows(Cluster& c, const std::vector<float*>& d_buf, int width, const std::vector<double>& want, double rel) {
+    bool ok = true;
+    for (auto& p : c.pes) {
+        c.use(p);
+        std::vector<float> h((size_t)p.rows() * width);
+        CLI_CUDA(cudaMemcpy(h.data(), d_buf[p.pe], h.size() * sizeof(float), cudaMemcpyDeviceToHost));
+        for (int r = 0; r < p.rows() && ok; r++) {
+            const double w = want[p.lb + r];
+            for (int d = 0; d < width; d++) {
+                const double got = h[(size_t)r * width + d];
+                const bool same = rel == 0.0 ? got == w : std::fabs(got - w) <= rel * std::fabs(w) + 1e-4;
+                if (!same) { printf("[PE %d row %d] ref: %.6g -- out: %.6g\n", p.pe, r, w, got); ok = false; break; }
+            }
+        }
+    }
+    printf("Validation status: %s\n", ok ? "True" : "False");
+    return ok;
+}
+
+// sum over the neighbors j of node i of v[j], for every node (host, double)
+inline std::vector<double> neighbor_sums(const Graph& g, const std::vector<double>& v) {
+    std::vector<double> out(g.n, 0.0);
+    for (int64_t i = 0; i < g.n; i++)
+        for (int64_t e = g.row_ptr[i]; e < g.row_ptr[i + 1]; e++) out[i] += v[g.col[e]];
+    return out;
 }
 
 inline void report(const Cluster& c, const Args& a, const Graph& g, double ms, int aggregations, int agg_dim) {

@@ -1,7 +1,9 @@
 // MGG_np_div_gin_mem: 5-layer GIN forward, 100 timed passes.
 // Same command line and stdout lines as the reference's src/mgg_np_div_gin_mem.cu; eps = 0.5 as
 // hard-coded there (:49).  Pass = dense(dim->hidden) | 5 x [GIN aggregate(hidden), dense] | softmax,
-// the last dense mapping hidden->outdim.  Publishing alternates between two symmetric buffers.
+// the last dense mapping hidden->outdim.  Publishing alternates between two symmetric buffers (every pass
+// ends with a barrier, so the next pass may reuse the first).  With MGG_VALIDATE=1 in the environment the
+// last aggregation's output is checked against a double-precision host evaluation of the same recurrence.
 #include "cli_common.hpp"
 
 int main(int argc, char* argv[]) {
@@ -46,6 +48,15 @@ int main(int argc, char* argv[]) {
         c.barrier();
     };
     double ms = cli::time_loop(c, 100, 10, pass);
+    if (cli::validate_enabled()) {
+        // all ones: every column of a layer is one number per node; follow it through the five layers
+        std::vector<double> h(g.n, (double)a.dim), z;
+        for (int k = 0; k < layers; k++) {
+            z = cli::neighbor_sums(g, h);
+            for (int64_t i = 0; i < g.n; i++) { z[i] += (1.0 + (double)eps) * h[i]; h[i] = (double)a.hiddenSize * z[i]; }
+        }
+        cli::validate_rows(c, d_agg, a.hiddenSize, z, 1e-5);
+    }
     cli::report(c, a, g, ms, layers, a.hiddenSize);
     return 0;
 }

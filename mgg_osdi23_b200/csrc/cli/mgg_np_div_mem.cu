@@ -3,7 +3,8 @@
 //   MGG_np_div_mem beg_file csr_file weight_file num_GPUs partSize warpPerBlock interleaved_dist dim hidden outdim
 // Pass = dense(dim->hidden) | aggregate(hidden) | aggregate(hidden), dense(hidden->outdim), softmax;
 // "|" marks where every PE waits for its peers.  Inputs and weights are all 1.0 as in the reference
-// (:128, include/layer_new.cuh:307).
+// (:128, include/layer_new.cuh:307).  With MGG_VALIDATE=1 in the environment the second aggregation's
+// output is checked against the host's count (dim x the sum of the neighbors' degrees).
 #include "cli_common.hpp"
 
 int main(int argc, char* argv[]) {
@@ -46,6 +47,14 @@ int main(int argc, char* argv[]) {
         c.barrier();
     };
     double ms = cli::time_loop(c, 100, 10, pass);
+    if (cli::validate_enabled()) {
+        // all ones: X*W1 = dim everywhere, first aggregation = degree * dim, second = dim * sum of the neighbors' degrees
+        std::vector<double> h(g.n, (double)a.dim);
+        auto z2 = cli::neighbor_sums(g, cli::neighbor_sums(g, h));
+        bool exact = true;
+        for (double v : z2) exact = exact && v < 16777216.0;      // integers below 2^24 are exact in fp32
+        cli::validate_rows(c, d_agg, a.hiddenSize, z2, exact ? 0.0 : 1e-5);
+    }
     cli::report(c, a, g, ms, 2, a.hiddenSize);
     return 0;
 }

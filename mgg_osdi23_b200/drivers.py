@@ -309,7 +309,12 @@ class _Forward:
 
         The first layer's dense product is row-local, so the upload is cut into ``chunks`` row blocks
         on a copy stream and each block is multiplied as soon as it has arrived: the product (and the
-        publication to peers) hides behind the PCIe transfer."""
+        publication to peers) hides behind the PCIe transfer.  ``marks``: when a list, three CUDA events of
+        this call (start, forward done, probabilities copied out) are appended to it as one list."""
+        ev = None
+        if marks is not None:
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            ev[0].record()
         first = getattr(self, "first_dense", None)
         rows = self.shard.rows
         if first is None or chunks <= 1 or rows < 4096 * chunks:

@@ -79,13 +79,15 @@ def _csr_from_keys(keys: torch.Tensor, n: int, meta: dict) -> Graph:
     return Graph(n, row_ptr, col, meta)
 
 
-def _finish(src: torch.Tensor, dst: torch.Tensor, n: int, symmetric: bool, self_loops: bool) -> torch.Tensor:
+def _finish(src: torch.Tensor, dst: torch.Tensor, n: int, symmetric: bool, self_loops: bool, dedup: bool = True) -> torch.Tensor:
     keys = src * n + dst
     if symmetric:
         keys = torch.cat([keys, dst * n + src])
     if self_loops:
         ids = torch.arange(n, dtype=torch.int64, device=src.device)
         keys = torch.cat([keys, ids * n + ids])
+    if not dedup:       # a multigraph: every sampled pair is an edge, repeated pairs are repeated neighbors
+        return torch.sort(keys).values
     return torch.unique(keys, sorted=True)
 
 
@@ -133,10 +135,11 @@ def rmat_edges(scale: int, n_edges: int, a: float, b: float, c: float, seed: int
 
 
 def rmat_graph(scale: int, n_edges: int, a=0.57, b=0.19, c=0.19, seed=0, symmetric=True, self_loops=True,
-               num_nodes: int | None = None, device="cpu", relabel: bool = False) -> Graph:
+               num_nodes: int | None = None, device="cpu", relabel: bool = False, dedup: bool = True) -> Graph:
     """R-MAT graph.  With num_nodes < 2^scale, sampled pairs with an endpoint >= num_nodes are dropped
     and sampling continues until n_edges pairs are kept (before symmetrisation / deduplication).
-    relabel=True renumbers the nodes with ``relabel_ids`` (same graph up to isomorphism)."""
+    relabel=True renumbers the nodes with ``relabel_ids`` (same graph up to isomorphism).
+    dedup=False keeps repeated pairs (the edge list as an R-MAT generator emits it: a multigraph)."""
     n = num_nodes if num_nodes is not None else (1 << scale)
     if n == (1 << scale):
         src, dst = rmat_edges(scale, n_edges, a, b, c, seed, device)
@@ -154,9 +157,11 @@ def rmat_graph(scale: int, n_edges: int, a=0.57, b=0.19, c=0.19, seed=0, symmetr
         src, dst = torch.cat(kept_s), torch.cat(kept_d)
     if relabel:
         src, dst = relabel_ids(src, n, seed), relabel_ids(dst, n, seed)
-    keys = _finish(src, dst, n, symmetric, self_loops)
+    keys = _finish(src, dst, n, symmetric, self_loops, dedup)
     meta = dict(kind="rmat", scale=scale, sampled_edges=n_edges, a=a, b=b, c=c, d=round(1 - a - b - c, 6),
                 seed=seed, symmetric=symmetric, self_loops=self_loops, relabelled=relabel)
+    if not dedup:
+        meta["repeated_pairs_kept"] = True
     return _csr_from_keys(keys, n, meta)
 
 
@@ -249,12 +254,18 @@ def config3_graph(device="cpu", seed=0, scale: float = 1.0) -> Graph:
 
 
 def config4_graph(device="cpu", seed=0, scale_shift: int = 0) -> Graph:
-    """enwiki-shaped skewed directed R-MAT (a=.6 b=.15 c=.15 d=.1): 4,206,785 nodes, ~101.3 M edges, not
-    symmetrised, node ids relabelled pseudo-randomly.  scale_shift > 0 halves ids and edges that many
-    times for tests."""
+    """enwiki-shaped skewed directed R-MAT (a=.6 b=.15 c=.15 d=.1): 4,206,785 nodes, 101.3 M edges, not
+    symmetrised, node ids relabelled pseudo-randomly, largest neighbor list above 10^5 (checked at full
+    size).  The 101.3 M sampled pairs are all kept, repeats included, as an R-MAT generator emits them:
+    with repeats removed these parameters give 96.5 M edges and a largest list of 72 K, short of the
+    shape's defining skew.  scale_shift > 0 halves ids and edges that many times for tests."""
     n = 4_206_785 >> scale_shift
-    return rmat_graph(23 - scale_shift, 101_300_000 >> scale_shift, 0.6, 0.15, 0.15, seed=seed,
-                      symmetric=False, self_loops=False, num_nodes=n, device=device, relabel=True)
+    g = rmat_graph(23 - scale_shift, 101_300_000 >> scale_shift, 0.6, 0.15, 0.15, seed=seed,
+                   symmetric=False, self_loops=False, num_nodes=n, device=device, relabel=True, dedup=False)
+    g.meta["max_in_degree"] = int((g.row_ptr[1:] - g.row_ptr[:-1]).max())
+    if scale_shift == 0 and g.meta["max_in_degree"] <= 100_000:
+        raise AssertionError(f"config 4 needs a node with more than 10^5 in-edges, the generator gave {g.meta['max_in_degree']}")
+    return g
 
 
 def rmat_shard(scale: int, n_pairs: int, num_nodes: int, lb: int, ub: int, a=0.57, b=0.19, c=0.19, seed=0,

@@ -49,12 +49,37 @@ def test_single_aggregation_driver_validates(graph_files, num_gpus):
     assert info["edges"] == g.num_edges and info["num_GPUs"] == num_gpus and info["ps"] == 16
 
 
-def test_gcn_and_gin_drivers_run(graph_files):
+@pytest.mark.parametrize("num_gpus", [1, 2, 3])
+def test_gcn_and_gin_drivers_validate(graph_files, num_gpus):
+    """All-ones inputs and weights, as in the reference: the host follows the per-node value through the
+    layers and the executables compare their last aggregation with it (MGG_VALIDATE=1)."""
     files, g = graph_files
-    out = _run(_exe("MGG_np_div_mem"), files, 2, 16, 4, 1, 32, 16, 8)
+    out = _run(_exe("MGG_np_div_mem"), files, num_gpus, 16, 4, 1, 32, 16, 8, env={"MGG_VALIDATE": "1"})
     assert re.search(r"MPI time \(ms\) \d+\.\d+", out) and out.startswith("Graph File: ")
-    out = _run(_exe("MGG_np_div_gin_mem"), files, 2, 8, 2, 2, 32, 64, 8)
+    assert "Validation status: True" in out
+    out = _run(_exe("MGG_np_div_gin_mem"), files, num_gpus, 8, 2, 2, 32, 64, 8, env={"MGG_VALIDATE": "1"})
     assert re.search(r"MPI time \(ms\) \d+\.\d+", out)
+    assert "Validation status: True" in out
+
+
+def test_cpp_shim_device_half_through_the_symmetric_registry(tmp_path):
+    """A driver written like the reference's src/mgg_np_div_kernel.cu main(): the older structs
+    (dense_param_beg owning a symmetric d_out, dense_param_hidden, softmax_param) and mgg_SAG_np_div /
+    mgg_GIN_np_div with the reference's exact parameter lists, two PEs, peers found through the shim's
+    registry; results checked exactly against degrees inside the program."""
+    import shutil
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not found")
+    exe = str(tmp_path / "compat_device_check")
+    pkg = os.path.join(ROOT, "mgg_osdi23_b200")
+    cmd = [nvcc, "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a", "-I", os.path.join(ROOT, "include"),
+           os.path.join(ROOT, "tests", "cpp", "compat_device_check.cu"), "-o", exe, "-L", pkg, "-lmggb200",
+           "-Xlinker", "-rpath", "-Xlinker", pkg]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "compat device check: ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
 def test_usage_error():

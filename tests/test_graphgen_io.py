@@ -9,13 +9,16 @@ import mgg_osdi23_b200 as mgg
 from mgg_osdi23_b200 import graphgen as gg, graphio
 
 
-def _check_csr(g, symmetric):
+def _check_csr(g, symmetric, repeats=False):
     rp, col = g.row_ptr.numpy(), g.col_idx.numpy()
     assert rp[0] == 0 and rp[-1] == col.size and np.all(np.diff(rp) >= 0)
     assert col.min() >= 0 and col.max() < g.num_nodes
     rows = np.repeat(np.arange(g.num_nodes), np.diff(rp))
     keys = rows.astype(np.int64) * g.num_nodes + col
-    assert np.all(np.diff(keys) > 0)                 # sorted, no duplicates
+    if repeats:
+        assert np.all(np.diff(keys) >= 0) and np.any(np.diff(keys) == 0)   # sorted; an edge list with repeated pairs
+    else:
+        assert np.all(np.diff(keys) > 0)             # sorted, no duplicates
     if symmetric:
         rev = np.sort(col.astype(np.int64) * g.num_nodes + rows)
         assert np.array_equal(rev, keys)
@@ -43,8 +46,11 @@ def test_chung_lu_communities():
 
 def test_directed_rmat_subset():
     g = gg.config4_graph(scale_shift=8)
-    _check_csr(g, False)
+    _check_csr(g, False, repeats=True)
     assert g.num_nodes == 4_206_785 >> 8
+    # every sampled pair is an edge (the shape's edge count and its skew both count repeated pairs)
+    assert g.num_edges == 101_300_000 >> 8 and g.meta["repeated_pairs_kept"]
+    assert g.meta["max_in_degree"] == int(np.diff(g.row_ptr.numpy()).max()) > 50 * g.num_edges // g.num_nodes
 
 
 def test_features_are_shard_independent():
