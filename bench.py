@@ -64,9 +64,9 @@ def parse_args():
     ap.add_argument("--barrier", default="flag", choices=["flag", "nccl"],
                     help="what separates the stages of a pass at N > 1: 'flag' = epoch flags in peer memory (one small kernel), "
                          "'nccl' = a one-element all-reduce")
-    ap.add_argument("--staging", default="auto", choices=["auto", "local", "none"],
-                    help="rows staged through shared memory by bulk copies: 'auto' = rows pulled from peers only, 'local' = this "
-                         "GPU's rows as well (MGGB_AGG_STAGE_LOCAL), 'none' = never (MGGB_AGG_NO_STAGING)")
+    ap.add_argument("--staging", default="none", choices=["none", "rows"],
+                    help="'rows' = neighbor rows staged through shared memory by bulk copies (MGGB_AGG_STAGE_ROWS: the rows pulled "
+                         "from peers when there are any, every row otherwise); 'none' = rows loaded into registers (the default, faster)")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of the outputs with the oracle")
     ap.add_argument("--cpu-threads", type=int, default=0,
                     help="host threads of the CPU arm (--impl reference and cpu_baseline); 0 = all the cores this process may use, "
@@ -491,7 +491,7 @@ def run_ours(args, rank, world, local_rank):
     model_kind, din, hid, dout, dknobs, desc = CONFIGS[args.config]
     group_kernel = (args.group_per_node or args.config in ("cfg4", "cfg5")) and not args.no_group_per_node
     knobs = drivers.Knobs(args.ps or dknobs[0], args.wpb or dknobs[1], args.dist or dknobs[2],
-                          flags=(4 if group_kernel else 0) | {"auto": 0, "local": 8, "none": 16}[args.staging])
+                          flags=(4 if group_kernel else 0) | {"none": 0, "rows": 8}[args.staging])
 
     def sync_all():
         torch.cuda.synchronize()

@@ -44,12 +44,15 @@ enum {
                                  By default a node with more than max(16384, 64*ps*dist*wpb) neighbors is passed,
                                  through a work list in library-owned device memory (allocated once per device
                                  and stream, on first use), to a second kernel that gives it a 16-warp block */
-    MGGB_AGG_STAGE_LOCAL = 8, /* also bring the rows of THIS PE's memory (the local list, or a local replica) into shared
-                                 memory with bulk copies before they are added up, as is always done for rows pulled
-                                 from peers' buffers.  For wide rows (dim >= 64), where registers limit how many bytes
-                                 a warp keeps in flight.  dim must be 4, 8, ..., 128 (a power of two); ignored otherwise */
-    MGGB_AGG_NO_STAGING = 16, /* never stage rows through shared memory: remote rows are loaded into registers like
-                                 local ones (the first design; kept for comparison) */
+    MGGB_AGG_STAGE_ROWS = 8, /* bring neighbor rows into shared memory with bulk copies (one cp.async.bulk per row into a
+                                per-warp ring, completion on an mbarrier) and add them up from there, instead of
+                                loading them into registers: the rows pulled from peers' buffers when there are any
+                                (their copies are issued before the local list is walked), every row otherwise.
+                                dim must be 4, 8, ..., 128 (a power of two); ignored otherwise.  Measured on B200 it
+                                does not pay: remote 64-byte rows arrive at the same 530 GB/s either way (the link's
+                                rate for reads of that size), and local rows come 3.7x slower than through the
+                                load/store unit, because an SM's copy engine keeps only about a hundred row copies
+                                in flight.  Kept as an option for other row widths and machines */
     MGGB_AGG_GROUP_PER_NODE = 4 /* dim 16 only (ignored otherwise): a node is aggregated by one group of 4 lanes,
                                  8 nodes per warp, instead of by warp_per_block warps; part_size and
                                  interleaved_dist then do not apply, and nodes above 1024 neighbors take the

@@ -68,7 +68,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
             raise RuntimeError(f"nvcc failed compiling {src}")
     if not results and not _stale(LIB_PATH, objs):
         return LIB_PATH
-    r = subprocess.run([_nvcc(), "-shared"] + objs + ["-o", LIB_PATH, "-lgomp", "-lcuda"], capture_output=True, text=True)
+    r = subprocess.run([_nvcc(), "-shared"] + objs + ["-o", LIB_PATH, "-lgomp"], capture_output=True, text=True)
     if verbose or r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)
     if r.returncode != 0:

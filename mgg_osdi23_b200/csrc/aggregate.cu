@@ -482,14 +482,13 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
     }
     bool vec4 = (dim % 4 == 0);
     for (int p = 0; p < num_pes && vec4; p++) vec4 = ((uintptr_t)peer_input[p] % 16 == 0);
-    // Rows staged through shared memory by bulk copies: the remote list whenever remote rows are
-    // fetched from the owners' buffers (they are in flight for microseconds), every list when asked to.
+    // On request, rows staged through shared memory by bulk copies: the remote list when remote rows are
+    // fetched from the owners' buffers, every list otherwise.
     const int remote_mode = remote_mode_of(P);
-    const int stage_bits = (remote_mode == 1 ? 1 : 0) | ((flags & MGGB_AGG_STAGE_LOCAL) ? 2 : 0);
-    if (vec4 && stage_bits != 0 && !(flags & MGGB_AGG_NO_STAGING)) {
+    if (vec4 && (flags & MGGB_AGG_STAGE_ROWS)) {
         if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, sizeof(int), st));
         bool launched = false;
-        int rc = mggb::aggregate_staged(&P, wpb, remote_mode, stage_bits, st, &launched);
+        int rc = mggb::aggregate_staged(&P, wpb, remote_mode, remote_mode == 1 ? 1 : 2, st, &launched);
         if (rc != MGGB_OK) return rc;
         if (launched) return P.hub_count != nullptr ? launch_hub_for(P, remote_mode, st) : MGGB_OK;
     }

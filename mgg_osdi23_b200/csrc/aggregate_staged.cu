@@ -6,14 +6,19 @@
 // for one whole row (cp.async.bulk global -> shared, completion counted on an mbarrier), 32 rows per
 // batch, into a per-warp ring of stages.  The warp then adds the rows up from shared memory.
 //
-// Why.  A row gathered through the load/store unit holds registers and an L1 miss slot for as long
-// as it is in flight, which caps what an SM keeps outstanding; rows that come over NVLink from a
-// peer's memory (the reference's blocking nvshmemx_float_get_warp, include/neighbor_utils.cuh:1445)
-// are in flight for microseconds.  Bulk copies are queued in the copy engine, cost the warp nothing
-// while they fly, and land in shared memory, where eight 64-byte rows are read in four wavefronts
-// instead of the eight an L1 line gather needs.  The copies for the first stages of the REMOTE list
-// are issued before the warp walks its LOCAL list, so remote latency hides behind the local gather;
-// later remote batches are double-buffered (stage k+1 in flight while stage k is added up).
+// Why it exists.  A row gathered through the load/store unit holds registers and an L1 miss slot for
+// as long as it is in flight; rows that come over NVLink from a peer's memory (the reference's
+// blocking nvshmemx_float_get_warp, include/neighbor_utils.cuh:1445) are in flight for microseconds.
+// Bulk copies are queued in the copy engine, cost the warp nothing while they fly, and land in
+// shared memory.  The copies for the first stages of the REMOTE list are issued before the warp
+// walks its LOCAL list, so remote latency hides behind the local gather; later remote batches are
+// double-buffered (stage k+1 in flight while stage k is added up).
+// What measuring it on B200 showed (MGGB_AGG_STAGE_ROWS selects it; it is NOT the default): 64-byte
+// rows pulled from a peer arrive at 530 GB/s per GPU with either path (the link's rate for reads of
+// that size; 670 GB/s from 128-byte rows up), so for remote rows it is a tie; for rows of this GPU's
+// own memory it is 3.7x slower than register loads (2.5 ms against 0.68 ms on 115 M 64-byte rows that
+// sit in L2; 15.7 ms against 4.8 ms on 124 M 256-byte rows from HBM): an SM's copy engine keeps only
+// about a hundred row-sized copies in flight, far fewer bytes than its warps' loads do.
 //
 // STAGE bit 0: the remote list (owner lookup, REMOTE_MODE 1) is staged; bit 1: the directly
 // addressed lists are staged too (wide rows, where registers limit the bytes in flight).
@@ -249,8 +254,8 @@ int aggregate_staged(const void* params, int wpb, int remote_mode, int stage, vo
     *launched = false;
     const int q = P.dim / 4;
     if (P.dim % 4 != 0 || q < 1 || q > 32 || (q & (q - 1)) != 0 || wpb > MAX_WARPS) return MGGB_OK;
-    if (remote_mode == 1) stage |= 1;              // the owner-lookup list is what staging is for
-    else stage = 2;
+    if (remote_mode != 1) stage = 2;               // no owner-lookup list: the directly addressed lists are all there is
+    else if ((stage & 1) == 0) stage |= 1;
     const size_t row_bytes = (size_t)P.dim * 4;
     const size_t part = ((size_t)wpb * row_bytes + 127) & ~(size_t)127;
     // Ring depth: as many stages as fit a per-block budget that still lets several blocks share an SM.

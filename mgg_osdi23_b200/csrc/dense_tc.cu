@@ -10,12 +10,18 @@
 // exactly into hi + lo with both parts representable in TF32 (hi = top bits, lo = next bits; what is
 // dropped is below 2^-21 of the value) and all four partial products hi*hi, hi*lo, lo*hi, lo*lo are
 // accumulated in fp32 in tensor memory, so the result matches an fp32 GEMM to about 1e-6 relative.
+// MGGB_DENSE_TF32 keeps only hi * hi: one pass, operands truncated to 10 mantissa bits (about 1e-3).
 //
 // One persistent CTA per SM, 13 warps, no clusters:
-//   warps 0-3  loaders: cp.async a [128 rows x 32 floats] slab of x into a 4-stage ring in the
-//              128-byte-swizzled K-major layout the tensor core reads; warps 4-7 split what landed
-//              into hi and lo slabs.  Plain cp.async rather than TMA because Reddit-shaped rows
-//              (602 floats = 2408 bytes) break TMA's 16-byte stride rule; 8- or 16-byte pieces.
+//   bringing x in, a [128 rows x 32 floats] slab at a time, into a ring in the 128-byte-swizzled
+//   K-major layout the tensor core reads, split into hi and lo slabs:
+//     rows whose stride is a multiple of 16 bytes (dim1 % 4 == 0): TMA.  One thread (warp 13) issues
+//              one cp.async.bulk.tensor.2d per slab (SWIZZLE_128B tensor map over x, no multicast,
+//              this GPU's memory only; rows and columns past the matrix are zero-filled by the copy
+//              engine); warps 0-7 split the landed slab in place.
+//     other even dim1 (Reddit-shaped rows: 602 floats = 2408 bytes, which no tensor map takes):
+//              warps 0-7 load 8-byte pieces into registers, several slabs ahead, and write hi/lo.
+//     (MGGB_DENSE_CP_ASYNC at build time: the earlier cp.async loader / splitter pair for aligned rows.)
 //   warp 12    allocates tensor memory; one lane issues tcgen05.mma (M=128, N=pad16(M), K=8 per
 //              instruction, 4 k-steps x 4 partial products per slab) and commits to mbarriers.
 //   warps 8-11 epilogue: tcgen05.ld the 128 x N accumulator (double-buffered in tensor memory), apply
@@ -23,7 +29,9 @@
 // w is split and laid out in shared memory once per CTA.  Every wait on an mbarrier is bounded: on
 // expiry the CTA raises a status word the host can read (mggb_dense_device_status), drains its
 // copies, frees its tensor memory and returns.
+#include <cuda.h>
 #include <algorithm>
+#include <cstring>
 #include "common.h"
 
 namespace mggb {
@@ -47,6 +55,7 @@ constexpr int MAX_STAGES = MGGB_DENSE_STAGES;
 // Which warps bring x in: register-staged producers for 8-byte pieces, the cp.async loader/splitter
 // pair for 16-byte pieces (each measured faster on its shapes, see producer_role).
 template <int G> struct UseProducer { static constexpr bool value = (G == 8); };
+constexpr int TMA_THREADS = 2 * LOADERS + 128 + 32 + 32;   // the TMA path adds warp 13, the copy issuer
 // Consecutive K slabs a loader fetches per row visit: 2 for 8-byte pieces (a warp's copy instruction
 // then covers 256 contiguous bytes of a row pair), 1 for 16-byte pieces.  Measured on B200; the copy
 // rate is bound by the number of cp.async instructions an SM keeps in flight (about 40).
@@ -68,6 +77,7 @@ struct TcParams {
     const float* row_scale;
     long long n;
     int K, M, Npad, nchunks, stages, relu, stage_out;
+    int tf32;        // 1: one TF32 pass (hi * hi only); the lo halves are neither written nor multiplied
     int vec_store;   // 1: dim2 % 4 == 0 and out and every publish destination are 16-byte aligned (128-bit stores)
     unsigned tmem_cols;
     Publish pub;
@@ -251,13 +261,18 @@ __device__ void splitter_role(const TcParams& P, unsigned char* ring, uint32_t l
 }
 
 // Register-staged producers, used for 8-byte pieces (rows that are only 8-byte aligned, e.g. 602
-// floats); 16-byte pieces use the cp.async loader/splitter pair above.  All eight producer warps load their pieces of slab c+1 into registers with
-// streaming loads, then split slab c (already in registers) into hi/lo straight into its ring stage
-// and hand it to the tensor core.  Measured on B200: an SM keeps only about 40 cp.async instructions
-// in flight (10-20 KB), while plain loads are limited by registers: 256 threads x 2 slabs x 64 bytes
-// = 32 KB in flight per SM here.  Measured (232,965 x 602 -> 16): 0.30 ms against 0.34 ms with
-// cp.async; for 16-byte pieces (2,449,029 x 64 -> 64) cp.async wins, 0.32 ms against 0.37 ms.
+// floats); 16-byte pieces use the cp.async loader/splitter pair above.  All eight producer warps load
+// their pieces of the next slabs into registers with streaming loads, then split the oldest slab
+// (already in registers) into hi/lo straight into its ring stage and hand it to the tensor core.
+// The slabs rotate through PIPE register buffers with the loop unrolled PIPE times, so no buffer is
+// ever copied into another: a register move would wait for its load, and with it every later load
+// would be issued only after the earlier one had returned.  PIPE - 1 slabs (16 KiB each) are in
+// flight per SM while one is being split.
 constexpr int PRODUCERS = 2 * LOADERS;
+#ifndef MGGB_DENSE_PIPE
+#define MGGB_DENSE_PIPE 4
+#endif
+constexpr int PIPE = MGGB_DENSE_PIPE;
 
 template <int G> struct PVec;
 template <> struct PVec<16> { using T = float4; };
@@ -282,6 +297,7 @@ __device__ void producer_role(const TcParams& P, unsigned char* ring, uint32_t f
     const size_t src_step = (size_t)ROW_STEP * P.K;
 
     auto load_slab = [&](long long c, V* buf) {
+        if (c >= slabs) return;
         const long long tile = first_tile + (c / P.nchunks) * tile_step;
         const int kc = (int)(c % P.nchunks);
         const long long row0 = tile * TILE_M + r0;
@@ -291,25 +307,20 @@ __device__ void producer_role(const TcParams& P, unsigned char* ring, uint32_t f
         const bool rows_full = tile * TILE_M + TILE_M <= P.n;
 #pragma unroll
         for (int i = 0; i < COUNT; i++) {
-            V v;
-            if (G == 16) v = V{};
+            V v = V{};
             if (k_ok && (rows_full || row0 + i * ROW_STEP < P.n)) v = __ldcs(reinterpret_cast<const V*>(src0 + i * src_step));
-            else v = V{};
             buf[i] = v;
         }
     };
-
-    V cur[COUNT], nxt[COUNT];
-    if (slabs > 0) load_slab(0, cur);
-    for (long long c = 0; c < slabs; c++) {
-        if (c + 1 < slabs) load_slab(c + 1, nxt);          // in flight while this slab is split and stored
+    // splits the slab held in buf into hi/lo in its ring stage and hands it to the tensor core
+    auto store_slab = [&](long long c, const V* buf) -> bool {
         const int s = (int)(c % S);
         const long long use = c / S;
-        if (use >= 1 && !mbar_wait(empty0 + 8 * s, (unsigned)((use - 1) & 1), abort_flag, 2)) return;
+        if (use >= 1 && !mbar_wait(empty0 + 8 * s, (unsigned)((use - 1) & 1), abort_flag, 2)) return false;
         unsigned char* stage = ring + (size_t)s * STAGE_BYTES;
 #pragma unroll
         for (int i = 0; i < COUNT; i++) {
-            const float* v = reinterpret_cast<const float*>(&cur[i]);
+            const float* v = reinterpret_cast<const float*>(&buf[i]);
             float h[G / 4], l[G / 4];
 #pragma unroll
             for (int e = 0; e < G / 4; e++) {
@@ -317,12 +328,79 @@ __device__ void producer_role(const TcParams& P, unsigned char* ring, uint32_t f
                 l[e] = __uint_as_float(__float_as_uint(v[e] - h[e]) & TF32_MASK);
             }
             *reinterpret_cast<V*>(stage + off0 + i * SMEM_STEP) = *reinterpret_cast<V*>(h);
-            *reinterpret_cast<V*>(stage + SLAB_BYTES + off0 + i * SMEM_STEP) = *reinterpret_cast<V*>(l);
+            if (!P.tf32) *reinterpret_cast<V*>(stage + SLAB_BYTES + off0 + i * SMEM_STEP) = *reinterpret_cast<V*>(l);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
         mbar_arrive(full0 + 8 * s);
+        return true;
+    };
+
+    V buf[PIPE][COUNT];
 #pragma unroll
-        for (int i = 0; i < COUNT; i++) cur[i] = nxt[i];
+    for (int j = 0; j < PIPE - 1; j++) load_slab(j, buf[j]);
+    for (long long c0 = 0; c0 < slabs; c0 += PIPE) {
+#pragma unroll
+        for (int j = 0; j < PIPE; j++) {
+            const long long c = c0 + j;
+            if (c < slabs) {
+                load_slab(c + PIPE - 1, buf[(j + PIPE - 1) % PIPE]);   // the buffer split in the previous step is free again
+                if (!store_slab(c, buf[j])) return;
+            }
+        }
+    }
+}
+
+// TMA path (row stride a multiple of 16 bytes).  The issuer: one thread, one tensor copy per slab.
+__device__ void tma_issuer_role(const TcParams& P, const CUtensorMap* tmap, uint32_t ring_base, uint32_t landed0, uint32_t empty0,
+                                volatile int* abort_flag, long long first_tile, long long tile_step, long long tiles) {
+    const int S = P.stages;
+    long long c = 0;
+    for (long long tile = first_tile; tile < tiles; tile += tile_step) {
+        for (int kc = 0; kc < P.nchunks; kc++, c++) {
+            const int s = (int)(c % S);
+            if (c / S >= 1 && !mbar_wait(empty0 + 8 * s, (unsigned)((c / S - 1) & 1), abort_flag, 2)) return;
+            const uint32_t bar = landed0 + 8 * s;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((unsigned)SLAB_BYTES) : "memory");
+            // coordinates: x = first float of the K slab (a multiple of 32 floats = 128 bytes), y = first row of the tile
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                         ::"r"(ring_base + (uint32_t)s * STAGE_BYTES), "l"(tmap), "r"(kc * CHUNK_K), "r"((int)(tile * TILE_M)), "r"(bar) : "memory");
+        }
+    }
+}
+
+// The splitters of the TMA path: eight warps turn the landed raw slab into hi (in place) and lo.
+__device__ void tma_splitter_role(const TcParams& P, unsigned char* ring, uint32_t landed0, uint32_t full0,
+                                  volatile int* abort_flag, long long first_tile, long long tile_step, long long tiles) {
+    constexpr int PPR = 8;                                // 16-byte pieces per 128-byte slab row
+    constexpr int COUNT = TILE_M * PPR / PRODUCERS;       // pieces per thread and slab
+    constexpr int ROW_STEP = PRODUCERS / PPR;
+    constexpr uint32_t SMEM_STEP = (ROW_STEP / 8) * 1024;
+    const int p = threadIdx.x;
+    const uint32_t off0 = swz(p / PPR, (p % PPR) * 16);
+    const int S = P.stages;
+    const long long my_tiles = first_tile < tiles ? (tiles - first_tile + tile_step - 1) / tile_step : 0;
+    const long long slabs = my_tiles * P.nchunks;
+    for (long long c = 0; c < slabs; c++) {
+        const int s = (int)(c % S);
+        if (!mbar_wait(landed0 + 8 * s, (unsigned)((c / S) & 1), abort_flag, 5)) return;
+        unsigned char* stage = ring + (size_t)s * STAGE_BYTES;
+        float4 v[COUNT];
+#pragma unroll
+        for (int i = 0; i < COUNT; i++) v[i] = *reinterpret_cast<const float4*>(stage + off0 + i * SMEM_STEP);
+#pragma unroll
+        for (int i = 0; i < COUNT; i++) {
+            const float* f = reinterpret_cast<const float*>(&v[i]);
+            float h[4], l[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                h[e] = __uint_as_float(__float_as_uint(f[e]) & TF32_MASK);
+                l[e] = __uint_as_float(__float_as_uint(f[e] - h[e]) & TF32_MASK);
+            }
+            *reinterpret_cast<float4*>(stage + off0 + i * SMEM_STEP) = *reinterpret_cast<float4*>(h);
+            if (!P.tf32) *reinterpret_cast<float4*>(stage + SLAB_BYTES + off0 + i * SMEM_STEP) = *reinterpret_cast<float4*>(l);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
+        mbar_arrive(full0 + 8 * s);
     }
 }
 
@@ -352,9 +430,11 @@ __device__ void mma_role(const TcParams& P, uint32_t ring_base, uint32_t w_hi, u
                 const uint64_t dah = umma_desc(a_hi + koff), dal = umma_desc(a_lo + koff);
                 const uint64_t dbh = umma_desc(b_hi + koff), dbl = umma_desc(b_lo + koff);
                 umma_tf32(d_tmem, dah, dbh, idesc, (kc > 0 || ks > 0) ? 1u : 0u);
-                umma_tf32(d_tmem, dah, dbl, idesc, 1u);
-                umma_tf32(d_tmem, dal, dbh, idesc, 1u);
-                umma_tf32(d_tmem, dal, dbl, idesc, 1u);
+                if (!P.tf32) {
+                    umma_tf32(d_tmem, dah, dbl, idesc, 1u);
+                    umma_tf32(d_tmem, dal, dbh, idesc, 1u);
+                    umma_tf32(d_tmem, dal, dbl, idesc, 1u);
+                }
             }
             umma_commit(empty0 + 8 * s);            // the slab may be overwritten once these MMAs are done
         }
@@ -444,8 +524,9 @@ __device__ void epilogue_role(const TcParams& P, float* out_stage, uint32_t tful
     }
 }
 
+// G: bytes per piece of the loaders (8 or 16), or 0 for the TMA path (tmap then describes x).
 template <int G>
-__global__ void __launch_bounds__(THREADS, 1) dense_tc_kernel(const TcParams P) {
+__global__ void __launch_bounds__(G == 0 ? TMA_THREADS : THREADS, 1) dense_tc_kernel(const TcParams P, const __grid_constant__ CUtensorMap tmap) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // carve: [w_hi][w_lo][ring][barriers][tmem ptr]; every region a multiple of 1024 bytes
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -465,9 +546,9 @@ __global__ void __launch_bounds__(THREADS, 1) dense_tc_kernel(const TcParams P) 
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < MAX_STAGES; s++) {
-            mbar_init(full0 + 8 * s, UseProducer<G>::value ? PRODUCERS : LOADERS);
+            mbar_init(full0 + 8 * s, (G == 0 || UseProducer<G>::value) ? PRODUCERS : LOADERS);
             mbar_init(empty0 + 8 * s, 1);
-            mbar_init(landed0 + 8 * s, LOADERS);
+            mbar_init(landed0 + 8 * s, G == 0 ? 1 : LOADERS);
         }
         for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 128); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -477,7 +558,7 @@ __global__ void __launch_bounds__(THREADS, 1) dense_tc_kernel(const TcParams P) 
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // w, split into hi/lo, transposed into K-major swizzled panels of [Npad rows x 32 floats]
-    for (int idx = threadIdx.x; idx < P.nchunks * CHUNK_K * P.Npad; idx += THREADS) {
+    for (int idx = threadIdx.x; idx < P.nchunks * CHUNK_K * P.Npad; idx += blockDim.x) {
         const int nn = idx % P.Npad, kk = (idx / P.Npad) % CHUNK_K, kc = idx / (P.Npad * CHUNK_K);
         const int k = kc * CHUNK_K + kk;
         const float v = (k < P.K && nn < P.M) ? __ldg(P.w + (long long)k * P.M + nn) : 0.f;
@@ -493,12 +574,17 @@ __global__ void __launch_bounds__(THREADS, 1) dense_tc_kernel(const TcParams P) 
     const uint32_t tmem_base = s_tmem_base;
 
     const long long tiles = (P.n + TILE_M - 1) / TILE_M;
-    if (UseProducer<G>::value && warp < 2 * LOADER_WARPS) {
-        producer_role<G>(P, ring, full0, empty0, &s_abort, blockIdx.x, gridDim.x, tiles);
-    } else if (warp < LOADER_WARPS) {
-        loader_role<G>(P, ring, landed0, empty0, &s_abort, blockIdx.x, gridDim.x, tiles);
-    } else if (warp < 2 * LOADER_WARPS) {
-        splitter_role<G>(P, ring, landed0, full0, &s_abort, blockIdx.x, gridDim.x, tiles);
+    if (G == 0 && warp < 2 * LOADER_WARPS) {
+        tma_splitter_role(P, ring, landed0, full0, &s_abort, blockIdx.x, gridDim.x, tiles);
+    } else if (G == 0 && warp == 2 * LOADER_WARPS + 5) {
+        if ((threadIdx.x & 31) == 0)
+            tma_issuer_role(P, &tmap, smem_u32(ring), landed0, empty0, &s_abort, blockIdx.x, gridDim.x, tiles);
+    } else if (UseProducer<G>::value && warp < 2 * LOADER_WARPS) {
+        producer_role<(G == 0 ? 8 : G)>(P, ring, full0, empty0, &s_abort, blockIdx.x, gridDim.x, tiles);
+    } else if (G != 0 && warp < LOADER_WARPS) {
+        loader_role<(G == 0 ? 16 : G)>(P, ring, landed0, empty0, &s_abort, blockIdx.x, gridDim.x, tiles);
+    } else if (G != 0 && warp < 2 * LOADER_WARPS) {
+        splitter_role<(G == 0 ? 16 : G)>(P, ring, landed0, full0, &s_abort, blockIdx.x, gridDim.x, tiles);
     } else if (warp < 2 * LOADER_WARPS + 4) {
         // staging rows (odd output widths, publishing calls): 32 rows x (Npad+1) floats per epilogue warp, after the barriers
         float* out_stage = P.stage_out ? reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + 256) +
@@ -514,6 +600,28 @@ __global__ void __launch_bounds__(THREADS, 1) dense_tc_kernel(const TcParams P) 
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P.tmem_cols) : "memory");
     }
+}
+
+}  // namespace
+
+namespace {
+
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link against
+// the driver library (machines that only build it have none).  NULL when the driver offers none.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static bool looked = false;
+    if (!looked) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        looked = true;
+    }
+    return fn;
 }
 
 }  // namespace
@@ -548,6 +656,7 @@ int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, in
     P.out = out; P.x = x; P.w = w; P.row_scale = row_scale; P.n = n;
     P.K = dim1; P.M = dim2; P.Npad = Npad; P.nchunks = nchunks; P.stages = stages;
     P.relu = (flags & MGGB_DENSE_RELU) ? 1 : 0;
+    P.tf32 = (flags & MGGB_DENSE_TF32) ? 1 : 0;
     P.stage_out = stage_out ? 1 : 0;
     // 128-bit stores need 16-byte aligned destinations (a view that starts at an odd float offset is
     // not); otherwise the epilogue stores float by float.
@@ -563,12 +672,30 @@ int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, in
     const long long tiles = (n + TILE_M - 1) / TILE_M;
     const int grid = (int)std::min<long long>(tiles, sms);
     const bool wide = (dim1 % 4 == 0) && ((uintptr_t)x % 16 == 0);
+    CUtensorMap tmap;
+    memset(&tmap, 0, sizeof(tmap));
+#ifndef MGGB_DENSE_CP_ASYNC
+    if (wide && encode_tiled() != nullptr) {
+        // x as a 2-D tensor [n rows][dim1 floats] (row stride dim1 * 4 bytes, a multiple of 16); one box = one slab
+        const cuuint64_t gdim[2] = {(cuuint64_t)dim1, (cuuint64_t)n};
+        const cuuint64_t gstride[1] = {(cuuint64_t)dim1 * sizeof(float)};
+        const cuuint32_t box[2] = {(cuuint32_t)CHUNK_K, (cuuint32_t)TILE_M};
+        const cuuint32_t estride[2] = {1, 1};
+        CUresult r = encode_tiled()(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(x), gdim, gstride, box, estride,
+                                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return mggb::fail(MGGB_ERR_CUDA, "dense_forward: cuTensorMapEncodeTiled failed with CUresult %d (n=%lld dim1=%d)", (int)r, (long long)n, dim1);
+        MGGB_CUDA(cudaFuncSetAttribute(dense_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        dense_tc_kernel<0><<<grid, TMA_THREADS, smem, st>>>(P, tmap);
+    } else
+#endif
     if (wide) {
         MGGB_CUDA(cudaFuncSetAttribute(dense_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        dense_tc_kernel<16><<<grid, THREADS, smem, st>>>(P);
+        dense_tc_kernel<16><<<grid, THREADS, smem, st>>>(P, tmap);
     } else {
         MGGB_CUDA(cudaFuncSetAttribute(dense_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        dense_tc_kernel<8><<<grid, THREADS, smem, st>>>(P);
+        dense_tc_kernel<8><<<grid, THREADS, smem, st>>>(P, tmap);
     }
     MGGB_CUDA(cudaGetLastError());
     *launched = true;

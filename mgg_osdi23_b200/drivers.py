@@ -69,7 +69,13 @@ class Shard:
         self.pe, self.num_pes, self.num_nodes = pe, num_pes, n
         self.node_per_pe, self.lb, self.ub = api.shard_range(n, num_pes, pe)
         self.rows = self.ub - self.lb
-        lp, rp, lc, rc = api.split_CSR(row_ptr, col_idx, self.lb, self.ub, first_row=self.lb if shard_local else 0)
+        first_row = self.lb if shard_local else 0
+        lp, rp, lc, rc = api.split_CSR(row_ptr, col_idx, self.lb, self.ub, first_row=first_row)
+        # this shard's rows of the UNSPLIT lists (views, nothing copied): what a PE that holds a full
+        # replica of the embedding matrix gathers from, see merged_lists()
+        e0, e1 = int(row_ptr[self.lb - first_row]), int(row_ptr[self.ub - first_row])
+        self._host_rows = (row_ptr[self.lb - first_row: self.ub - first_row + 1], np.asarray(col_idx)[e0:e1], e0)
+        self._merged = None
         self.e_local, self.e_remote = int(lc.size), int(rc.size)
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.device = dev
@@ -92,6 +98,7 @@ class Shard:
         self.row_order = torch.from_numpy(self._order_host).to(dev) if self._order_host is not None else None
         self._blocks = {}
         self._flag_cache = {}
+        self.use_merged_lists = True   # False: a replica is gathered from through the two split lists as well
         self._dinv = None
         self.event_sink = None   # when a list: (start, end) CUDA events of every aggregation launch are appended
         self._in_span = False
@@ -152,6 +159,26 @@ class Shard:
                 api.inv_sqrt_degree(self._dinv, self.rp_l, self.rp_r)
         return self._dinv
 
+    def merged_lists(self):
+        """(row_ptr, col_idx, empty row_ptr, dummy col_idx) on the device: each row's whole neighbor list,
+        local and remote ids together in stored order, as the "local" half, and an empty "remote" half.
+        For aggregating from a REPLICA of the embedding matrix: every id is then addressed the same way,
+        so the split into two lists (two walks per node, two ragged tails) buys nothing."""
+        if self._merged is None:
+            rp, col, e0 = self._host_rows
+            rp_m = np.ascontiguousarray(np.asarray(rp, dtype=np.int64) - e0, dtype=np.int32)
+            ci_m = np.ascontiguousarray(col, dtype=np.int32)
+            self._merged = (torch.from_numpy(rp_m).to(self.device),
+                            torch.from_numpy(ci_m if ci_m.size else np.zeros(1, np.int32)).to(self.device),
+                            torch.zeros(self.rows + 1, dtype=torch.int32, device=self.device),
+                            torch.zeros(1, dtype=torch.int32, device=self.device))
+        return self._merged
+
+    def _lists_for(self, sym):
+        if getattr(sym, "slot_elems", None) is not None and self.num_pes > 1 and self.use_merged_lists:
+            return self.merged_lists()
+        return self.rp_l, self.ci_l, self.rp_r, self.ci_r
+
     def agg_flags(self, knobs: Knobs, dim: int) -> int:
         """The knobs' flags, plus NO_HUB_SPLIT when no row of this shard exceeds the hub threshold."""
         key = (knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, knobs.flags, dim)
@@ -163,13 +190,13 @@ class Shard:
     def aggregate(self, out, sym, dim, knobs: Knobs, accumulate=False, row_scale_=None, publish=None, rows=None):
         """``rows``: a row list from :meth:`row_blocks` (only those rows are computed); None = the whole shard."""
         self._timed(lambda: api.mgg_SAG_np_div(
-            out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim, self.node_per_pe, self.pe,
+            out, sym, *self._lists_for(sym), self.lb, self.ub, dim, self.node_per_pe, self.pe,
             knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, accumulate=accumulate, row_scale_=row_scale_,
             publish=publish, row_order=self.row_order, rows=rows, flags=self.agg_flags(knobs, dim)))
 
     def aggregate_gin(self, out, sym, dim, knobs: Knobs, eps: float, rows=None):
         self._timed(lambda: api.mgg_GIN_np_div(
-            out, sym, self.rp_l, self.ci_l, self.rp_r, self.ci_r, self.lb, self.ub, dim, self.node_per_pe, self.pe,
+            out, sym, *self._lists_for(sym), self.lb, self.ub, dim, self.node_per_pe, self.pe,
             knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, eps, row_order=self.row_order, rows=rows,
             flags=self.agg_flags(knobs, dim)))
 

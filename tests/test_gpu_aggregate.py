@@ -284,24 +284,24 @@ def test_publish_rows_copies_to_every_destination():
 @pytest.mark.parametrize("dim", [4, 8, 16, 32, 64, 128])
 @pytest.mark.parametrize("G", [1, 2, 3])
 def test_rows_staged_through_shared_memory_match_the_oracle(oracle, dim, G):
-    """Rows brought in by bulk copies (always for rows pulled from other PEs' buffers; for local rows
-    too with AGG_STAGE_LOCAL) against the register path (AGG_NO_STAGING) and the fp64 oracle: short,
-    long and empty lists, a hub row, chunk sizes below and above a 32-row batch, 1 to 8 warps."""
+    """Rows brought in by bulk copies (AGG_STAGE_ROWS: the rows pulled from other PEs' buffers when there
+    are peers, every row otherwise) against the register path and the fp64 oracle: short, long and
+    empty lists, a hub row, chunk sizes below and above a 32-row batch, 1 to 8 warps."""
     import ctypes as C
     from mgg_osdi23_b200 import _lib
     rp, col = random_graph(700, 40, seed=10 * dim + G, hubs=[(5, 20000), (333, 3000), (7, 0), (699, 1)])
     x = np.random.default_rng(dim).uniform(-0.02, 0.02, (700, dim)).astype(np.float32)
     want = oracle.sag_f64(x, rp, col)
-    for flags in (_lib.AGG_STAGE_LOCAL, 0, _lib.AGG_NO_STAGING):
+    for flags in (_lib.AGG_STAGE_ROWS, 0):
         for knobs in ((16, 4, 1), (3, 2, 2), (32, 1, 1), (8, 8, 4)):
             got = emulated_aggregate(rp, col, x, G, knobs, flags=flags)
             np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL, err_msg=f"flags={flags} knobs={knobs}")
     # the shared epilogue: GIN combine, accumulate and row scaling on the staged path
-    got = emulated_aggregate(rp, col, x, G, (16, 4, 2), gin_eps=0.25, flags=_lib.AGG_STAGE_LOCAL)
+    got = emulated_aggregate(rp, col, x, G, (16, 4, 2), gin_eps=0.25, flags=_lib.AGG_STAGE_ROWS)
     np.testing.assert_allclose(got, want + 1.25 * x, rtol=RTOL, atol=ATOL)
     init = np.random.default_rng(1).uniform(-1, 1, x.shape).astype(np.float32)
     scale = np.random.default_rng(2).uniform(0.5, 1.5, 700).astype(np.float32)
-    got = emulated_aggregate(rp, col, x, G, (16, 4, 2), accumulate=True, init=init, row_scale=scale, flags=_lib.AGG_STAGE_LOCAL)
+    got = emulated_aggregate(rp, col, x, G, (16, 4, 2), accumulate=True, init=init, row_scale=scale, flags=_lib.AGG_STAGE_ROWS)
     np.testing.assert_allclose(got, want * scale[:, None] + init, rtol=RTOL, atol=ATOL)
     st = C.c_int(-1)
     _lib.check(_lib.lib.mggb_agg_device_status(C.byref(st), 0))

@@ -144,3 +144,26 @@ def test_dense_output_and_publish_views_at_odd_float_offsets(oracle, n, k, m):
     st = mgg._lib.C.c_int(-1)
     mgg._lib.check(mgg._lib.lib.mggb_dense_device_status(mgg._lib.C.byref(st), 0))
     assert st.value == 0
+
+
+@pytest.mark.parametrize("n,k,m", [(2000, 602, 16), (1500, 64, 64), (900, 100, 47)])
+def test_single_pass_tf32_mode(oracle, n, k, m):
+    """MGGB_DENSE_TF32: one tensor-core pass with both operands truncated to TF32 (10 mantissa bits), what
+    cublasSgemm gives under its TF32 math mode.  Tolerance: 2e-3 of sum_k |x_ik| |w_kj| per element (each
+    product is off by at most 2 * 2^-10 of its magnitude).  The default mode on the same inputs stays within
+    the fp32 tolerance, so the flag is what made the difference."""
+    dev = torch.device("cuda")
+    x = gg.features(n, k, seed=n).numpy()
+    w = gg.glorot_uniform(k, m, seed=k).numpy()
+    want = oracle.dense(x, w)
+    mag = oracle.dense(np.abs(x), np.abs(w))
+    xd, wd = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
+    fast = torch.empty(n, m, device=dev)
+    mgg.dense_forward(fast, xd, wd, flags=mgg._lib.DENSE_TF32)
+    full = torch.empty(n, m, device=dev)
+    mgg.dense_forward(full, xd, wd)
+    torch.cuda.synchronize()
+    err_fast = np.abs(fast.cpu().numpy() - want)
+    assert np.all(err_fast <= 2e-3 * mag + 1e-6)
+    np.testing.assert_allclose(full.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+    assert err_fast.max() > 10 * np.abs(full.cpu().numpy() - want).max()

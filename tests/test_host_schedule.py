@@ -94,3 +94,21 @@ def test_leading_barrier_is_issued_before_stage_zero():
     M.leading_barrier = False
     drivers.run_stages([M()], barrier=lambda: calls.append("b"))
     assert calls == ["s0", "b", "s1"]
+
+
+def test_merged_lists_are_the_shard_rows_of_the_unsplit_graph():
+    """What a PE gathers from a replica: each row's whole stored list as the "local" half, nothing in the
+    "remote" half; the same arrays whether the shard was built from the whole graph or from its own rows."""
+    rp, col = _graph()
+    for pe in range(3):
+        sh = drivers.Shard(rp, col, pe, 3, device="cpu")
+        m = sh.merged_lists()
+        assert np.array_equal(m[0].numpy(), rp[sh.lb:sh.ub + 1] - rp[sh.lb])
+        assert np.array_equal(m[1].numpy(), col[rp[sh.lb]:rp[sh.ub]])
+        assert m[2].numel() == sh.rows + 1 and int(m[2].abs().sum()) == 0
+        local = drivers.Shard((rp[sh.lb:sh.ub + 1] - rp[sh.lb]).astype(np.int64), col[rp[sh.lb]:rp[sh.ub]], pe, 3, device="cpu",
+                              num_nodes=len(rp) - 1, shard_local=True)
+        assert all(torch.equal(a, b) for a, b in zip(m, local.merged_lists()))
+        # only a replica (it has slots) gets them; a pulled symmetric buffer keeps the split lists
+        rep = type("R", (), {"slot_elems": 4})()
+        assert sh._lists_for(rep)[0] is m[0] and sh._lists_for(object())[0] is sh.rp_l
