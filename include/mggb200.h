@@ -53,6 +53,7 @@ enum {
                                 rate for reads of that size), and local rows come 3.7x slower than through the
                                 load/store unit, because an SM's copy engine keeps only about a hundred row copies
                                 in flight.  Kept as an option for other row widths and machines */
+    MGGB_AGG_GIN_COMBINE = 32, /* mggb_sag_np_part only: out = (1+eps) * x_self + sum, as mggb_gin_np_div computes */
     MGGB_AGG_GROUP_PER_NODE = 4 /* dim 16 only (ignored otherwise): a node is aggregated by one group of 4 lanes,
                                  8 nodes per warp, instead of by warp_per_block warps; part_size and
                                  interleaved_dist then do not apply, and nodes above 1024 neighbors take the
@@ -230,6 +231,33 @@ int mggb_publish_rows(const float* in, int64_t count, float* const* publish_out,
 /* Host helper: order[k] = the shard row with the k-th largest neighbor count (local + remote; ties
  * in row order).  row_ptr_r may be NULL.  No counterpart in the reference. */
 int mggb_degree_order(const int32_t* row_ptr_l, const int32_t* row_ptr_r, int32_t num_rows, int32_t* order);
+
+/* The aggregation over EXPLICIT neighbor partitions.  Replaces SAG_host_fused_interleaved /
+ * SAG_cuda_kernel_fused_interleaved (include/neighbor_utils.cuh:593-676, :2598-2760; driver
+ * src/test_neighbor_part.cu:93-211) and takes what mggb_build_part_* returns for each half of the split
+ * CSR: part_ptr (first edge of each partition), part2node (its row), node2part (first partition of each
+ * row, ub-lb+2 entries).  One warp serves interleaved_dist consecutive partitions of the local half and
+ * the same range of the remote half (the reference's map, :2636-2640), warp_per_block warps per block, so
+ * the grid grows with the number of partitions and a row with 10^5 neighbors is spread over thousands of
+ * warps.  Each partition's partial row goes to `scratch` ([num_parts_l + num_parts_r] x dim floats, device
+ * memory the CALLER provides: mggb_sag_np_part_scratch_bytes gives the size; contents need no
+ * initialisation and are garbage afterwards); a second kernel adds each row's partial rows in partition
+ * order and stores the output row once.  The reference instead adds every partial row into the output
+ * with a spinning float atomic (:2683-2686) and has its remote half commented out (:2693-2759).
+ * A partition ends at min(part_ptr[p] + part_size, end of its row); part_ptr[p+1] is never read, so both
+ * sentinel conventions of mggb_build_part_fill work.  row_scale, MGGB_AGG_ACCUMULATE and the result are as
+ * for mggb_sag_np_div (same sums up to fp32 order; bit-reproducible for fixed knobs);
+ * MGGB_AGG_GIN_COMBINE with eps gives mggb_gin_np_div's combine.  Other flags are ignored. */
+int mggb_sag_np_part_scratch_bytes(int64_t num_parts_l, int64_t num_parts_r, int dim, size_t* bytes);
+int mggb_sag_np_part(float* output, const float* const* peer_input, int num_pes,
+                     const int32_t* row_ptr_l, const int32_t* col_idx_l, const int32_t* part_ptr_l,
+                     const int32_t* part2node_l, const int32_t* node2part_l, int64_t num_parts_l,
+                     const int32_t* row_ptr_r, const int32_t* col_idx_r, const int32_t* part_ptr_r,
+                     const int32_t* part2node_r, const int32_t* node2part_r, int64_t num_parts_r,
+                     int32_t lb, int32_t ub, int dim, int32_t node_per_pe, int pe,
+                     int part_size, int warp_per_block, int interleaved_dist,
+                     const float* row_scale, int flags, float eps,
+                     float* scratch, size_t scratch_bytes, void* stream);
 
 /* Neighbor count above which the aggregation entry points hand a row to the wide-block kernel at
  * these knobs, dim and flags (MGGB_AGG_*); -1 when no row ever is.  A caller that knows its shard's

@@ -12,7 +12,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libmggb200.so")
 
 OK, ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_PEER, ERR_IO = range(6)
-AGG_ACCUMULATE, AGG_NO_HUB_SPLIT, AGG_GROUP_PER_NODE, AGG_STAGE_ROWS = 1, 2, 4, 8
+AGG_ACCUMULATE, AGG_NO_HUB_SPLIT, AGG_GROUP_PER_NODE, AGG_STAGE_ROWS, AGG_GIN_COMBINE = 1, 2, 4, 8, 32
 DENSE_RELU, DENSE_TF32, DENSE_SIMT = 1, 2, 4
 MAX_PES = 16
 
@@ -69,6 +69,9 @@ SIGNATURES = {
                              _int, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp, _i64, _vp],
     "mggb_gin_np_div_rows": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
                              _int, _int, _int, _f, _int, _vp, _i64, _vp],
+    "mggb_sag_np_part_scratch_bytes": [_i64, _i64, _int, C.POINTER(C.c_size_t)],
+    "mggb_sag_np_part": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64,
+                         _i32, _i32, _int, _i32, _int, _int, _int, _int, _vp, _int, _f, _vp, C.c_size_t, _vp],
     "mggb_publish_rows": [_vp, _i64, C.POINTER(_vp), _int, _vp],
     "mggb_degree_order": [_vp, _vp, _i32, _vp],
     "mggb_hub_threshold": [_int, _int, _int, _int, _int, _pi64],

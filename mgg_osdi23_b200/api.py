@@ -29,7 +29,7 @@ from . import _lib
 from ._lib import lib, check
 
 __all__ = [
-    "shard_range", "split_CSR", "build_part", "mgg_SAG_np_div", "mgg_GIN_np_div",
+    "shard_range", "split_CSR", "build_part", "mgg_SAG_np_div", "mgg_GIN_np_div", "SAG_host_fused_interleaved",
     "dense_param_new_beg", "dense_param_new_hidden", "softmax_new_param",
     "dense_beg_new_forward", "dense_hidden_new_forward", "softmax_new_forward", "dense_hidden_softmax_new_forward",
     "dense_forward", "softmax_forward", "dense_softmax_forward", "dense_softmax_fits", "publish_rows", "row_scale", "inv_sqrt_degree", "degree_order", "hub_threshold",
@@ -224,6 +224,39 @@ def mgg_GIN_np_div(output, input, row_pointers_l, column_index_l, row_pointers_r
         _dev_ptr(row_pointers_r, torch.int32, "row_pointers_r"), _dev_ptr(column_index_r, torch.int32, "column_index_r"),
         lb, ub, dim, nodePerPE, peid, np_size, warpPerBlock, interleaved_dist, float(eps), flags,
         _dev_ptr(row_order, torch.int32, "row_order"), _stream()))
+
+
+def SAG_host_fused_interleaved(output, input, local_row_pointers, local_column_index, local_part_pointers, local_part2Node,
+                               local_num_parts, remote_row_pointers, remote_column_index, remote_part_pointers, remote_part2Node,
+                               remote_num_parts, num_nodes, lowbound, partSize, dim, dimWorker, warpPerBlock, interleaved_dist=1,
+                               *, local_node2Part, remote_node2Part=None, nodePerPE=None, peid=0, scratch=None,
+                               accumulate: bool = True, row_scale_=None, gin_eps=None):
+    """The aggregation over explicit neighbor partitions, with the reference launcher's argument order
+    (``include/neighbor_utils.cuh:593-616``): ``num_nodes`` rows starting at global row ``lowbound``;
+    the ``*_part_pointers`` / ``*_part2Node`` device arrays are ``build_part``'s first two outputs for
+    each half of the split CSR.  ``dimWorker`` is accepted for signature parity (the kernels choose
+    their own lane mapping).  Beyond the reference's list: ``*_node2Part`` (``build_part``'s third
+    output; the per-row reduce needs it where the reference uses atomics), ``nodePerPE`` / ``peid`` and
+    a table ``input`` for several PEs, and an optional ``scratch`` tensor (allocated here when None)."""
+    del dimWorker
+    table, num_pes = _peer_table(input)
+    npp = num_nodes if nodePerPE is None else nodePerPE
+    need = C.c_size_t()
+    check(lib.mggb_sag_np_part_scratch_bytes(local_num_parts, remote_num_parts, dim, C.byref(need)))
+    if scratch is None:
+        scratch = torch.empty(max(need.value // 4, 4), dtype=torch.float32, device=output.device)
+    flags = (_lib.AGG_ACCUMULATE if accumulate and gin_eps is None else 0) | (_lib.AGG_GIN_COMBINE if gin_eps is not None else 0)
+    kernel_launches[0] += 2 if num_nodes else 0
+    check(lib.mggb_sag_np_part(
+        _dev_ptr(output, torch.float32, "output"), table, num_pes,
+        _dev_ptr(local_row_pointers, torch.int32), _dev_ptr(local_column_index, torch.int32), _dev_ptr(local_part_pointers, torch.int32),
+        _dev_ptr(local_part2Node, torch.int32), _dev_ptr(local_node2Part, torch.int32), local_num_parts,
+        _dev_ptr(remote_row_pointers, torch.int32), _dev_ptr(remote_column_index, torch.int32), _dev_ptr(remote_part_pointers, torch.int32),
+        _dev_ptr(remote_part2Node, torch.int32), _dev_ptr(remote_node2Part, torch.int32), remote_num_parts,
+        lowbound, lowbound + num_nodes, dim, npp, peid, partSize, warpPerBlock, interleaved_dist,
+        _dev_ptr(row_scale_, torch.float32, "row_scale"), flags, float(gin_eps or 0.0),
+        _dev_ptr(scratch, torch.float32, "scratch"), scratch.numel() * 4, _stream()))
+    return scratch
 
 
 # ---- dense update and softmax ---------------------------------------------------------------------

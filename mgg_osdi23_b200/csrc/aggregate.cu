@@ -275,16 +275,6 @@ long long hub_threshold(int ps, int wpb, int dist, int dim, int flags) {
     return std::max<long long>(HUB_MIN_EDGES, 64 * chunk * wpb);
 }
 
-// Exact unsigned division by a runtime constant d for every 32-bit numerator:
-// q = (n * magic) >> shift with shift = 32 + ceil(log2 d), magic = ceil(2^shift / d) < 2^33.
-void make_divider(uint32_t d, unsigned long long* magic, int* shift) {
-    int lg = 0;
-    while ((1ull << lg) < d) lg++;
-    *shift = 32 + lg;
-    const unsigned __int128 one = 1;
-    *magic = (unsigned long long)(((one << *shift) + d - 1) / d);
-}
-
 template <int LPR, int VEC, bool EXACT>
 int launch_exact(const AggParams& P, int wpb, cudaStream_t st);
 

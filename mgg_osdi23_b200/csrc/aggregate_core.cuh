@@ -62,6 +62,7 @@ template <> struct Vec<4> {
         v.w += __shfl_xor_sync(0xffffffffu, v.w, off);
     }
     __device__ __forceinline__ void store_smem(float* p) const { *reinterpret_cast<float4*>(p) = v; }
+    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }   // 16-byte aligned destination
 };
 template <> struct Vec<1> {
     float v;
@@ -70,6 +71,7 @@ template <> struct Vec<1> {
     __device__ __forceinline__ void add(const Vec& o) { v += o.v; }
     __device__ __forceinline__ void xor_reduce(int off) { v += __shfl_xor_sync(0xffffffffu, v, off); }
     __device__ __forceinline__ void store_smem(float* p) const { *p = v; }
+    __device__ __forceinline__ void store(float* p) const { *p = v; }
 };
 
 // Adds the rows of up to 32 neighbors (ids held one per lane in `my`, -1 = none) into acc.
@@ -194,6 +196,16 @@ __device__ __forceinline__ void accumulate_row(Vec<VEC>& acc, const AggParams& P
                 gather_list<LPR, VEC, false, WALK>(acc, P, s_peer, ci, beg, end, base, half ? rwarp : warp, nwarps, lane, col, col_ok);
         }
     }
+}
+
+// Exact unsigned division by a runtime constant d for every 32-bit numerator:
+// q = (n * magic) >> shift with shift = 32 + ceil(log2 d), magic = ceil(2^shift / d) < 2^33.
+inline void make_divider(uint32_t d, unsigned long long* magic, int* shift) {
+    int lg = 0;
+    while ((1ull << lg) < d) lg++;
+    *shift = 32 + lg;
+    const unsigned __int128 one = 1;
+    *magic = (unsigned long long)(((one << *shift) + d - 1) / d);
 }
 
 // Single writer per output element: sums the warps' partial rows (s_part[w * dim + c], complete and

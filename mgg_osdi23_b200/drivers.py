@@ -97,6 +97,7 @@ class Shard:
         self._order_host = api.degree_order(lp, rp) if (order_rows and self.rows) else None
         self.row_order = torch.from_numpy(self._order_host).to(dev) if self._order_host is not None else None
         self._blocks = {}
+        self._parts = {}
         self._flag_cache = {}
         self.use_merged_lists = True   # False: a replica is gathered from through the two split lists as well
         self._dinv = None
@@ -178,6 +179,31 @@ class Shard:
         if getattr(sym, "slot_elems", None) is not None and self.num_pes > 1 and self.use_merged_lists:
             return self.merged_lists()
         return self.rp_l, self.ci_l, self.rp_r, self.ci_r
+
+    def partitions(self, part_size: int):
+        """``build_part`` of both halves of this shard's split CSR at ``part_size``, on the device (cached):
+        a dict with ``l`` and ``r`` = (part_ptr, part2node, node2part, num_parts)."""
+        if part_size not in self._parts:
+            out = {}
+            for key, rp in (("l", self.rp_l), ("r", self.rp_r)):
+                pp, p2n, n2p = api.build_part(key, rp.cpu().numpy(), self.rows, part_size)
+                pad = lambda a: torch.from_numpy(a if a.size else np.zeros(1, np.int32)).to(self.device)
+                out[key] = (pad(pp), pad(p2n), pad(n2p), int(p2n.size))
+            self._parts[part_size] = out
+        return self._parts[part_size]
+
+    def aggregate_parts(self, out, sym, dim, knobs: Knobs, accumulate=False, row_scale_=None, gin_eps=None, scratch=None):
+        """The same aggregation through the explicit-partition kernels (``api.SAG_host_fused_interleaved``):
+        one warp per ``interleaved_dist`` partitions of ``partSize`` edges.  Returns the scratch tensor used."""
+        parts = self.partitions(knobs.partSize)
+        (pl, p2l, n2l, nl), (pr, p2r, n2r, nr) = parts["l"], parts["r"]
+        box = []
+        self._timed(lambda: box.append(api.SAG_host_fused_interleaved(
+            out, sym, self.rp_l, self.ci_l, pl, p2l, nl, self.rp_r, self.ci_r, pr, p2r, nr if self.num_pes > 1 else 0,
+            self.rows, self.lb, knobs.partSize, dim, min(dim, 32), knobs.warpPerBlock, knobs.interleaved_dist,
+            local_node2Part=n2l, remote_node2Part=n2r, nodePerPE=self.node_per_pe, peid=self.pe, scratch=scratch,
+            accumulate=accumulate, row_scale_=row_scale_, gin_eps=gin_eps)))
+        return box[0]
 
     def agg_flags(self, knobs: Knobs, dim: int) -> int:
         """The knobs' flags, plus NO_HUB_SPLIT when no row of this shard exceeds the hub threshold."""
