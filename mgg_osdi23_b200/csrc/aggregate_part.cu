@@ -100,7 +100,9 @@ __global__ void __launch_bounds__(512) sag_part_kernel(const PartParams Q) {
     }
 }
 
-// One thread per (node, column): adds the node's partial rows, local half first, in partition order.
+// One thread per (node, column): adds the node's partial rows, local half first, in partition order
+// (long lists: in LANES interleaved running sums).
+constexpr int LANES = 16;
 __global__ void __launch_bounds__(256) sag_part_reduce_kernel(const PartParams Q, const int halves) {
     const AggParams& P = Q.A;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -112,12 +114,25 @@ __global__ void __launch_bounds__(256) sag_part_reduce_kernel(const PartParams Q
         const PartHalf& H = Q.half[h];
         const int a = H.node2part[row], b = H.node2part[row + 1];
         const float* src = H.partial + (long long)a * P.dim + c;
+        const long long step = P.dim;
         int p = a;
-        for (; p + 4 <= b; p += 4, src += 4 * (long long)P.dim) {      // four independent loads in flight
-            const float v0 = src[0], v1 = src[P.dim], v2 = src[2 * (long long)P.dim], v3 = src[3 * (long long)P.dim];
-            s += v0; s += v1; s += v2; s += v3;
+        if (b - a >= 2 * LANES) {
+            // a long list (a hub row cut into thousands of partitions): LANES running sums, folded pairwise at
+            // the end, keep LANES loads in flight and the rounding error LANES times below one running sum's
+            float acc[LANES];
+#pragma unroll
+            for (int j = 0; j < LANES; j++) acc[j] = 0.f;
+            for (; p + LANES <= b; p += LANES, src += LANES * step) {
+#pragma unroll
+                for (int j = 0; j < LANES; j++) acc[j] += src[j * step];
+            }
+#pragma unroll
+            for (int w = LANES / 2; w >= 1; w >>= 1)
+#pragma unroll
+                for (int j = 0; j < w; j++) acc[j] += acc[j + w];
+            s += acc[0];
         }
-        for (; p < b; p++, src += P.dim) s += *src;
+        for (; p < b; p++, src += step) s += *src;
     }
     if (P.row_scale) s *= P.row_scale[row];
     const long long o = (long long)row * P.dim + c;

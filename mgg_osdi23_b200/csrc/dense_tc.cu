@@ -335,6 +335,28 @@ __device__ void producer_role(const TcParams& P, unsigned char* ring, uint32_t f
         return true;
     };
 
+    // A slab is 128 bytes of each of 128 rows: on its own that is a strided walk through DRAM (one short
+    // read per row, 19 passes over a 602-float row), which HBM serves at a fraction of its streaming rate.
+    // So the CTA's NEXT tile - one contiguous range of 128 rows - is requested into L2 as a whole
+    // (cp.async.bulk.prefetch.L2, a few threads, 8 KiB each) while the current tile is consumed: DRAM sees
+    // a sequential stream and the strided slab reads hit L2.  The streaming loads above evict what they
+    // have read first, so the working set in L2 stays near one tile per SM.
+    const bool can_prefetch = ((uintptr_t)P.x % 16) == 0;
+    auto prefetch_tile = [&](long long t) {       // t-th tile of this CTA
+        if (!can_prefetch || t >= my_tiles) return;
+        const long long tile = first_tile + t * tile_step;
+        const long long rows = min((long long)TILE_M, P.n - tile * TILE_M);
+        const long long bytes = (rows * P.K * 4) & ~15LL;
+        const long long off = (long long)p * 8192;
+        if (off < bytes) {
+            const char* src = reinterpret_cast<const char*>(P.x + tile * TILE_M * P.K) + off;
+            const unsigned sz = (unsigned)min(8192LL, bytes - off);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(sz) : "memory");
+        }
+    };
+    prefetch_tile(0);
+    prefetch_tile(1);
+
     V buf[PIPE][COUNT];
 #pragma unroll
     for (int j = 0; j < PIPE - 1; j++) load_slab(j, buf[j]);
@@ -343,6 +365,7 @@ __device__ void producer_role(const TcParams& P, unsigned char* ring, uint32_t f
         for (int j = 0; j < PIPE; j++) {
             const long long c = c0 + j;
             if (c < slabs) {
+                if (c % P.nchunks == 0 && c > 0) prefetch_tile(c / P.nchunks + 1);   // entering tile c/nchunks: ask for the one after
                 load_slab(c + PIPE - 1, buf[(j + PIPE - 1) % PIPE]);   // the buffer split in the previous step is free again
                 if (!store_slab(c, buf[j])) return;
             }
@@ -404,37 +427,34 @@ __device__ void tma_splitter_role(const TcParams& P, unsigned char* ring, uint32
     }
 }
 
-__device__ void mma_role(const TcParams& P, uint32_t ring_base, uint32_t w_hi, uint32_t w_lo, uint32_t full0,
+__device__ void mma_role(const TcParams& P, uint32_t ring_base, uint32_t w_base, uint32_t full0,
                          uint32_t empty0, uint32_t tfull0, uint32_t tempty0, uint32_t tmem_base,
                          volatile int* abort_flag, long long first_tile, long long tile_step, long long tiles) {
     const int S = P.stages;
-    const uint32_t panel = (uint32_t)P.Npad * 128u;
-    // instruction descriptor: D fp32, A/B TF32, both K-major, N = Npad, M = 128
-    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(P.Npad >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+    const uint32_t panel = 2u * (uint32_t)P.Npad * 128u;     // hi rows then lo rows of one K chunk
+    // instruction descriptor: D fp32, A/B TF32, both K-major, M = 128, N = 2*Npad (hi and lo columns of w side by
+    // side in the accumulator) or Npad for the single-pass mode (hi only)
+    const uint32_t ncols = (uint32_t)(P.tf32 ? P.Npad : 2 * P.Npad);
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((ncols >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
     long long consumed = 0, t = 0;
     for (long long tile = first_tile; tile < tiles; tile += tile_step, t++) {
         const int buf = (int)(t & 1);
         const long long use_t = t >> 1;
         if (use_t >= 1 && !mbar_wait(tempty0 + 8 * buf, (unsigned)((use_t - 1) & 1), abort_flag, 4)) return;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.Npad);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * 2 * P.Npad);
         for (int kc = 0; kc < P.nchunks; kc++, consumed++) {
             const int s = (int)(consumed % S);
             if (!mbar_wait(full0 + 8 * s, (unsigned)((consumed / S) & 1), abort_flag, 1)) return;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_hi = ring_base + (uint32_t)s * STAGE_BYTES, a_lo = a_hi + SLAB_BYTES;
-            const uint32_t b_hi = w_hi + (uint32_t)kc * panel, b_lo = w_lo + (uint32_t)kc * panel;
+            const uint32_t b = w_base + (uint32_t)kc * panel;
 #pragma unroll
             for (int ks = 0; ks < CHUNK_K / 8; ks++) {
                 const uint32_t koff = (uint32_t)ks * 32u;   // 8 TF32 = 32 bytes along K inside the swizzled row
-                const uint64_t dah = umma_desc(a_hi + koff), dal = umma_desc(a_lo + koff);
-                const uint64_t dbh = umma_desc(b_hi + koff), dbl = umma_desc(b_lo + koff);
-                umma_tf32(d_tmem, dah, dbh, idesc, (kc > 0 || ks > 0) ? 1u : 0u);
-                if (!P.tf32) {
-                    umma_tf32(d_tmem, dah, dbl, idesc, 1u);
-                    umma_tf32(d_tmem, dal, dbh, idesc, 1u);
-                    umma_tf32(d_tmem, dal, dbl, idesc, 1u);
-                }
+                const uint64_t db = umma_desc(b + koff);
+                umma_tf32(d_tmem, umma_desc(a_hi + koff), db, idesc, (kc > 0 || ks > 0) ? 1u : 0u);   // x_hi * [w_hi | w_lo]
+                if (!P.tf32) umma_tf32(d_tmem, umma_desc(a_lo + koff), db, idesc, 1u);                 // x_lo * [w_hi | w_lo]
             }
             umma_commit(empty0 + 8 * s);            // the slab may be overwritten once these MMAs are done
         }
@@ -455,14 +475,26 @@ __device__ void epilogue_role(const TcParams& P, float* out_stage, uint32_t tful
         const long long row = tile * TILE_M + quarter * 32 + lane;
         const float scale = (P.row_scale && row < P.n) ? P.row_scale[row] : 1.f;
         for (int c0 = 0; c0 < P.Npad; c0 += 16) {
-            uint32_t r[16];
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P.Npad + c0);
+            // columns c0.. of the accumulator hold x * w_hi, columns Npad + c0.. hold x * w_lo: the product is their sum
+            uint32_t r[16], q[16];
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * 2 * P.Npad + c0);
             asm volatile(
                 "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                 : "r"(taddr));
+            if (!P.tf32) {
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                    : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]), "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7]),
+                      "=r"(q[8]), "=r"(q[9]), "=r"(q[10]), "=r"(q[11]), "=r"(q[12]), "=r"(q[13]), "=r"(q[14]), "=r"(q[15])
+                    : "r"(taddr + (uint32_t)P.Npad));
+            }
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (!P.tf32) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(q[j]));
+            }
             if (row < P.n) {
                 float v[16];
 #pragma unroll
@@ -530,9 +562,11 @@ __global__ void __launch_bounds__(G == 0 ? TMA_THREADS : THREADS, 1) dense_tc_ke
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // carve: [w_hi][w_lo][ring][barriers][tmem ptr]; every region a multiple of 1024 bytes
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // w: per K chunk one panel of [2*Npad rows x 32 floats]: rows 0..Npad-1 hold the hi part of w's
+    // columns, rows Npad..2*Npad-1 the lo part, so ONE tensor-core instruction with N = 2*Npad multiplies a
+    // slab by both and x's slabs are read from shared memory twice per k-step (hi, lo) instead of four times.
     const size_t w_bytes = (size_t)P.nchunks * P.Npad * 128;
     unsigned char* w_hi = base;
-    unsigned char* w_lo = base + w_bytes;
     unsigned char* ring = base + 2 * w_bytes;
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(ring + (size_t)P.stages * STAGE_BYTES);
     // bars: full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2], landed[MAX_STAGES]
@@ -563,9 +597,9 @@ __global__ void __launch_bounds__(G == 0 ? TMA_THREADS : THREADS, 1) dense_tc_ke
         const int k = kc * CHUNK_K + kk;
         const float v = (k < P.K && nn < P.M) ? __ldg(P.w + (long long)k * P.M + nn) : 0.f;
         const float h = __uint_as_float(__float_as_uint(v) & TF32_MASK);
-        const uint32_t off = (uint32_t)kc * P.Npad * 128u + swz(nn, kk * 4);
-        *reinterpret_cast<float*>(w_hi + off) = h;
-        *reinterpret_cast<float*>(w_lo + off) = __uint_as_float(__float_as_uint(v - h) & TF32_MASK);
+        const uint32_t chunk0 = (uint32_t)kc * 2u * P.Npad * 128u;
+        *reinterpret_cast<float*>(w_hi + chunk0 + swz(nn, kk * 4)) = h;
+        *reinterpret_cast<float*>(w_hi + chunk0 + swz(P.Npad + nn, kk * 4)) = __uint_as_float(__float_as_uint(v - h) & TF32_MASK);
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -591,7 +625,7 @@ __global__ void __launch_bounds__(G == 0 ? TMA_THREADS : THREADS, 1) dense_tc_ke
                                              (size_t)(warp - 2 * LOADER_WARPS) * 32 * (P.Npad + 1) : nullptr;
         epilogue_role(P, out_stage, tfull0, tempty0, tmem_base, &s_abort, blockIdx.x, gridDim.x, tiles);
     } else if ((threadIdx.x & 31) == 0) {
-        mma_role(P, smem_u32(ring), smem_u32(w_hi), smem_u32(w_lo), full0, empty0, tfull0, tempty0, tmem_base,
+        mma_role(P, smem_u32(ring), smem_u32(w_hi), full0, empty0, tfull0, tempty0, tmem_base,
                  &s_abort, blockIdx.x, gridDim.x, tiles);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -636,7 +670,7 @@ int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, in
     *launched = false;
     if (dim1 % 2 != 0 || ((uintptr_t)x % 8) != 0) return MGGB_OK;         // cp.async pieces are 8 or 16 bytes
     const int Npad = (dim2 + 15) / 16 * 16;
-    if (Npad > 256) return MGGB_OK;
+    if (Npad > 128) return MGGB_OK;     // the accumulator holds 2*Npad columns (x*w_hi | x*w_lo) and one instruction spans them
     const int nchunks = (dim1 + CHUNK_K - 1) / CHUNK_K;
     if (nchunks < 2) return MGGB_OK;   // one slab per tile leaves the four epilogue warps as the limit: the CUDA-core kernel is faster
     const size_t w_bytes = 2 * (size_t)nchunks * Npad * 128;
@@ -649,7 +683,7 @@ int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, in
     if (fixed + 2 * STAGE_BYTES > budget) return MGGB_OK;                  // needs at least a 2-stage ring
     const int stages = (int)std::min<size_t>(MAX_STAGES, (budget - fixed) / STAGE_BYTES);
     unsigned tmem_cols = 32;
-    while (tmem_cols < 2u * Npad) tmem_cols <<= 1;
+    while (tmem_cols < 4u * Npad) tmem_cols <<= 1;      // two accumulators (double buffering) of 2*Npad columns
     if (tmem_cols > 512) return MGGB_OK;
 
     TcParams P{};

@@ -53,6 +53,9 @@ def main(argv=None):
     ap.add_argument("--fetch", default="peer", choices=["peer", "replica"],
                     help="peer: remote rows are read from the owners' memory inside the kernel (the reference's scheme); "
                          "replica: every PE holds a copy of the whole matrix and the kernel reads local memory only")
+    ap.add_argument("--kernel", default="node", choices=["node", "part"],
+                    help="node: the block-per-node kernels (mggb_sag_np_div); part: the warp-per-partition kernels over "
+                         "build_part's arrays (mggb_sag_np_part), whose grid grows with the number of partitions")
     ap.add_argument("--group-per-node", action="store_true",
                     help="also time the 4-lanes-per-node kernel (width 16 only; it ignores the three knobs)")
     args = ap.parse_args(argv)
@@ -94,17 +97,28 @@ def main(argv=None):
             dist_.barrier()
             torch.cuda.synchronize()
 
+    scratch = [None]
+
+    def run_once(k):
+        if not shard.rows:
+            return
+        if args.kernel == "part" and not (k.flags & _lib.AGG_GROUP_PER_NODE):
+            scratch[0] = shard.aggregate_parts(out, sym, args.dim, k, scratch=scratch[0])
+            if scratch[0].numel() * 4 > (8 << 30):       # part_size 1 on a large graph: do not keep 8 GB around
+                scratch[0] = None
+        else:
+            shard.aggregate(out, sym, args.dim, k)
+
     def time_point(ps, wpb, dist, flags=0):
         k = drivers.Knobs(ps, wpb, dist, flags)
+        scratch[0] = None
         for _ in range(args.warmup):
-            if shard.rows:
-                shard.aggregate(out, sym, args.dim, k)
+            run_once(k)
         sync()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(args.iters):
-            if shard.rows:
-                shard.aggregate(out, sym, args.dim, k)
+            run_once(k)
         b.record()
         sync()
         t = torch.tensor([a.elapsed_time(b) / args.iters], dtype=torch.float64, device=dev)
