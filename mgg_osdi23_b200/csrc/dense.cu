@@ -119,7 +119,10 @@ int dense_simt(float* out, const float* x, const float* w, int64_t n, int dim1, 
     return MGGB_OK;
 }
 
-// Tensor-core kernel (dense_tc.cu); sets *launched = false when the shape does not fit it.
+// Row-streaming CUDA-core kernel for outputs of at most 16 columns (dense_rowstream.cu) and the
+// tensor-core kernel (dense_tc.cu); each sets *launched = false when the shape does not fit it.
+int dense_rowstream(float* out, const float* x, const float* w, int64_t n, int dim1, int dim2, const float* row_scale,
+                    int flags, float* const* publish_out, int num_publish, cudaStream_t st, bool* launched);
 int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, int dim2, const float* row_scale,
              int flags, float* const* publish_out, int num_publish, cudaStream_t st, bool* launched);
 
@@ -135,6 +138,13 @@ extern "C" int mggb_dense_forward(float* out, const float* x, const float* w, in
     MGGB_REQUIRE(n >= 0 && dim1 >= 1 && dim2 >= 1, "dense_forward: need n >= 0, dim1 >= 1, dim2 >= 1 (n=%lld dim1=%d dim2=%d)", (long long)n, dim1, dim2);
     MGGB_REQUIRE(out != x, "dense_forward: out must not alias x");
     if (n == 0) return MGGB_OK;
+    // Narrow outputs: the row-streaming kernel (fp32 FMA) unless the caller asked for tensor cores.
+    if (!(flags & (MGGB_DENSE_TENSOR | MGGB_DENSE_TF32))) {
+        bool launched = false;
+        const int st = mggb::dense_rowstream(out, x, w, n, dim1, dim2, row_scale, flags, publish_out, num_publish,
+                                             (cudaStream_t)stream, &launched);
+        if (st != MGGB_OK || launched) return st;
+    }
     if (!(flags & MGGB_DENSE_SIMT)) {
         bool launched = false;
         const int st = mggb::dense_tc(out, x, w, n, dim1, dim2, row_scale, flags, publish_out, num_publish,

@@ -58,18 +58,21 @@ def test_softmax_matches_oracle(oracle, n, c):
 
 
 def test_tensor_core_kernel_reports_clean_status_and_matches_cuda_core_kernel(oracle):
-    """The default path (tcgen05 kernel where the shape fits) against the forced CUDA-core kernel,
-    including rows that do not fill a 128-row tile and a K tail that does not fill a 32-float slab."""
+    """The default path (row-streaming kernel for outputs of at most 16 columns, tcgen05 kernel otherwise),
+    the tensor-core kernel forced (DENSE_TENSOR) and the CUDA-core kernels forced (DENSE_SIMT), including
+    rows that do not fill a 128-row tile and a K tail that does not fill a 32-float slab."""
     import ctypes as C
     from mgg_osdi23_b200 import _lib
     dev = torch.device("cuda")
-    for n, k, m in [(128, 32, 16), (129, 602, 16), (1000, 100, 64), (5000, 64, 47), (77, 16, 41), (40000, 602, 16)]:
+    for n, k, m in [(128, 32, 16), (129, 602, 16), (1000, 100, 64), (5000, 64, 47), (77, 16, 41), (40000, 602, 16),
+                    (3001, 128, 16), (1001, 130, 12), (333, 602, 9), (7, 64, 1), (2050, 100, 128)]:
         x = gg.features(n, k, seed=n).numpy()
         w = gg.glorot_uniform(k, m, seed=k).numpy()
         xd, wd = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
-        a, b = torch.full((n, m), 9.0, device=dev), torch.full((n, m), 9.0, device=dev)
+        a, b, c = (torch.full((n, m), 9.0, device=dev) for _ in range(3))
         mgg.dense_forward(a, xd, wd)
         mgg.dense_forward(b, xd, wd, flags=_lib.DENSE_SIMT)
+        mgg.dense_forward(c, xd, wd, flags=_lib.DENSE_TENSOR)
         torch.cuda.synchronize()
         status = C.c_int(-1)
         _lib.check(_lib.lib.mggb_dense_device_status(C.byref(status), 1))
@@ -77,6 +80,7 @@ def test_tensor_core_kernel_reports_clean_status_and_matches_cuda_core_kernel(or
         want = oracle.dense(x, w)
         np.testing.assert_allclose(a.cpu().numpy(), want, rtol=RTOL, atol=ATOL, err_msg=str((n, k, m)))
         np.testing.assert_allclose(b.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(c.cpu().numpy(), want, rtol=RTOL, atol=ATOL, err_msg=str((n, k, m)))
         np.testing.assert_allclose(a.cpu().numpy(), b.cpu().numpy(), rtol=RTOL, atol=2e-5)
 
 
@@ -136,10 +140,12 @@ def test_dense_output_and_publish_views_at_odd_float_offsets(oracle, n, k, m):
         out = raw_o[off_out:off_out + n * m].view(n, m)
         pub = raw_p[off_pub:off_pub + n * m].view(n, m)
         assert out.data_ptr() % 16 == (4 * off_out) % 16
-        mgg.dense_forward(out, xd, wd, publish=[pub])
-        torch.cuda.synchronize()
-        np.testing.assert_allclose(out.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
-        assert torch.equal(out, pub)
+        for flags in (0, mgg._lib.DENSE_TENSOR):
+            out.zero_(); pub.zero_()
+            mgg.dense_forward(out, xd, wd, publish=[pub], flags=flags)
+            torch.cuda.synchronize()
+            np.testing.assert_allclose(out.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+            assert torch.equal(out, pub)
         assert float(raw_o[:off_out].abs().sum()) == 0.0 and float(raw_o[off_out + n * m:].abs().sum()) == 0.0
     st = mgg._lib.C.c_int(-1)
     mgg._lib.check(mgg._lib.lib.mggb_dense_device_status(mgg._lib.C.byref(st), 0))
@@ -161,7 +167,7 @@ def test_single_pass_tf32_mode(oracle, n, k, m):
     fast = torch.empty(n, m, device=dev)
     mgg.dense_forward(fast, xd, wd, flags=mgg._lib.DENSE_TF32)
     full = torch.empty(n, m, device=dev)
-    mgg.dense_forward(full, xd, wd)
+    mgg.dense_forward(full, xd, wd, flags=mgg._lib.DENSE_TENSOR)
     torch.cuda.synchronize()
     err_fast = np.abs(fast.cpu().numpy() - want)
     assert np.all(err_fast <= 2e-3 * mag + 1e-6)
