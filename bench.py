@@ -535,8 +535,10 @@ def run_ours(args, rank, world, local_rank):
     x_dev = gg.features(shard.rows, din, seed=1, device=dev, first_row=shard.lb)
     if model_kind == "agg" and norm == "sym":
         x_dev = x_dev * shard.inv_sqrt_degree()[:, None]
-    x_host = torch.empty(x_dev.shape, dtype=torch.float32, pin_memory=True)
-    x_host.copy_(x_dev)
+    x_host = None
+    if not args.no_e2e:                          # the host copy of the features, for the end-to-end leg only
+        x_host = torch.empty(x_dev.shape, dtype=torch.float32, pin_memory=True)
+        x_host.copy_(x_dev)
     naggs = {"agg": 1, "gcn2": 2, "gin5": 5}[model_kind]
     total_edges = g_edges
 
