@@ -66,9 +66,9 @@ enum {
     MGGB_DENSE_RELU = 1,      /* clamp the result at 0 (the reference's timed path has no activation) */
     MGGB_DENSE_TF32 = 2,      /* single-pass TF32 tensor-core product (about 1e-3 relative) */
     MGGB_DENSE_SIMT = 4,      /* no tensor cores: the fp32 CUDA-core kernels only */
-    MGGB_DENSE_TENSOR = 8     /* the tensor-core kernel also for outputs of at most 16 columns, which by default go to a
-                                 CUDA-core kernel that streams x row by row (faster there: 2*dim2 flops per loaded float
-                                 is within the fp32 pipes' reach, and whole rows are read front to back) */
+    MGGB_DENSE_TENSOR = 8     /* the tensor-core kernel also where the default is a CUDA-core kernel that streams x row by
+                                 row: outputs of at most 16 columns from rows whose stride is not a multiple of 16 bytes
+                                 (602 floats), which TMA cannot load and a slab-wise walk reads at a third of HBM's rate */
 };
 
 #define MGGB_MAX_PES 16

@@ -122,7 +122,7 @@ int dense_simt(float* out, const float* x, const float* w, int64_t n, int dim1, 
 // Row-streaming CUDA-core kernel for outputs of at most 16 columns (dense_rowstream.cu) and the
 // tensor-core kernel (dense_tc.cu); each sets *launched = false when the shape does not fit it.
 int dense_rowstream(float* out, const float* x, const float* w, int64_t n, int dim1, int dim2, const float* row_scale,
-                    int flags, float* const* publish_out, int num_publish, cudaStream_t st, bool* launched);
+                    int flags, float* const* publish_out, int num_publish, cudaStream_t st, bool even_if_aligned, bool* launched);
 int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, int dim2, const float* row_scale,
              int flags, float* const* publish_out, int num_publish, cudaStream_t st, bool* launched);
 
@@ -138,11 +138,12 @@ extern "C" int mggb_dense_forward(float* out, const float* x, const float* w, in
     MGGB_REQUIRE(n >= 0 && dim1 >= 1 && dim2 >= 1, "dense_forward: need n >= 0, dim1 >= 1, dim2 >= 1 (n=%lld dim1=%d dim2=%d)", (long long)n, dim1, dim2);
     MGGB_REQUIRE(out != x, "dense_forward: out must not alias x");
     if (n == 0) return MGGB_OK;
-    // Narrow outputs: the row-streaming kernel (fp32 FMA) unless the caller asked for tensor cores.
+    // Narrow outputs from rows that no tensor map takes (stride not a multiple of 16 bytes): the row-streaming
+    // kernel (fp32 FMA), unless the caller asked for tensor cores.  With MGGB_DENSE_SIMT it also takes aligned rows.
     if (!(flags & (MGGB_DENSE_TENSOR | MGGB_DENSE_TF32))) {
         bool launched = false;
         const int st = mggb::dense_rowstream(out, x, w, n, dim1, dim2, row_scale, flags, publish_out, num_publish,
-                                             (cudaStream_t)stream, &launched);
+                                             (cudaStream_t)stream, (flags & MGGB_DENSE_SIMT) != 0, &launched);
         if (st != MGGB_OK || launched) return st;
     }
     if (!(flags & MGGB_DENSE_SIMT)) {

@@ -21,7 +21,8 @@
 //              engine); warps 0-7 split the landed slab in place.
 //     other even dim1 (Reddit-shaped rows: 602 floats = 2408 bytes, which no tensor map takes):
 //              warps 0-7 load 8-byte pieces into registers, several slabs ahead, and write hi/lo.
-//     (MGGB_DENSE_CP_ASYNC at build time: the earlier cp.async loader / splitter pair for aligned rows.)
+//     (aligned rows on a driver that cannot encode a tensor map: warps 0-3 cp.async 16-byte pieces, warps
+//     4-7 split what landed.)
 //   warp 12    allocates tensor memory; one lane issues tcgen05.mma (M=128, N=pad16(M), K=8 per
 //              instruction, 4 k-steps x 4 partial products per slab) and commits to mbarriers.
 //   warps 8-11 epilogue: tcgen05.ld the 128 x N accumulator (double-buffered in tensor memory), apply
@@ -48,10 +49,7 @@ constexpr int STAGE_BYTES = 2 * SLAB_BYTES;  // hi + lo
 constexpr int LOADERS = 128;              // warps 0-3 copy slabs, warps 4-7 split them (same piece mapping)
 constexpr int LOADER_WARPS = LOADERS / 32;
 constexpr int THREADS = 2 * LOADERS + 128 + 32;  // + 4 epilogue warps + the MMA warp
-#ifndef MGGB_DENSE_STAGES
-#define MGGB_DENSE_STAGES 4
-#endif
-constexpr int MAX_STAGES = MGGB_DENSE_STAGES;
+constexpr int MAX_STAGES = 4;               // ring depth (fewer when w leaves less room)
 // Which warps bring x in: register-staged producers for 8-byte pieces, the cp.async loader/splitter
 // pair for 16-byte pieces (each measured faster on its shapes, see producer_role).
 template <int G> struct UseProducer { static constexpr bool value = (G == 8); };
@@ -269,10 +267,7 @@ __device__ void splitter_role(const TcParams& P, unsigned char* ring, uint32_t l
 // would be issued only after the earlier one had returned.  PIPE - 1 slabs (16 KiB each) are in
 // flight per SM while one is being split.
 constexpr int PRODUCERS = 2 * LOADERS;
-#ifndef MGGB_DENSE_PIPE
-#define MGGB_DENSE_PIPE 4
-#endif
-constexpr int PIPE = MGGB_DENSE_PIPE;
+constexpr int PIPE = 4;
 
 template <int G> struct PVec;
 template <> struct PVec<16> { using T = float4; };
@@ -708,7 +703,6 @@ int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, in
     const bool wide = (dim1 % 4 == 0) && ((uintptr_t)x % 16 == 0);
     CUtensorMap tmap;
     memset(&tmap, 0, sizeof(tmap));
-#ifndef MGGB_DENSE_CP_ASYNC
     if (wide && encode_tiled() != nullptr) {
         // x as a 2-D tensor [n rows][dim1 floats] (row stride dim1 * 4 bytes, a multiple of 16); one box = one slab
         const cuuint64_t gdim[2] = {(cuuint64_t)dim1, (cuuint64_t)n};
@@ -722,9 +716,7 @@ int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, in
             return mggb::fail(MGGB_ERR_CUDA, "dense_forward: cuTensorMapEncodeTiled failed with CUresult %d (n=%lld dim1=%d)", (int)r, (long long)n, dim1);
         MGGB_CUDA(cudaFuncSetAttribute(dense_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         dense_tc_kernel<0><<<grid, TMA_THREADS, smem, st>>>(P, tmap);
-    } else
-#endif
-    if (wide) {
+    } else if (wide) {      // a driver without the tensor-map entry point: the cp.async loader / splitter pair
         MGGB_CUDA(cudaFuncSetAttribute(dense_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         dense_tc_kernel<16><<<grid, THREADS, smem, st>>>(P, tmap);
     } else {

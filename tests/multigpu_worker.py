@@ -30,7 +30,8 @@ def main():
     w1, w2 = gg.glorot_uniform(din, hid, 1), gg.glorot_uniform(hid, dout, 2)
     sh = drivers.Shard(rp, col, rank, world, device=dev)
     assert world == 1 or sh.e_remote > 0
-    barrier = drivers.nccl_stream_barrier()
+    nccl_barrier = drivers.nccl_stream_barrier()
+    barrier = drivers.FlagBarrier(None, rank, world)       # epoch flags in peer memory: the two-sided wait on real peers
     xh = torch.from_numpy(x[sh.lb:sh.ub].copy()).pin_memory()
     dinv = orc.inv_sqrt_degree(rp)
     agg = lambda t: orc.row_scale(orc.sag_f64(orc.row_scale(t, dinv), rp, col), dinv)
@@ -45,7 +46,37 @@ def main():
         for _ in range(3):                   # repeated passes exercise the buffer alternation
             probs = m.forward_host(xh, barrier)
         np.testing.assert_allclose(probs.numpy(), want[sh.lb:sh.ub], rtol=1e-5, atol=1e-4)
+        probs = m.forward_host(xh, nccl_barrier)                 # and once with the all-reduce barrier
+        np.testing.assert_allclose(probs.numpy(), want[sh.lb:sh.ub], rtol=1e-5, atol=1e-4)
         barrier()
+    assert barrier.status() == 0, "a flag-barrier wait expired"
+
+    # 5-layer GIN with the third published buffer: back-to-back passes with DIFFERENT inputs and no barrier
+    # between passes; every pass must match the oracle for its own input
+    ws = [gg.glorot_uniform(din, 64, 10) * 0.1] + [gg.glorot_uniform(64, 64, 11 + k) * 0.1 for k in range(4)] + [gg.glorot_uniform(64, dout, 20) * 0.1]
+    for make in (lambda: SymmetricBuffer(sh.node_per_pe * 64, None, rank, world), lambda: ReplicaBuffer(sh.node_per_pe, 64, None, rank, world)):
+        bufs = [make() for _ in range(3)]
+        gin = drivers.GIN5Forward(sh, din, 64, dout, bufs[0], bufs[1], drivers.Knobs(8, 2, 2), eps=0.0, weights=[w.to(dev) for w in ws], sym_c=bufs[2])
+        gin.keep_logits = True
+        assert not gin.leading_barrier
+        inputs = [x, gg.features(n, din, seed=33).numpy(), x]
+        got = []
+        for xi in inputs:
+            gin.d_in.copy_(torch.from_numpy(xi[sh.lb:sh.ub].copy()).to(dev), non_blocking=True)
+            gin.forward(barrier)
+            got.append(gin.logits.clone())
+        torch.cuda.synchronize()
+        for xi, g_ in zip(inputs, got):
+            h = orc.dense(xi, ws[0].numpy())
+            for k in range(5):
+                h = orc.dense((orc.sag_f64(h, rp, col).astype(np.float64) + h).astype(np.float32), ws[k + 1].numpy())
+            scale = max(1.0, float(np.abs(h).max()))
+            np.testing.assert_allclose(g_.cpu().numpy() / scale, h[sh.lb:sh.ub] / scale, rtol=1e-4, atol=1e-4)
+        barrier()
+        torch.cuda.synchronize(); dist.barrier()
+        for b_ in bufs:
+            b_.close()
+    assert barrier.status() == 0, "a flag-barrier wait expired"
 
     # single aggregation, dim 64, GIN combine
     sc = SymmetricBuffer(sh.node_per_pe * 64, None, rank, world)
@@ -61,6 +92,7 @@ def main():
     torch.cuda.synchronize()
     for s in (sa, sb, sc, ra, rb):
         s.close()
+    barrier.close()
     dist.destroy_process_group()
     print(f"rank {rank}/{world} ok: local {sh.e_local} remote {sh.e_remote} edges")
 
