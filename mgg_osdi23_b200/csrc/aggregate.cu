@@ -172,9 +172,14 @@ __device__ __forceinline__ void group_gather_list(float4& acc, const AggParams& 
                                                   const int32_t* __restrict__ ci, int beg, int end,
                                                   const char* base, bool remote, int l, unsigned group_mask) {
     const unsigned row_bytes = 64u;
-    // every group of the warp keeps stepping until the longest list among them is done
+    // every group of the warp keeps stepping until the longest list among them is done.  The ids of
+    // step t+1 are requested before the rows of step t, so the two dependent latencies (id, then row)
+    // of consecutive steps overlap instead of adding up.
+    int nxt = (beg + l < end) ? __ldcs(ci + beg + l) : -1;
     for (int e = beg; __any_sync(0xffffffffu, e < end); e += GROUP_LANES) {
-        const int my = (e + l < end) ? __ldcs(ci + e + l) : -1;
+        const int my = nxt;
+        const int en = e + GROUP_LANES;
+        nxt = (en + l < end) ? __ldcs(ci + en + l) : -1;
         float4 v[GROUP_LANES];
         bool ok[GROUP_LANES];
 #pragma unroll

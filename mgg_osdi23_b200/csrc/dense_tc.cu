@@ -36,6 +36,7 @@
 #include "common.h"
 
 namespace mggb {
+int dense_rowstream_status(int* status, int reset);
 int dense_simt(float* out, const float* x, const float* w, int64_t n, int dim1, int dim2,
                const float* row_scale, int flags, float* const* publish_out, int num_publish, cudaStream_t st);
 }
@@ -414,7 +415,9 @@ __device__ void tma_splitter_role(const TcParams& P, unsigned char* ring, uint32
                 h[e] = __uint_as_float(__float_as_uint(f[e]) & TF32_MASK);
                 l[e] = __uint_as_float(__float_as_uint(f[e] - h[e]) & TF32_MASK);
             }
-            *reinterpret_cast<float4*>(stage + off0 + i * SMEM_STEP) = *reinterpret_cast<float4*>(h);
+            // The hi half is NOT written back: the slab holds the raw fp32 values and the tensor core reads a
+            // TF32 operand from the upper 19 bits of each 32-bit container, ignoring the lower 13: the
+            // truncation that h stands for.  Only the lo half (the exact remainder v - h) is stored.
             if (!P.tf32) *reinterpret_cast<float4*>(stage + SLAB_BYTES + off0 + i * SMEM_STEP) = *reinterpret_cast<float4*>(l);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
@@ -737,5 +740,9 @@ extern "C" int mggb_dense_device_status(int* status, int reset) {
         const int zero = 0;
         MGGB_CUDA(cudaMemcpyToSymbol(g_dense_status, &zero, sizeof(int)));
     }
+    int rs = 0;
+    const int rc = mggb::dense_rowstream_status(&rs, reset);
+    if (rc != MGGB_OK) return rc;
+    if (*status == 0 && rs != 0) *status = 16 + rs;      // the row-streaming kernel's waits
     return MGGB_OK;
 }
