@@ -329,8 +329,7 @@ int mggb_agg_device_status(int* status, int reset);
 /* Reads (and with reset != 0 clears) the status word of the tensor-core dense kernel on the current
  * device; synchronises the device.  0 = every launch so far ran to completion; 1..4 = a bounded wait
  * inside the kernel expired (1 input slab, 2 free slab, 3 accumulator ready, 4 accumulator free) and
- * that launch returned early with an incomplete output; 17 / 18 = the same for the row-streaming kernel's
- * waits (staged rows, free stage).  The reference has no counterpart (cuBLAS
+ * that launch returned early with an incomplete output.  The reference has no counterpart (cuBLAS
  * reports nothing from the device). */
 int mggb_dense_device_status(int* status, int reset);
 

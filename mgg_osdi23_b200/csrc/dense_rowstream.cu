@@ -18,14 +18,10 @@
 // finish the job (not 5 per sum) and lane L ends up with outputs 2L and 2L+1 of the R x 16 block, which
 // it stores as one 8-byte piece: the warp's store is one contiguous run of R rows.
 //
-// Two ways of bringing the rows in.  dense_rowstream_bulk_kernel (x 16-byte aligned): a ninth warp asks
-// the copy engine for the block's next 32 rows - ONE contiguous range of 32 * dim1 floats, in 8 KiB
-// bulk copies that complete on an mbarrier - into a two- or more-stage ring in shared memory while the
-// eight computing warps multiply the previous 32 rows out of it: 77 KiB per stage in flight per SM at
-// dim1 = 602, against the 32 KiB that register prefetching reaches.  No tensor map, no multicast, this
-// GPU's memory only; waits are bounded and report through mggb_dense_device_status.
-// dense_rowstream_kernel (any 8-byte aligned x): the lanes load their floats into registers, two
-// steps ahead.
+// The lanes load their floats into registers two steps ahead (three buffers in rotation).  A variant that
+// had a ninth warp stage the block's next 32 rows in shared memory with bulk copies (77 KiB in flight per
+// SM) was measured slower (0.27 ms against 0.22 ms on 232,965 x 602 -> 16): one block of eight computing
+// warps per SM does not keep the FMA pipes as busy as sixteen warps with their rows in registers.
 #include <algorithm>
 #include "common.h"
 
@@ -160,176 +156,9 @@ dense_rowstream_kernel(float* __restrict__ out, const float* __restrict__ x, con
 }
 
 
-// ---- rows staged by bulk copies -------------------------------------------------------------------
-
-constexpr int BULK_WARPS = RS_THREADS / 32;          // computing warps; one more warp issues the copies
-constexpr int BULK_ROWS = 4 * BULK_WARPS;            // rows per ring stage
-constexpr int BULK_MAX_STAGES = 4;
-constexpr unsigned BULK_PIECE = 8192;                // bytes per bulk copy
-constexpr unsigned BULK_SPIN = 1u << 22;
-
-__device__ int g_rowstream_status = 0;               // 0 ok; 1 = a wait for staged rows expired, 2 = a wait for a free stage expired
-
-__device__ __forceinline__ uint32_t rs_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ bool rs_wait(uint32_t bar, unsigned parity) {
-    for (unsigned i = 0; i < BULK_SPIN; i++) {
-        unsigned ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-
-// Dynamic shared memory: [w in lane order][stages x BULK_ROWS rows of K floats].  The block's stage j
-// holds rows (blockIdx.x + j * gridDim.x) * BULK_ROWS ... of x.
-template <int VEC>
-__global__ void __launch_bounds__(RS_THREADS + 32, 1)
-dense_rowstream_bulk_kernel(float* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w, long long n, int K, int M,
-                            const float* __restrict__ row_scale, int relu, int steps, int stages, const Publish pub) {
-    using V = typename XVec<VEC>::T;
-    constexpr int R = 4;
-    extern __shared__ __align__(128) unsigned char rs_raw[];
-    __shared__ __align__(8) unsigned long long s_full[BULK_MAX_STAGES], s_empty[BULK_MAX_STAGES];
-    float4* Wt = reinterpret_cast<float4*>(rs_raw);
-    const size_t w_bytes = ((size_t)steps * VEC * 4 * 32 * sizeof(float4) + 127) & ~(size_t)127;
-    const size_t stage_bytes = ((size_t)BULK_ROWS * K * sizeof(float) + 127) & ~(size_t)127;
-    unsigned char* ring = rs_raw + w_bytes;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    for (int idx = threadIdx.x; idx < steps * VEC * 4 * 32; idx += RS_THREADS + 32) {
-        const int l = idx & 31, g = (idx >> 5) & 3, ie = idx >> 7;
-        const int i = ie / VEC, e = ie - i * VEC;
-        const int k = (i * 32 + l) * VEC + e;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (k < K) {
-            const float* src = w + (long long)k * M + 4 * g;
-            if (4 * g + 0 < M) v.x = __ldg(src + 0);
-            if (4 * g + 1 < M) v.y = __ldg(src + 1);
-            if (4 * g + 2 < M) v.z = __ldg(src + 2);
-            if (4 * g + 3 < M) v.w = __ldg(src + 3);
-        }
-        Wt[idx] = v;
-    }
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < stages; s++) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(rs_smem(&s_full[s])));
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(rs_smem(&s_empty[s])), "r"(BULK_WARPS));
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-
-    const long long groups = (n + BULK_ROWS - 1) / BULK_ROWS;          // 32-row groups of the matrix
-    const long long mine = blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-
-    if (warp == BULK_WARPS) {
-        // the copy warp: group j of this block into stage j % stages, as soon as that stage is free
-        for (long long j = 0; j < mine; j++) {
-            const int s = (int)(j % stages);
-            if (j >= stages && !rs_wait(rs_smem(&s_empty[s]), (unsigned)((j / stages - 1) & 1))) { atomicCAS(&g_rowstream_status, 0, 2); break; }
-            const long long row0 = (blockIdx.x + j * gridDim.x) * BULK_ROWS;
-            const long long bytes = min((long long)BULK_ROWS, n - row0) * K * 4;     // a multiple of 8 (K is even)
-            const long long bulk = bytes & ~15LL;
-            const char* src = reinterpret_cast<const char*>(x + row0 * K);
-            unsigned char* dst = ring + (size_t)s * stage_bytes;
-            const uint32_t bar = rs_smem(&s_full[s]);
-            if (lane == 0)
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((unsigned)bulk) : "memory");
-            __syncwarp();
-            for (long long off = (long long)lane * BULK_PIECE; off < bulk; off += 32LL * BULK_PIECE) {
-                const unsigned sz = (unsigned)min((long long)BULK_PIECE, bulk - off);
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                             ::"r"(rs_smem(dst + off)), "l"(src + off), "r"(sz), "r"(bar) : "memory");
-            }
-        }
-        return;
-    }
-
-    for (long long j = 0; j < mine; j++) {
-        const int s = (int)(j % stages);
-        const long long row0 = (blockIdx.x + j * gridDim.x) * BULK_ROWS + warp * R;
-        const long long grp_rows = min((long long)BULK_ROWS, n - (blockIdx.x + j * gridDim.x) * BULK_ROWS);
-        const bool arrived = rs_wait(rs_smem(&s_full[s]), (unsigned)((j / stages) & 1));
-        if (!__all_sync(0xffffffffu, arrived)) { atomicCAS(&g_rowstream_status, 0, 1); return; }
-        const float* stage = reinterpret_cast<const float*>(ring + (size_t)s * stage_bytes);
-        // the last 8 bytes of a group whose size is not a multiple of 16 come from global memory directly
-        const long long grp_floats = grp_rows * K;
-        const bool odd_tail = (grp_floats & 3) != 0;
-
-        float acc[RS_COLS * 8];
-#pragma unroll
-        for (int q = 0; q < RS_COLS * R; q++) acc[q] = 0.f;
-#pragma unroll 2
-        for (int i = 0; i < steps; i++) {
-            const int k0 = (i * 32 + lane) * VEC;
-            V xv[R];
-#pragma unroll
-            for (int r = 0; r < R; r++) {
-                V v = V{};
-                const long long lr = warp * R + r;                     // row inside the group
-                if (k0 < K && lr < grp_rows) {
-                    const long long f = lr * K + k0;                   // float offset inside the group
-                    if (odd_tail && f + VEC > (grp_floats & ~3LL)) v = *reinterpret_cast<const V*>(x + (row0 - warp * R) * K + f);
-                    else v = *reinterpret_cast<const V*>(stage + f);
-                }
-                xv[r] = v;
-            }
-#pragma unroll
-            for (int e = 0; e < VEC; e++) {
-#pragma unroll
-                for (int g = 0; g < 4; g++) {
-                    const float4 wv = Wt[((i * VEC + e) * 4 + g) * 32 + lane];
-#pragma unroll
-                    for (int r = 0; r < R; r++) {
-                        const float a = reinterpret_cast<const float*>(&xv[r])[e];
-                        acc[r * RS_COLS + 4 * g + 0] = fmaf(a, wv.x, acc[r * RS_COLS + 4 * g + 0]);
-                        acc[r * RS_COLS + 4 * g + 1] = fmaf(a, wv.y, acc[r * RS_COLS + 4 * g + 1]);
-                        acc[r * RS_COLS + 4 * g + 2] = fmaf(a, wv.z, acc[r * RS_COLS + 4 * g + 2]);
-                        acc[r * RS_COLS + 4 * g + 3] = fmaf(a, wv.w, acc[r * RS_COLS + 4 * g + 3]);
-                    }
-                }
-            }
-        }
-        __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(rs_smem(&s_empty[s])) : "memory");
-
-        fold<64>(acc, lane, 16);
-        fold<32>(acc, lane, 8);
-        fold<16>(acc, lane, 4);
-        fold<8>(acc, lane, 2);
-        fold<4>(acc, lane, 1);
-        const int f = 2 * lane;                                      // flat element of the warp's 4 x 16 block
-        const long long row = row0 + f / RS_COLS;
-        const int c = f % RS_COLS;
-        if (row < n) {
-            const float sc = row_scale ? row_scale[row] : 1.f;
-            float v0 = acc[0] * sc, v1 = acc[1] * sc;
-            if (relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
-            const long long o = row * M + c;
-            if (c < M) { out[o] = v0; for (int q = 0; q < pub.n; q++) pub.dst[q][o] = v0; }
-            if (c + 1 < M) { out[o + 1] = v1; for (int q = 0; q < pub.n; q++) pub.dst[q][o + 1] = v1; }
-        }
-    }
-}
-
 }  // namespace
 
 namespace mggb {
-
-// Status of the bulk-copy row-streaming kernel on the current device (0 ok), for mggb_dense_device_status.
-int dense_rowstream_status(int* status, int reset) {
-    MGGB_CUDA(cudaMemcpyFromSymbol(status, g_rowstream_status, sizeof(int)));
-    if (reset) {
-        const int zero = 0;
-        MGGB_CUDA(cudaMemcpyToSymbol(g_rowstream_status, &zero, sizeof(int)));
-    }
-    return MGGB_OK;
-}
 
 // *launched = false (and MGGB_OK) when the shape is not served: dim2 > 16, odd dim1, x not 8-byte
 // aligned, or w too large for shared memory.  `even_if_aligned`: also take rows whose stride is a
@@ -350,29 +179,6 @@ int dense_rowstream(float* out, const float* x, const float* w, int64_t n, int d
     Publish pub{};
     pub.n = num_publish;
     for (int q = 0; q < num_publish; q++) pub.dst[q] = publish_out[q];
-    // rows staged by bulk copies when x is 16-byte aligned and at least two stages of 32 rows fit beside w
-    if (((uintptr_t)x % 16) == 0) {
-        const size_t w_bytes = (smem + 127) & ~(size_t)127;
-        const size_t stage_bytes = ((size_t)BULK_ROWS * dim1 * sizeof(float) + 127) & ~(size_t)127;
-        const size_t room = 220 * 1024 > w_bytes ? 220 * 1024 - w_bytes : 0;
-        const int stages = (int)std::min<size_t>(BULK_MAX_STAGES, room / stage_bytes);
-        if (stages >= 2) {
-            const size_t total = w_bytes + (size_t)stages * stage_bytes;
-            const long long groups32 = (n + BULK_ROWS - 1) / BULK_ROWS;
-            const int grid32 = (int)std::min<long long>(groups32, mggb::sm_count());
-            const int relu32 = (flags & MGGB_DENSE_RELU) ? 1 : 0;
-            if (wide) {
-                MGGB_CUDA(cudaFuncSetAttribute(dense_rowstream_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)total));
-                dense_rowstream_bulk_kernel<4><<<grid32, RS_THREADS + 32, total, st>>>(out, x, w, n, dim1, dim2, row_scale, relu32, steps, stages, pub);
-            } else {
-                MGGB_CUDA(cudaFuncSetAttribute(dense_rowstream_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)total));
-                dense_rowstream_bulk_kernel<2><<<grid32, RS_THREADS + 32, total, st>>>(out, x, w, n, dim1, dim2, row_scale, relu32, steps, stages, pub);
-            }
-            MGGB_CUDA(cudaGetLastError());
-            *launched = true;
-            return MGGB_OK;
-        }
-    }
     constexpr int R = 4;
     const long long groups = (n + R - 1) / R;
     const long long blocks = (groups + RS_THREADS / 32 - 1) / (RS_THREADS / 32);

@@ -36,7 +36,6 @@
 #include "common.h"
 
 namespace mggb {
-int dense_rowstream_status(int* status, int reset);
 int dense_simt(float* out, const float* x, const float* w, int64_t n, int dim1, int dim2,
                const float* row_scale, int flags, float* const* publish_out, int num_publish, cudaStream_t st);
 }
@@ -740,9 +739,5 @@ extern "C" int mggb_dense_device_status(int* status, int reset) {
         const int zero = 0;
         MGGB_CUDA(cudaMemcpyToSymbol(g_dense_status, &zero, sizeof(int)));
     }
-    int rs = 0;
-    const int rc = mggb::dense_rowstream_status(&rs, reset);
-    if (rc != MGGB_OK) return rc;
-    if (*status == 0 && rs != 0) *status = 16 + rs;      // the row-streaming kernel's waits
     return MGGB_OK;
 }
