@@ -582,6 +582,15 @@ def run_ours(args, rank, world, local_rank):
 
     fetch = "both" if args.fetch == "auto" else args.fetch
     mode_names = ["single"] if world == 1 else {"both": ["pull", "push"], "peer": ["pull"], "replica": ["push"]}[fetch]
+    # Pull mode over several GB of peer memory is not timed unless asked for (--fetch peer): on 8 GPUs the
+    # 111 M-node graph's remote rows (6.2 GB of peers' buffers, touched 64 bytes at a time at random) came in
+    # at 0.1 G rows/s per GPU, 6.9 s per pass against 41 ms in push mode.
+    pull_skipped = None
+    remote_span = (world - 1) * npp * hid * 4
+    if fetch == "both" and world > 1 and remote_span > (2 << 30):
+        mode_names = ["push"]
+        pull_skipped = (f"not timed by default: {remote_span / 1e9:.1f} GB of peers' buffers read 4*{hid} bytes at a time at random "
+                        "(measured on 8 GPUs at full size: 6.9 s per pass; pass --fetch peer to time it)")
     agg_events = []
     results = {}
     sampler = ClockSampler(local_rank)
@@ -780,7 +789,8 @@ def run_ours(args, rank, world, local_rank):
             "check": r["check"],
             "fetch": {"single": "single GPU, no peers", "pull": "peer (rows pulled inside the aggregation kernel)",
                       "push": "replica (rows pushed by the producing kernel)"}[best],
-            "modes": {m: mode_summary(m) for m in results} if world > 1 else None,
+            "modes": (dict({m: mode_summary(m) for m in results}, **({"pull": {"skipped": pull_skipped}} if pull_skipped else {}))
+                      if world > 1 else None),
             "barrier": (args.barrier if world > 1 else None),
             "dense_kernel": "cuda-core" if args.dense == "simt" else "tcgen05 where the shape fits",
             "overlap_blocks": r["overlap_blocks"],

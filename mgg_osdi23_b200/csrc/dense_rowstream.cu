@@ -77,6 +77,8 @@ dense_rowstream_kernel(float* __restrict__ out, const float* __restrict__ x, con
     }
     __syncthreads();
 
+    bool pair_ok = (M == RS_COLS) && ((uintptr_t)out % 8 == 0);
+    for (int q = 0; q < pub.n; q++) pair_ok = pair_ok && ((uintptr_t)pub.dst[q] % 8 == 0);
     const long long warps = ((long long)gridDim.x * RS_THREADS) >> 5;
     const long long groups = (n + R - 1) / R;
     for (long long grp = (((long long)blockIdx.x * RS_THREADS + threadIdx.x) >> 5); grp < groups; grp += warps) {
@@ -149,8 +151,16 @@ dense_rowstream_kernel(float* __restrict__ out, const float* __restrict__ x, con
             float v0 = res[2 * b] * s, v1 = res[2 * b + 1] * s;
             if (relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
             const long long o = row * M + c;
-            if (c < M) { out[o] = v0; for (int q = 0; q < pub.n; q++) pub.dst[q][o] = v0; }
-            if (c + 1 < M) { out[o + 1] = v1; for (int q = 0; q < pub.n; q++) pub.dst[q][o + 1] = v1; }
+            if (pair_ok) {
+                // full-width rows and 8-byte aligned destinations: one 8-byte store per lane, so the warp writes
+                // its R rows as one contiguous run (what a peer's replica wants to receive over NVLink)
+                const float2 v = make_float2(v0, v1);
+                *reinterpret_cast<float2*>(out + o) = v;
+                for (int q = 0; q < pub.n; q++) *reinterpret_cast<float2*>(pub.dst[q] + o) = v;
+            } else {
+                if (c < M) { out[o] = v0; for (int q = 0; q < pub.n; q++) pub.dst[q][o] = v0; }
+                if (c + 1 < M) { out[o + 1] = v1; for (int q = 0; q < pub.n; q++) pub.dst[q][o + 1] = v1; }
+            }
         }
     }
 }
