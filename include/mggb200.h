@@ -9,7 +9,7 @@
  *     validates nothing; mggb_last_error() returns the message of the calling thread's last failure;
  *   - the caller owns every buffer it passes and the library keeps no pointer to one after a call
  *     returns.  The library's own device memory is small and listed where it arises: the hub work
- *     list of the aggregation (1 MiB per device and stream, allocated on first use and kept until the
+ *     lists of the aggregation (17 MiB per device and stream, allocated on first use and kept until the
  *     process exits; mggb_sag_np_div_static allocates nothing) and the barrier's status word;
  *   - device work is enqueued on the given stream (a cudaStream_t passed as void*, NULL = default
  *     stream) of the CURRENT device and is NOT synchronised (the reference synchronises the device
@@ -43,7 +43,11 @@ enum {
     MGGB_AGG_NO_HUB_SPLIT = 2, /* keep every node on its own warp_per_block-warp block, as the reference does.
                                  By default a node with more than max(16384, 64*ps*dist*wpb) neighbors is passed,
                                  through a work list in library-owned device memory (allocated once per device
-                                 and stream, on first use), to a second kernel that gives it a 16-warp block */
+                                 and stream, on first use), to a second kernel that gives it a 16-warp block; a node
+                                 with more than 16384 neighbors is cut there into up to 64 segments of at least 4096
+                                 neighbors, each summed by a block of its own, and the block that finishes last adds
+                                 the segments' partial rows in segment order (no atomics on the data: same bits on
+                                 every call) */
     MGGB_AGG_STAGE_ROWS = 8, /* bring neighbor rows into shared memory with bulk copies (one cp.async.bulk per row into a
                                 per-warp ring, completion on an mbarrier) and add them up from there, instead of
                                 loading them into registers: the rows pulled from peers' buffers when there are any
@@ -277,8 +281,11 @@ int mggb_hub_threshold(int part_size, int warp_per_block, int interleaved_dist, 
  * running inside a memory pool that owns the whole device, a latency-critical loop where an implicit
  * device synchronisation inside cudaMalloc is not acceptable, or a process that is forbidden to
  * grow its footprint after start-up.  This variant computes exactly the same result with the same
- * kernels, but its hub list lives in a fixed array inside the library's device image (32 KiB + a
- * 256-byte header, present on every GPU that loads the library, for the life of the process).  It
+ * kernels, but its work lists live in fixed arrays inside the library's device image (32 KiB + a
+ * 256-byte header for the hub list, 5 KiB for 256 cut rows and 256 KiB for their segments' partial
+ * rows, present on every GPU that loads the library, for the life of the process).  A shard with more
+ * than 256 rows above 16384 neighbors, or more segments than 65536 / dim, leaves the rest whole on the
+ * hub list: same sums, a different fp32 summation order for those rows than mggb_sag_np_div's.  It
  * calls no cudaMalloc / cudaFree and no allocating library routine.
  *
  *   shard_edges  stored edges of this shard (local + remote, what mggb_split_csr_count returned).

@@ -40,16 +40,14 @@ int aggregate_staged(const void* params, int wpb, int remote_mode, int stage, vo
 
 namespace {
 
-// Aggregates one node with all warps of the block and stores its output row.  s_part: nwarps * dim
-// floats of shared memory.  Ends with the block's threads past a __syncthreads() only on entry, so a
-// caller that loops over rows must synchronise before reusing s_part.
+// Sums the neighbor rows of the list ranges [lbeg, lend) (local) and [rbeg, rend) (remote) with all warps of
+// the block: on return (past a __syncthreads()) s_part[w * dim + c] holds warp w's partial sums.
+// s_part: nwarps * dim floats of shared memory.
 template <int LPR, int VEC, bool EXACT, int REMOTE_MODE, int WALK>
-__device__ __forceinline__ void aggregate_row(const AggParams& P, const int row, float* s_part,
-                                              const float* const* s_peer) {
+__device__ __forceinline__ void aggregate_range(const AggParams& P, int lbeg, int lend, int rbeg, int rend,
+                                                float* s_part, const float* const* s_peer) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
-    const int lbeg = P.rp_l[row], lend = P.rp_l[row + 1];
-    const int rbeg = P.rp_r[row], rend = P.rp_r[row + 1];
     const int l = lane % LPR;
     constexpr int COLS = LPR * VEC;  // columns covered per pass
 
@@ -65,8 +63,15 @@ __device__ __forceinline__ void aggregate_row(const AggParams& P, const int row,
         if (lane < LPR && col_ok) acc.store_smem(s_part + warp * P.dim + col);
     }
     __syncthreads();
+}
 
-    store_row(P, row, s_part, nwarps);
+// Aggregates one node with all warps of the block and stores its output row.  A caller that loops over
+// rows must synchronise before reusing s_part.
+template <int LPR, int VEC, bool EXACT, int REMOTE_MODE, int WALK>
+__device__ __forceinline__ void aggregate_row(const AggParams& P, const int row, float* s_part,
+                                              const float* const* s_peer) {
+    aggregate_range<LPR, VEC, EXACT, REMOTE_MODE, WALK>(P, P.rp_l[row], P.rp_l[row + 1], P.rp_r[row], P.rp_r[row + 1], s_part, s_peer);
+    store_row(P, row, s_part, blockDim.x >> 5);
 }
 
 // One block per node.  Dynamic shared memory: nwarps * dim floats (the warps' partial rows).
@@ -88,13 +93,9 @@ __global__ void __launch_bounds__(512, (LPR <= 4 ? MGGB_AGG_MIN_BLOCKS_NARROW : 
     if (P.hub_count != nullptr) {
         const int edges = (P.rp_l[row + 1] - P.rp_l[row]) + (P.rp_r[row + 1] - P.rp_r[row]);
         if (edges > P.hub_min_edges) {
-            if (threadIdx.x == 0) {
-                // handed to the wide-block kernel if the list still has room; otherwise this block
-                // aggregates the row after all (slower, same result)
-                const int slot = atomicAdd(P.hub_count, 1);
-                s_deferred = slot < P.hub_cap;
-                if (slot < P.hub_cap) P.hub_list[slot] = row;
-            }
+            // handed to the wide-block kernel if its lists still have room; otherwise this block
+            // aggregates the row after all (slower, same result)
+            if (threadIdx.x == 0) s_deferred = defer_row(P, row, edges);
             __syncthreads();
             if (s_deferred) return;
         }
@@ -123,11 +124,7 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, (LPR <= 4 ? 6 : 2)) sag_row_pe
     const int rbeg = P.rp_r[row], rend = P.rp_r[row + 1];
     if (P.hub_count != nullptr && (lend - lbeg) + (rend - rbeg) > P.hub_min_edges) {
         int deferred = 0;
-        if (lane == 0) {
-            const int slot = atomicAdd(P.hub_count, 1);
-            deferred = slot < P.hub_cap;
-            if (deferred) P.hub_list[slot] = row;
-        }
+        if (lane == 0) deferred = defer_row(P, row, (lend - lbeg) + (rend - rbeg));
         if (__shfl_sync(0xffffffffu, deferred, 0)) return;
     }
     const int l = lane % LPR;
@@ -223,11 +220,7 @@ __global__ void __launch_bounds__(GROUP_BLOCK, 4) sag_group_per_node_kernel(cons
     // list has room).  The decision is shared with an unconditional group-wide shuffle.
     const bool hub = active && P.hub_count != nullptr && (lend - lbeg) + (rend - rbeg) > P.hub_min_edges;
     int handed = 0;
-    if (hub && l == 0) {
-        const int hs = atomicAdd(P.hub_count, 1);
-        handed = hs < P.hub_cap;
-        if (handed) P.hub_list[hs] = row;
-    }
+    if (hub && l == 0) handed = defer_row(P, row, (lend - lbeg) + (rend - rbeg));
     handed = __shfl_sync(0xffffffffu, handed, 0, GROUP_LANES);
     const bool mine = active && !handed;   // false: nothing to aggregate or store here
     if (!mine) { lbeg = lend = rbeg = rend = 0; }
@@ -251,23 +244,79 @@ __global__ void __launch_bounds__(GROUP_BLOCK, 4) sag_group_per_node_kernel(cons
     for (int k = 0; k < P.num_publish; k++) *reinterpret_cast<float4*>(P.publish[k] + o) = acc;
 }
 
-// Hub rows: a fixed grid of 16-warp blocks walks the list the kernel above filled.  Each listed row
-// is aggregated by ONE block with the same warp/chunk mapping (just more warps), so its result does
-// not depend on the order in which rows were appended.  The next batch of neighbor ids is
+// Hub rows: a fixed grid of 16-warp blocks walks the lists the kernel above filled.  First the segments of
+// the giant rows, one block per segment: the block sums its segment into a partial row in global memory,
+// and the block that finishes a row's last segment adds the row's partial rows in segment order and
+// stores the output row (so the result depends neither on which block came last nor on the order in
+// which rows were appended).  Then the hub list proper: each listed row is aggregated by ONE block with
+// the same warp/chunk mapping as a one-node block (just more warps).  The next batch of neighbor ids is
 // prefetched here: a hub's warps run hundreds of batches back to back.
 template <int LPR, int VEC, bool EXACT, int REMOTE_MODE, int WALK>
 __global__ void __launch_bounds__(512, 2) sag_hub_rows_kernel(const AggParams P) {
     extern __shared__ __align__(16) float s_part[];
     __shared__ const float* s_peer[MGGB_MAX_PES];
+    __shared__ GiantRow s_giant;
+    __shared__ int s_giant_index, s_last;
     if (threadIdx.x < MGGB_MAX_PES) s_peer[threadIdx.x] = P.peer[threadIdx.x < P.num_pes ? threadIdx.x : 0];
+    if (threadIdx.x == 0) s_giant_index = -1;
+    __syncthreads();
+    const int nwarps = blockDim.x >> 5;
+    const int giants = P.giant_rows != nullptr ? min(P.hub_count[1], P.giant_row_cap) : 0;
+    const int items = giants > 0 ? min(P.hub_count[2], P.giant_item_cap) : 0;
+    for (int j = blockIdx.x; j < items; j += gridDim.x) {
+        // whose segment is partial row j?  (entries that did not get their partial rows have row < 0)
+        for (int g = threadIdx.x; g < giants; g += blockDim.x) {
+            const GiantRow r = P.giant_rows[g];
+            if (r.row >= 0 && j >= r.first && j < r.first + r.nseg) { s_giant = r; s_giant_index = g; }
+        }
+        __syncthreads();
+        const int gi = s_giant_index;
+        const GiantRow r = s_giant;
+        __syncthreads();   // everyone has read the match before it is cleared for the next round
+        if (threadIdx.x == 0) s_giant_index = -1;
+        if (gi >= 0) {
+            const int lbeg = P.rp_l[r.row], lend = P.rp_l[r.row + 1];
+            const int rbeg = P.rp_r[r.row], rend = P.rp_r[r.row + 1];
+            // neighbors [a, b) of the row's local list followed by its remote list
+            const long long a = (long long)(j - r.first) * r.seg_edges, b = a + r.seg_edges;
+            const int nl = lend - lbeg, nr = rend - rbeg;
+            const int la = (int)min((long long)nl, a), lb_ = (int)min((long long)nl, b);
+            const int ra = (int)min((long long)nr, max(0LL, a - nl)), rb = (int)min((long long)nr, max(0LL, b - nl));
+            aggregate_range<LPR, VEC, EXACT, REMOTE_MODE, WALK>(P, lbeg + la, lbeg + lb_, rbeg + ra, rbeg + rb, s_part, s_peer);
+            float* mine = P.giant_part + (long long)j * P.dim;
+            for (int c = threadIdx.x; c < P.dim; c += blockDim.x) {
+                float s = 0.f;
+                for (int w = 0; w < nwarps; w++) s += s_part[w * P.dim + c];
+                mine[c] = s;
+            }
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) s_last = (atomicAdd(P.giant_done + gi, 1) == r.nseg - 1);
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                const float* parts = P.giant_part + (long long)r.first * P.dim;
+                for (int c = threadIdx.x; c < P.dim; c += blockDim.x) {
+                    float s = 0.f;
+                    for (int q = 0; q < r.nseg; q++) s += __ldcg(parts + (long long)q * P.dim + c);
+                    finish_element(P, r.row, c, s);
+                }
+                if (threadIdx.x == 0) P.giant_done[gi] = 0;   // zero again for the next call
+            }
+        }
+        __syncthreads();   // s_part, s_giant and s_last are reused
+    }
     __syncthreads();
     const int count = min(*P.hub_count, P.hub_cap);
-    for (int i = blockIdx.x; i < count; i += gridDim.x) {
+    // blocks that took no (or fewer) segments start the list
+    const int shift = items % gridDim.x;
+    for (int i = (blockIdx.x + gridDim.x - shift) % gridDim.x; i < count; i += gridDim.x) {
         aggregate_row<LPR, VEC, EXACT, REMOTE_MODE, WALK>(P, P.hub_list[i], s_part, s_peer);
         __syncthreads();   // s_part is reused by the next row
     }
 }
 
+constexpr int HUB_COUNTERS = 4;   // ints cleared before every call: [0] hub rows, [1] giant rows, [2] partial rows handed out
 constexpr int GROUP_HUB_MIN_EDGES = 1024;   // group-per-node kernel: longer lists would leave one 4-lane group as the kernel's tail
 
 // Neighbor count above which a row is handed to the wide-block kernel, or -1 when these knobs use no
@@ -349,7 +398,7 @@ int launch_walk(const AggParams& P, int wpb, cudaStream_t st) {
     const size_t smem = (size_t)wpb * P.dim * sizeof(float);
     if (smem > 48 * 1024)
         MGGB_CUDA(cudaFuncSetAttribute(sag_np_div_kernel<LPR, VEC, EXACT, REMOTE_MODE, WALK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, sizeof(int), st));
+    if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, HUB_COUNTERS * sizeof(int), st));
     if (wpb == 1 && LPR <= 4)   // wide rows stream from HBM and measured no better this way
         sag_row_per_warp_kernel<LPR, VEC, EXACT, REMOTE_MODE, WALK><<<(P.num_rows + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, st>>>(P);
     else
@@ -368,7 +417,13 @@ int launch_kernel(const AggParams& P, int wpb, cudaStream_t st) {
 
 // Hub work list: per (device, stream) so that calls ordered on one stream reuse it safely and calls
 // on different streams never share one.  Allocated on first use, kept until the process exits.
-struct HubScratch { int* count; int* list; };
+struct HubScratch {
+    int* count; int* list;
+    GiantRow* giant_rows; int* giant_done; float* giant_part;   // giant_rows NULL: giant rows are not cut
+    int giant_row_cap; long long giant_part_floats;
+};
+
+constexpr long long GIANT_PART_FLOATS = 4 << 20;   // 16 MiB of partial rows per (device, stream)
 
 int hub_scratch(cudaStream_t st, HubScratch* out) {
     static std::mutex mu;
@@ -379,9 +434,19 @@ int hub_scratch(cudaStream_t st, HubScratch* out) {
     auto key = std::make_pair(dev, st);
     auto it = table.find(key);
     if (it == table.end()) {
+        // one block: [64 counters][HUB_CAP rows][GIANT_ROWS_CAP descriptors][GIANT_ROWS_CAP counters][partial rows]
+        const size_t ints = 64 + (size_t)HUB_CAP + 4 * (size_t)GIANT_ROWS_CAP + GIANT_ROWS_CAP;
         int* base = nullptr;
-        MGGB_CUDA(cudaMalloc((void**)&base, sizeof(int) * (size_t)(HUB_CAP + 64)));
-        it = table.emplace(key, HubScratch{base, base + 64}).first;
+        MGGB_CUDA(cudaMalloc((void**)&base, sizeof(int) * ints + sizeof(float) * (size_t)GIANT_PART_FLOATS));
+        HubScratch hs{};
+        hs.count = base; hs.list = base + 64;
+        hs.giant_rows = reinterpret_cast<GiantRow*>(base + 64 + HUB_CAP);
+        hs.giant_done = base + 64 + HUB_CAP + 4 * GIANT_ROWS_CAP;
+        hs.giant_part = reinterpret_cast<float*>(base + ints);
+        hs.giant_row_cap = GIANT_ROWS_CAP; hs.giant_part_floats = GIANT_PART_FLOATS;
+        // the segment counters start at zero and every call leaves them at zero
+        MGGB_CUDA(cudaMemset(hs.giant_done, 0, sizeof(int) * GIANT_ROWS_CAP));
+        it = table.emplace(key, hs).first;
     }
     *out = it->second;
     return MGGB_OK;
@@ -390,7 +455,7 @@ int hub_scratch(cudaStream_t st, HubScratch* out) {
 // The group-per-node kernel, then the hub kernel for whatever it deferred.
 int launch_group_per_node(const AggParams& P, cudaStream_t st) {
     const int mode = remote_mode_of(P);
-    if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, sizeof(int), st));
+    if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, HUB_COUNTERS * sizeof(int), st));
     const int grid = (P.num_rows + GROUP_ROWS_PER_BLOCK - 1) / GROUP_ROWS_PER_BLOCK;
     const size_t hub_smem = (size_t)HUB_WARPS * P.dim * sizeof(float);
     if (mode == 0) sag_group_per_node_kernel<0><<<grid, GROUP_BLOCK, 0, st>>>(P);
@@ -453,15 +518,27 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
     // Hub rows get wide blocks unless the caller asked for none, already runs wide blocks, or the wide
     // block's partial rows would not fit in shared memory (then every node stays on its own block).
     P.hub_count = nullptr; P.hub_list = nullptr; P.hub_cap = 0;
+    P.giant_rows = nullptr; P.giant_done = nullptr; P.giant_part = nullptr; P.giant_row_cap = 0; P.giant_item_cap = 0;
+    const HubScratch* scratch = nullptr;
+    HubScratch own{};
     const long long hub_min = hub_threshold(ps, wpb, dist, dim, caller_scratch ? (flags & ~MGGB_AGG_GROUP_PER_NODE) : flags);
     P.hub_min_edges = (int)std::min<long long>(std::max<long long>(hub_min, 0), INT_MAX);
     if (hub_min >= 0 && caller_scratch != nullptr) {
-        P.hub_count = caller_scratch->count; P.hub_list = caller_scratch->list; P.hub_cap = caller_scratch_cap;
+        scratch = caller_scratch;
+        P.hub_cap = caller_scratch_cap;
     } else if (hub_min >= 0) {
-        HubScratch hs;
-        int st_ = hub_scratch((cudaStream_t)stream, &hs);
+        int st_ = hub_scratch((cudaStream_t)stream, &own);
         if (st_ != MGGB_OK) return st_;
-        P.hub_count = hs.count; P.hub_list = hs.list; P.hub_cap = HUB_CAP;
+        scratch = &own;
+        P.hub_cap = HUB_CAP;
+    }
+    if (scratch != nullptr) {
+        P.hub_count = scratch->count; P.hub_list = scratch->list;
+        if (scratch->giant_rows != nullptr) {
+            P.giant_rows = scratch->giant_rows; P.giant_done = scratch->giant_done; P.giant_part = scratch->giant_part;
+            P.giant_row_cap = scratch->giant_row_cap;
+            P.giant_item_cap = (int)std::min<long long>(scratch->giant_part_floats / dim, (long long)GIANT_ROWS_CAP * GIANT_MAX_SEG);
+        }
     }
 
     cudaStream_t st = (cudaStream_t)stream;
@@ -481,7 +558,7 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
     // fetched from the owners' buffers, every list otherwise.
     const int remote_mode = remote_mode_of(P);
     if (vec4 && (flags & MGGB_AGG_STAGE_ROWS)) {
-        if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, sizeof(int), st));
+        if (P.hub_count != nullptr) MGGB_CUDA(cudaMemsetAsync(P.hub_count, 0, HUB_COUNTERS * sizeof(int), st));
         bool launched = false;
         int rc = mggb::aggregate_staged(&P, wpb, remote_mode, remote_mode == 1 ? 1 : 2, st, &launched);
         if (rc != MGGB_OK) return rc;
@@ -510,6 +587,13 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
 // starts 64 ints in (256-byte aligned like the array).
 constexpr int STATIC_HUB_CAP = 8192;
 static __device__ __align__(256) int g_static_hub[64 + STATIC_HUB_CAP];
+// Giant rows of the same entry point: descriptors, segment counters (zero in the image, left at zero by
+// every call) and 256 KiB of partial rows (4096 segments at dim 16, 1024 at dim 64).
+constexpr int STATIC_GIANT_ROWS = 256;
+constexpr int STATIC_GIANT_FLOATS = 64 * 1024;
+static __device__ __align__(16) int g_static_giant_rows[4 * STATIC_GIANT_ROWS];
+static __device__ int g_static_giant_done[STATIC_GIANT_ROWS];
+static __device__ __align__(16) float g_static_giant_part[STATIC_GIANT_FLOATS];
 
 // The array's name is only a host-side handle; the kernels need its device address, which differs
 // per device.  Looked up once per device (with that device current) and cached.
@@ -517,6 +601,9 @@ int static_hub_scratch(HubScratch* out) {
     constexpr int MAX_DEVICES = 64;
     static std::mutex mu;
     static int* base[MAX_DEVICES] = {nullptr};
+    static int* giant_rows[MAX_DEVICES] = {nullptr};
+    static int* giant_done[MAX_DEVICES] = {nullptr};
+    static float* giant_part[MAX_DEVICES] = {nullptr};
     int dev = 0;
     MGGB_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MAX_DEVICES)
@@ -527,10 +614,21 @@ int static_hub_scratch(HubScratch* out) {
         cudaError_t e = cudaGetSymbolAddress((void**)&p, g_static_hub);
         if (e != cudaSuccess || p == nullptr)
             return mggb::fail(MGGB_ERR_CUDA, "sag_np_div_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+        int *rows = nullptr, *done = nullptr;
+        float* part = nullptr;
+        if (cudaGetSymbolAddress((void**)&rows, g_static_giant_rows) != cudaSuccess || cudaGetSymbolAddress((void**)&done, g_static_giant_done) != cudaSuccess ||
+            cudaGetSymbolAddress((void**)&part, g_static_giant_part) != cudaSuccess)
+            return mggb::fail(MGGB_ERR_CUDA, "sag_np_div_static: cudaGetSymbolAddress failed on device %d", dev);
+        giant_rows[dev] = rows; giant_done[dev] = done; giant_part[dev] = part;
         base[dev] = p;
     }
     out->count = base[dev];
     out->list = base[dev] + 64;
+    out->giant_rows = reinterpret_cast<GiantRow*>(giant_rows[dev]);
+    out->giant_done = giant_done[dev];
+    out->giant_part = giant_part[dev];
+    out->giant_row_cap = STATIC_GIANT_ROWS;
+    out->giant_part_floats = STATIC_GIANT_FLOATS;
     return MGGB_OK;
 }
 
@@ -566,7 +664,7 @@ int mggb_sag_np_div_static(float* output, const float* const* peer_input, int nu
         return mggb::fail(MGGB_ERR_UNSUPPORTED,
                           "sag_np_div_static: a shard of %lld edges may hold more than %d hub rows (limit %lld edges at these knobs); "
                           "use mggb_sag_np_div, which sizes its work list on the heap", (long long)shard_edges, STATIC_HUB_CAP, max_edges);
-    HubScratch hs;
+    HubScratch hs{};
     int st = static_hub_scratch(&hs);
     if (st != MGGB_OK) return st;
     return aggregate(output, peer_input, num_pes, row_ptr_l, col_idx_l, row_ptr_r, col_idx_r, lb, ub, dim,

@@ -16,6 +16,16 @@ constexpr int HUB_WARPS = 16;        // warps of a hub row's block
 constexpr int HUB_BLOCKS_PER_SM = 2;  // blocks walking the hub list, per SM of the device
 constexpr int HUB_MIN_EDGES = 16384; // smallest neighbor count treated as a hub (a 4-warp block needs > 100 us for it)
 constexpr int HUB_CAP = 1 << 18;     // list entries: enough for every row above 16384 edges of a 2^32-edge shard
+// Giant rows: one 16-warp block needs about 25 us per 16384 neighbors of 64 bytes, so a row of 10^5 or more
+// neighbors would be the kernel's tail.  Such a row is cut into segments of consecutive neighbors, each
+// summed by a block of its own into a partial row; the block that finishes last adds the partial rows in
+// segment order and stores the output row.
+constexpr int GIANT_MIN_EDGES = 16384;  // rows above this are cut
+constexpr int GIANT_SEG_EDGES = 4096;   // shortest segment
+constexpr int GIANT_MAX_SEG = 64;       // most segments per row (longer rows get longer segments)
+constexpr int GIANT_ROWS_CAP = 1024;    // giant rows per call; further ones stay whole on the hub list
+
+struct GiantRow { int row, first, nseg, seg_edges; };   // partial rows first .. first+nseg-1; row < 0: not taken
 
 struct AggParams {
     float* out;
@@ -45,6 +55,13 @@ struct AggParams {
     int* hub_list;
     int hub_cap;
     int hub_min_edges;
+    // Giant rows (NULL giant_rows = none are cut).  hub_count[1] counts the rows appended, hub_count[2]
+    // the partial rows handed out; giant_done[g] counts row g's finished segments and is zero between calls.
+    GiantRow* giant_rows;
+    int* giant_done;
+    float* giant_part;     // giant_item_cap partial rows of dim floats
+    int giant_row_cap;
+    int giant_item_cap;
 };
 
 enum { MODE_OVERWRITE = 0, MODE_ACCUMULATE = 1, MODE_GIN = 2 };
@@ -208,19 +225,47 @@ inline void make_divider(uint32_t d, unsigned long long* magic, int* shift) {
     *magic = (unsigned long long)(((one << *shift) + d - 1) / d);
 }
 
+// Hands a row with `edges` neighbors (more than hub_min_edges) to the wide-block kernel: as a giant row cut
+// into segments when it is long enough and the tables have room, else whole on the hub list.  Called by
+// ONE thread.  False: no room anywhere, the caller aggregates the row itself.
+__device__ __forceinline__ bool defer_row(const AggParams& P, int row, int edges) {
+    if (P.giant_rows != nullptr && edges > GIANT_MIN_EDGES) {
+        const int seg_edges = max(GIANT_SEG_EDGES, (edges + GIANT_MAX_SEG - 1) / GIANT_MAX_SEG);
+        const int nseg = (edges + seg_edges - 1) / seg_edges;
+        const int g = atomicAdd(P.hub_count + 1, 1);
+        if (g < P.giant_row_cap) {
+            const int first = atomicAdd(P.hub_count + 2, nseg);
+            if (first >= 0 && first + nseg <= P.giant_item_cap) {
+                P.giant_rows[g] = GiantRow{row, first, nseg, seg_edges};
+                return true;
+            }
+            P.giant_rows[g] = GiantRow{-1, 0, 0, 0};   // no partial rows left: the row goes on the hub list whole
+        }
+    }
+    const int slot = atomicAdd(P.hub_count, 1);
+    if (slot < P.hub_cap) P.hub_list[slot] = row;
+    return slot < P.hub_cap;
+}
+
+// One output element: epilogue (row scale, accumulate / GIN combine) and the stores, also to every publish
+// destination.
+__device__ __forceinline__ void finish_element(const AggParams& P, int row, int c, float s) {
+    const long long o = (long long)row * P.dim + c;
+    if (P.row_scale) s *= P.row_scale[row];
+    if (P.mode == MODE_GIN) s += P.self_scale * P.peer[P.pe][o];
+    else if (P.mode == MODE_ACCUMULATE) s += P.out[o];
+    P.out[o] = s;
+    for (int k = 0; k < P.num_publish; k++) P.publish[k][o] = s;
+}
+
 // Single writer per output element: sums the warps' partial rows (s_part[w * dim + c], complete and
 // visible to the block) in warp order, applies the epilogue and stores the row, also to every publish
 // destination.  Called by all threads of the block.
 __device__ __forceinline__ void store_row(const AggParams& P, int row, const float* s_part, int nwarps) {
-    const long long obase = (long long)row * P.dim;
     for (int c = threadIdx.x; c < P.dim; c += blockDim.x) {
         float s = 0.f;
         for (int w = 0; w < nwarps; w++) s += s_part[w * P.dim + c];
-        if (P.row_scale) s *= P.row_scale[row];
-        if (P.mode == MODE_GIN) s += P.self_scale * P.peer[P.pe][obase + c];
-        else if (P.mode == MODE_ACCUMULATE) s += P.out[obase + c];
-        P.out[obase + c] = s;
-        for (int k = 0; k < P.num_publish; k++) P.publish[k][obase + c] = s;
+        finish_element(P, row, c, s);
     }
     // No fence here: the pushed rows only have to be visible to kernels that peers launch after the
     // next barrier, and a kernel's stores are complete, system-wide, when the kernel has finished.

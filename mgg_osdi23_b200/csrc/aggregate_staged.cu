@@ -154,11 +154,7 @@ __global__ void __launch_bounds__(512, 1) sag_staged_kernel(const AggParams P, c
     const int lbeg = P.rp_l[row], lend = P.rp_l[row + 1];
     const int rbeg = P.rp_r[row], rend = P.rp_r[row + 1];
     if (P.hub_count != nullptr && (lend - lbeg) + (rend - rbeg) > P.hub_min_edges) {
-        if (threadIdx.x == 0) {
-            const int slot = atomicAdd(P.hub_count, 1);
-            s_deferred = slot < P.hub_cap;
-            if (slot < P.hub_cap) P.hub_list[slot] = row;
-        }
+        if (threadIdx.x == 0) s_deferred = defer_row(P, row, (lend - lbeg) + (rend - rbeg));
         __syncthreads();
         if (s_deferred) return;      // no copy has been issued yet
     }

@@ -188,6 +188,41 @@ def test_hub_rows_every_epilogue(oracle, G):
     assert torch.equal(a, pub)
 
 
+@pytest.mark.parametrize("dim,G,knobs", [(16, 1, (16, 2, 1)), (16, 3, (32, 1, 1)), (64, 2, (16, 1, 2)), (7, 2, (8, 4, 1)), (128, 1, (16, 4, 2))])
+def test_giant_rows_are_cut_into_segments(oracle, dim, G, knobs):
+    """Rows above 16384 neighbors are summed segment by segment by several blocks (up to 64 segments per
+    row); the sums agree with the oracle for every epilogue and are the same bits on every call and for
+    every order in which the blocks take the rows."""
+    n = 900
+    hubs = [(0, 300_000), (1, 64 * 4096 + 1), (450, 16385), (451, 16384), (899, 70_000), (5, 20_000), (6, 0)]
+    rp, col = random_graph(n, 12, seed=41, hubs=hubs)
+    x = np.random.default_rng(13).uniform(-0.005, 0.005, (n, dim)).astype(np.float32)
+    want = oracle.sag_f64(x, rp, col)
+    got = emulated_aggregate(rp, col, x, G, knobs=knobs)
+    np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
+    scale = np.random.default_rng(14).uniform(0.5, 1.5, n).astype(np.float32)
+    np.testing.assert_allclose(emulated_aggregate(rp, col, x, G, knobs=knobs, row_scale=scale), want * scale[:, None], rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(emulated_aggregate(rp, col, x, G, knobs=knobs, gin_eps=0.5), want + 1.5 * x, rtol=RTOL, atol=ATOL)
+    init = np.random.default_rng(15).uniform(-1, 1, (n, dim)).astype(np.float32)
+    np.testing.assert_allclose(emulated_aggregate(rp, col, x, G, knobs=knobs, accumulate=True, init=init), want + init, rtol=RTOL, atol=ATOL)
+    assert np.array_equal(got, emulated_aggregate(rp, col, x, G, knobs=knobs))
+    # another block order, a publish destination, and the group-per-node kernel's hand-over (dim 16)
+    dev = torch.device("cuda")
+    sh = drivers.Shard(rp, col, 0, 1, device=dev, order_rows=True)
+    xd = torch.from_numpy(x).to(dev)
+    a, b, pub = (torch.zeros(n, dim, device=dev) for _ in range(3))
+    sh.aggregate(a, xd, dim, drivers.Knobs(*knobs))
+    sh.row_order = torch.from_numpy(np.random.default_rng(16).permutation(n).astype(np.int32)).to(dev)
+    sh.aggregate(b, xd, dim, drivers.Knobs(*knobs), publish=[pub])
+    torch.cuda.synchronize()
+    assert torch.equal(a, b) and torch.equal(b, pub)
+    if G == 1:
+        assert np.array_equal(a.cpu().numpy(), got)
+    if dim == 16:
+        from mgg_osdi23_b200 import _lib
+        np.testing.assert_allclose(emulated_aggregate(rp, col, x, G, knobs=knobs, flags=_lib.AGG_GROUP_PER_NODE), want, rtol=RTOL, atol=ATOL)
+
+
 def test_row_order_changes_schedule_not_results():
     """Blocks taking rows longest-first (or in any permutation) give bit-identical sums."""
     dev = torch.device("cuda")

@@ -65,6 +65,29 @@ def test_static_scratch_variant_matches_regular_entry_point(oracle):
     np.testing.assert_allclose(second.cpu().numpy(), want * scale.cpu().numpy()[:, None], rtol=RTOL, atol=ATOL)
 
 
+def test_static_scratch_variant_with_more_giant_rows_than_its_tables_hold(oracle):
+    """300 rows above 16384 neighbors at dim 64: the fixed tables take 256 rows and 1024 partial rows, so
+    some rows are cut into segments, some run out of partial rows and some find the table full; those
+    stay whole on the hub list.  Every row must still come out right, call after call."""
+    dev = torch.device("cuda")
+    n, dim = 320, 64
+    rp, col = random_graph(n, 8, seed=23, hubs=[(i, 16385 + 37 * i) for i in range(300)])
+    x_np = np.random.default_rng(24).uniform(-0.01, 0.01, (n, dim)).astype(np.float32)
+    want = oracle.sag_f64(x_np, rp, col)
+    sh = drivers.Shard(rp, col, 0, 1, device=dev)
+    x = torch.from_numpy(x_np).to(dev)
+    lib = _lib.lib
+    outs = [torch.full((n, dim), float(k), device=dev) for k in range(3)]
+    for o in outs:
+        _lib.check(_call(lib.mggb_sag_np_div_static, o, x, sh, dim, (16, 2, 1), extra_edges=sh.edges))
+    regular = torch.zeros(n, dim, device=dev)
+    _lib.check(_call(lib.mggb_sag_np_div, regular, x, sh, dim, (16, 2, 1)))
+    torch.cuda.synchronize()
+    for o in outs:
+        np.testing.assert_allclose(o.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(regular.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+
+
 def test_static_scratch_variant_refuses_oversized_shards():
     dev = torch.device("cuda")
     rp, col = random_graph(50, 5, seed=1)
