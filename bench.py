@@ -64,6 +64,9 @@ def parse_args():
     ap.add_argument("--barrier", default="flag", choices=["flag", "nccl"],
                     help="what separates the stages of a pass at N > 1: 'flag' = epoch flags in peer memory (one small kernel), "
                          "'nccl' = a one-element all-reduce")
+    ap.add_argument("--launch", default="graph", choices=["graph", "stream"],
+                    help="how the timed passes are launched: 'graph' = each pass recorded once as a CUDA graph and replayed with one "
+                         "launch (needs the flag barrier at N > 1); 'stream' = every kernel launched from the host, pass after pass")
     ap.add_argument("--staging", default="none", choices=["none", "rows"],
                     help="'rows' = neighbor rows staged through shared memory by bulk copies (MGGB_AGG_STAGE_ROWS: the rows pulled "
                          "from peers when there are any, every row otherwise); 'none' = rows loaded into registers (the default, faster)")
@@ -627,8 +630,17 @@ def run_ours(args, rank, world, local_rank):
         for _ in range(max(args.warmup, 3)):
             model.forward(barrier)
         sync_all()
+        # one CUDA graph per pass unless asked otherwise: needs a barrier that can be recorded (the flag
+        # barrier, or none on one GPU) and the default single-stream schedule
+        use_graph = args.launch == "graph" and (barrier is None or barrier_obj is not None) and model.overlap_blocks <= 1
+        if use_graph:
+            model.capture(barrier)
+            for _ in range(3):
+                model.replay()
+            sync_all()
+        run_pass = model.replay if use_graph else (lambda: model.forward(barrier))
         del agg_events[:]
-        shard.event_sink = agg_events
+        shard.event_sink = None if use_graph else agg_events
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         loop_ms, launches = [], 0
         for rep in range(max(1, args.repeats)):
@@ -637,12 +649,19 @@ def run_ours(args, rank, world, local_rank):
             sampler.resume()
             e0.record()
             for _ in range(args.steps):
-                model.forward(barrier)
+                run_pass()
             e1.record()
             sync_all()
             sampler.pause()
             launches = api.kernel_launches[0] - launches0
             loop_ms.append(max_over_ranks(e0.elapsed_time(e1) / args.steps))
+        if use_graph:
+            # a replayed pass carries no events: the aggregation kernel is timed in K more passes launched
+            # one by one, outside the timed region
+            shard.event_sink = agg_events
+            for _ in range(args.steps):
+                model.forward(barrier)
+            sync_all()
         shard.event_sink = None
         step_ms = sorted(loop_ms)[len(loop_ms) // 2]
         launches = int(sum_over_ranks(launches))       # kernels of all ranks in one timed loop of K passes
@@ -659,6 +678,9 @@ def run_ours(args, rank, world, local_rank):
         sync_all()
         spans = len(marks[0]) - 1
         breakdown = [max_over_ranks(sum(m[i].elapsed_time(m[i + 1]) for m in marks) / len(marks)) for i in range(spans)]
+        if use_graph:       # what is checked below is what a replayed pass left in the output buffers
+            model.replay()
+            sync_all()
 
         # the outputs of the last pass against the oracle
         check = None
@@ -705,6 +727,7 @@ def run_ours(args, rank, world, local_rank):
 
         results[mode] = {"step_ms": step_ms, "loop_ms": loop_ms, "launches": launches, "agg_ms": agg_ms, "agg_ms_by_site": agg_ms_by_site,
                          "breakdown": breakdown, "spans": spans, "check": check, "e2e": e2e, "overlap_blocks": model.overlap_blocks,
+                         "launch": "cuda graph: one launch per pass" if use_graph else "stream: one launch per kernel",
                          "barrier_status": barrier_status, "leading_barrier": bool(model.leading_barrier)}
         sync_all()
         del model
@@ -769,7 +792,7 @@ def run_ours(args, rank, world, local_rank):
             out = {"ms_per_step": r["step_ms"], "ms_per_step_each_loop": r["loop_ms"], "value": naggs * total_edges / (r["step_ms"] * 1e-3),
                    "kernel_ms": r["agg_ms"], "bound": rf["bound"], "frac": rf["frac"], "aggregation_roofline_frac": rf["aggregation_roofline_frac"],
                    "check": r["check"], "barrier_status": r["barrier_status"], "starts_with_barrier": r["leading_barrier"],
-                   "pass_breakdown_ms": r["breakdown"]}
+                   "pass_breakdown_ms": r["breakdown"], "launch": r["launch"]}
             if r["e2e"]:
                 out["e2e_ms"] = r["e2e"]["ms"]
             return out
@@ -794,6 +817,7 @@ def run_ours(args, rank, world, local_rank):
             "barrier": (args.barrier if world > 1 else None),
             "dense_kernel": "cuda-core" if args.dense == "simt" else "tcgen05 where the shape fits",
             "overlap_blocks": r["overlap_blocks"],
+            "launch": r["launch"],
             "last_layer": "dense + softmax in one kernel" + (", logits stored too" if args.keep_logits else ", logits not stored"),
             "per_gpu_edges": [{"local": el, "remote": er, "rows": rr} for el, er, rr in allstats],
             "remote_fraction": sum(er for _, er, _ in allstats) / max(1, total_edges),

@@ -148,6 +148,13 @@ int mggb_enable_peer_access(int device, int peer_device);    /* MGGB_ERR_PEER if
  * 1 + the first PE that never arrived (0 = no wait has expired since the last reset; the call
  * synchronises the device).  Nothing here can hang a GPU. */
 int mggb_flag_barrier(int* const* peer_slots, int num_pes, int pe, int epoch, int64_t timeout_ns, void* stream);
+/* The same barrier with the epoch kept on the device: epoch_counter points to one int32 in THIS PE's
+ * device memory (zero before the first barrier, touched by nothing else); each launch uses its value + 1
+ * as the epoch and stores that back.  This is the form to record in a CUDA graph, where a replayed
+ * launch repeats its arguments: every replay still gets the next epoch.  Every PE must run the same
+ * number of barriers, and a PE must not mix the two forms on one slot array. */
+int mggb_flag_barrier_counted(int* const* peer_slots, int num_pes, int pe, int* epoch_counter, int64_t timeout_ns,
+                              void* stream);
 int mggb_flag_barrier_status(int* status, int reset);
 
 /* ---- neighbor aggregation ----------------------------------------------------------------------

@@ -54,6 +54,7 @@ SIGNATURES = {
     "mggb_sym_close": [_vp],
     "mggb_enable_peer_access": [_int, _int],
     "mggb_flag_barrier": [C.POINTER(_vp), _int, _int, _int, _i64, _vp],
+    "mggb_flag_barrier_counted": [C.POINTER(_vp), _int, _int, _vp, _i64, _vp],
     "mggb_flag_barrier_status": [C.POINTER(_int), _int],
     "mggb_sag_np_div": [_vp, C.POINTER(_vp), _int, _vp, _vp, _vp, _vp, _i32, _i32, _int, _i32, _int,
                         _int, _int, _int, _vp, _int, C.POINTER(_vp), _int, _vp],

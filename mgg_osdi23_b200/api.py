@@ -297,7 +297,8 @@ def dense_softmax_forward(out, x, w, logits=None):
 def dense_softmax_fits(dim1: int, dim2: int) -> bool:
     """Whether ``dense_softmax_forward`` takes this shape (dim2 <= 256 and w plus the staging rows within 160 KiB)."""
     j = (dim2 + 31) // 32
-    return j <= 8 and (dim1 * 32 * j + 64 * dim1) * 4 <= 160 * 1024
+    jp = (j + 1) // 2   # the kernel keeps w and the staged rows as pairs of floats
+    return j <= 8 and (dim1 * 32 * jp + 64 * dim1) * 8 <= 160 * 1024
 
 
 def publish_rows(src: torch.Tensor, publish, elem_offset: int = 0):

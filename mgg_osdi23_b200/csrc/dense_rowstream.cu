@@ -18,6 +18,10 @@
 // finish the job (not 5 per sum) and lane L ends up with outputs 2L and 2L+1 of the R x 16 block, which
 // it stores as one 8-byte piece: the warp's store is one contiguous run of R rows.
 //
+// With 8-byte loads the sums are kept as PAIRS (columns 2j, 2j+1 in one 64-bit register) and updated with
+// fma.rn.f32x2, two multiply-adds per instruction, each rounding like fmaf (sm_100); w is read from shared
+// memory as ready-made pairs.
+//
 // The lanes load their floats into registers two steps ahead (three buffers in rotation).  A variant that
 // had a ninth warp stage the block's next 32 rows in shared memory with bulk copies (77 KiB in flight per
 // SM) was measured slower (0.27 ms against 0.22 ms on 232,965 x 602 -> 16): one block of eight computing
@@ -34,10 +38,30 @@ struct Publish {
 
 constexpr int RS_THREADS = 256;
 constexpr int RS_COLS = 16;      // padded output width
+// Register buffers per row that a lane rotates through (loads in flight = buffers - 1 steps).  Measured on
+// 232,965 x 602 -> 16: 3 buffers 206 us, 4 buffers 231 us, 5 buffers 238 us: issue slots, not latency, are
+// what this kernel runs out of.
+constexpr int RS_BUFFERS = 3;
 
 template <int VEC> struct XVec;
 template <> struct XVec<2> { using T = float2; };
 template <> struct XVec<4> { using T = float4; };
+
+// Two fp32 multiply-adds per instruction (sm_100: fma.rn.f32x2; each half rounds like fmaf).  A pair lives
+// in one 64-bit register: low half = first element.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
 
 // Halves the number of live sums: lanes whose `mask` bit is clear keep a[0 .. N/2), the others keep
 // a[N/2 .. N); what a lane does not keep goes to its partner.  On return a[0 .. N/2) holds the kept sums.
@@ -53,7 +77,7 @@ __device__ __forceinline__ void fold(float (&a)[RS_COLS * 8], int lane, int mask
 }
 
 // R rows per warp (R * 16 must be a multiple of 64: R = 4 or 8), VEC floats per lane and step.
-template <int VEC, int R>
+template <int VEC, int R, bool PACKED>
 __global__ void __launch_bounds__(RS_THREADS, 2)
 dense_rowstream_kernel(float* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w, long long n, int K, int M,
                        const float* __restrict__ row_scale, int relu, int steps, const Publish pub) {
@@ -84,8 +108,11 @@ dense_rowstream_kernel(float* __restrict__ out, const float* __restrict__ x, con
     for (long long grp = (((long long)blockIdx.x * RS_THREADS + threadIdx.x) >> 5); grp < groups; grp += warps) {
         const long long row0 = grp * R;
         float acc[RS_COLS * 8];
+        unsigned long long acc2[RS_COLS * 4];   // PACKED: the same sums as pairs (columns 2j, 2j+1)
 #pragma unroll
         for (int j = 0; j < RS_COLS * R; j++) acc[j] = 0.f;
+#pragma unroll
+        for (int j = 0; j < RS_COLS * R / 2; j++) acc2[j] = 0ull;
 
         auto load_step = [&](int i, V* xv) {
             const int k0 = (i * 32 + lane) * VEC;
@@ -97,6 +124,28 @@ dense_rowstream_kernel(float* __restrict__ out, const float* __restrict__ x, con
             }
         };
         auto fma_step = [&](int i, const V* xv) {
+            if (PACKED) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) {
+                    unsigned long long aa[R];
+#pragma unroll
+                    for (int r = 0; r < R; r++) {
+                        const float a = reinterpret_cast<const float*>(&xv[r])[e];
+                        aa[r] = pack2(a, a);
+                    }
+#pragma unroll
+                    for (int g = 0; g < 4; g++) {
+                        // a float4 of w read as two ready-made pairs
+                        const ulonglong2 wv = reinterpret_cast<const ulonglong2*>(Wt)[((i * VEC + e) * 4 + g) * 32 + lane];
+#pragma unroll
+                        for (int r = 0; r < R; r++) {
+                            acc2[r * 8 + 2 * g + 0] = fma2(aa[r], wv.x, acc2[r * 8 + 2 * g + 0]);
+                            acc2[r * 8 + 2 * g + 1] = fma2(aa[r], wv.y, acc2[r * 8 + 2 * g + 1]);
+                        }
+                    }
+                }
+                return;
+            }
 #pragma unroll
             for (int e = 0; e < VEC; e++) {
 #pragma unroll
@@ -113,17 +162,24 @@ dense_rowstream_kernel(float* __restrict__ out, const float* __restrict__ x, con
                 }
             }
         };
-        // three register buffers in rotation, two steps of loads in flight while one is multiplied
-        V b0[R], b1[R], b2[R];
-        load_step(0, b0);
-        load_step(1, b1);
-        for (int i = 0; i < steps; i += 3) {
-            load_step(i + 2, b2);
-            fma_step(i, b0);
-            if (i + 1 < steps) { load_step(i + 3, b0); fma_step(i + 1, b1); }
-            if (i + 2 < steps) { load_step(i + 4, b1); fma_step(i + 2, b2); }
+        // RS_BUFFERS register buffers in rotation: RS_BUFFERS - 1 steps of loads in flight while one is multiplied
+        V buf[RS_BUFFERS][R];
+#pragma unroll
+        for (int b = 0; b < RS_BUFFERS - 1; b++) load_step(b, buf[b]);
+        for (int i = 0; i < steps; i += RS_BUFFERS) {
+#pragma unroll
+            for (int b = 0; b < RS_BUFFERS; b++) {
+                if (i + b < steps) {
+                    load_step(i + b + RS_BUFFERS - 1, buf[(b + RS_BUFFERS - 1) % RS_BUFFERS]);
+                    fma_step(i + b, buf[b]);
+                }
+            }
         }
 
+        if (PACKED) {
+#pragma unroll
+            for (int j = 0; j < RS_COLS * R / 2; j++) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
+        }
         // fold the 32 lanes' sums: 16*R -> 2 per lane; lane L is left with flat elements 2L, 2L+1 (+64 per further block)
         constexpr int BLOCKS = RS_COLS * R / 64;
         float res[2 * BLOCKS];
@@ -194,13 +250,15 @@ int dense_rowstream(float* out, const float* x, const float* w, int64_t n, int d
     const long long blocks = (groups + RS_THREADS / 32 - 1) / (RS_THREADS / 32);
     const int grid = (int)std::min<long long>(blocks, 2LL * mggb::sm_count());
     const int relu = (flags & MGGB_DENSE_RELU) ? 1 : 0;
-    if (wide) {
-        if (smem > 48 * 1024) MGGB_CUDA(cudaFuncSetAttribute(dense_rowstream_kernel<4, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        dense_rowstream_kernel<4, R><<<grid, RS_THREADS, smem, st>>>(out, x, w, n, dim1, dim2, row_scale, relu, steps, pub);
-    } else {
-        if (smem > 48 * 1024) MGGB_CUDA(cudaFuncSetAttribute(dense_rowstream_kernel<2, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        dense_rowstream_kernel<2, R><<<grid, RS_THREADS, smem, st>>>(out, x, w, n, dim1, dim2, row_scale, relu, steps, pub);
-    }
+    auto go = [&](auto kernel) -> int {
+        if (smem > 48 * 1024) MGGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kernel<<<grid, RS_THREADS, smem, st>>>(out, x, w, n, dim1, dim2, row_scale, relu, steps, pub);
+        return MGGB_OK;
+    };
+    // 8-byte loads: two multiply-adds per instruction (measured 235 -> 206 us on 232,965 x 602 -> 16);
+    // 16-byte loads leave no registers for the paired accumulators
+    const int rc = wide ? go(dense_rowstream_kernel<4, R, false>) : go(dense_rowstream_kernel<2, R, true>);
+    if (rc != MGGB_OK) return rc;
     MGGB_CUDA(cudaGetLastError());
     *launched = true;
     return MGGB_OK;

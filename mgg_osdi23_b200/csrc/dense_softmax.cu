@@ -7,10 +7,12 @@
 // and a narrow hidden width (172 classes from 16 features) the pass is bound by that traffic.
 //
 // A warp owns 8 rows at a time.  Lane l holds output columns l, l+32, ... (J of them) of each of
-// its rows in registers; w sits in shared memory once per block, zero-padded to 32*J columns; the
-// warp's 8 rows of x are staged in shared memory and read back as broadcasts.  Softmax is the
-// max-subtracted exp / sum of the separate kernel, reduced over the warp with shuffles, the 8 rows
-// side by side.
+// its rows in registers, as PAIRS (columns 64p + l and 64p + 32 + l in one 64-bit register) updated with
+// fma.rn.f32x2: two multiply-adds per instruction, each rounding like fmaf (sm_100).  The kernel is bound
+// by instruction issue, so both operands are laid out in shared memory as ready-made pairs: w once per
+// block as {w[k][64p+l], w[k][64p+32+l]}, zero-padded to 64*JP columns, and the warp's 8 rows of x with
+// every element stored twice ({x, x}), read back as broadcasts.  Softmax is the max-subtracted exp / sum
+// of the separate kernel, reduced over the warp with shuffles, the 8 rows side by side.
 #include <algorithm>
 #include <cfloat>
 #include <cstdint>
@@ -30,18 +32,29 @@ __device__ __forceinline__ float exp_neg(float d) {
     return r;
 }
 
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+// J = ceil(M / 32) column slots per lane, JP = ceil(J / 2) pairs of them.
 template <int J>
-__global__ void __launch_bounds__(FS_WARPS * 32)
+__global__ void __launch_bounds__(FS_WARPS * 32, 2)
 dense_softmax_kernel(float* __restrict__ out, float* __restrict__ logits, const float* __restrict__ x,
                      const float* __restrict__ w, long long n, int K, int M, int vec_ok) {
     extern __shared__ __align__(16) float fs_smem[];
-    constexpr int MP = 32 * J;
-    float* Ws = fs_smem;                                   // [K][MP]
+    constexpr int JP = (J + 1) / 2;
+    float2* Ws = reinterpret_cast<float2*>(fs_smem);       // [K][JP][32 lanes] of {column 64p + l, column 64p + 32 + l}
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* Xs = fs_smem + (size_t)K * MP + (size_t)warp * FS_ROWS * K;   // [FS_ROWS][K]
-    for (int idx = threadIdx.x; idx < K * MP; idx += FS_WARPS * 32) {
-        const int k = idx / MP, c = idx - k * MP;
-        Ws[idx] = c < M ? __ldg(w + (long long)k * M + c) : 0.f;
+    float2* Xs = Ws + (size_t)K * JP * 32 + (size_t)warp * FS_ROWS * K;   // [FS_ROWS][K] of {x, x}
+    for (int idx = threadIdx.x; idx < K * JP * 32; idx += FS_WARPS * 32) {
+        const int l = idx & 31, p = (idx >> 5) % JP, k = idx / (32 * JP);
+        const int c0 = 64 * p + l, c1 = c0 + 32;
+        Ws[idx] = make_float2(c0 < M ? __ldg(w + (long long)k * M + c0) : 0.f, c1 < M ? __ldg(w + (long long)k * M + c1) : 0.f);
     }
     __syncthreads();
 
@@ -54,51 +67,64 @@ dense_softmax_kernel(float* __restrict__ out, float* __restrict__ logits, const 
         const float* src = x + row0 * K;
         __syncwarp();                                      // the previous step's reads of Xs are done
         if (vec_ok) {
-            for (int i = lane * 4; i < FS_ROWS * K; i += 128)
-                *reinterpret_cast<float4*>(Xs + i) = i < count ? __ldcs(reinterpret_cast<const float4*>(src + i))
-                                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int i = lane * 4; i < FS_ROWS * K; i += 128) {
+                const float4 v = i < count ? __ldcs(reinterpret_cast<const float4*>(src + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4*>(Xs + i) = make_float4(v.x, v.x, v.y, v.y);
+                *reinterpret_cast<float4*>(Xs + i + 2) = make_float4(v.z, v.z, v.w, v.w);
+            }
         } else {
-            for (int i = lane; i < FS_ROWS * K; i += 32) Xs[i] = i < count ? __ldcs(src + i) : 0.f;
+            for (int i = lane; i < FS_ROWS * K; i += 32) {
+                const float v = i < count ? __ldcs(src + i) : 0.f;
+                Xs[i] = make_float2(v, v);
+            }
         }
         __syncwarp();
 
-        float acc[FS_ROWS][J];
+        unsigned long long acc2[FS_ROWS][JP];
 #pragma unroll
         for (int r = 0; r < FS_ROWS; r++)
 #pragma unroll
-            for (int j = 0; j < J; j++) acc[r][j] = 0.f;
+            for (int p = 0; p < JP; p++) acc2[r][p] = 0ull;
 
+        const unsigned long long* Wp = reinterpret_cast<const unsigned long long*>(Ws);
         if (vec_ok) {
-            for (int k = 0; k < K; k += 4) {
-                float4 xv[FS_ROWS];
+            for (int k = 0; k < K; k += 2) {
+                ulonglong2 xv[FS_ROWS];                    // {x[k], x[k]} and {x[k+1], x[k+1]} of every row
 #pragma unroll
-                for (int r = 0; r < FS_ROWS; r++) xv[r] = *reinterpret_cast<const float4*>(Xs + r * K + k);
+                for (int r = 0; r < FS_ROWS; r++) xv[r] = *reinterpret_cast<const ulonglong2*>(Xs + r * K + k);
 #pragma unroll
-                for (int kk = 0; kk < 4; kk++) {
-                    float wv[J];
+                for (int kk = 0; kk < 2; kk++) {
+                    unsigned long long wv[JP];
 #pragma unroll
-                    for (int j = 0; j < J; j++) wv[j] = Ws[(k + kk) * MP + j * 32 + lane];
+                    for (int p = 0; p < JP; p++) wv[p] = Wp[((k + kk) * JP + p) * 32 + lane];
 #pragma unroll
                     for (int r = 0; r < FS_ROWS; r++) {
-                        const float a = kk == 0 ? xv[r].x : kk == 1 ? xv[r].y : kk == 2 ? xv[r].z : xv[r].w;
+                        const unsigned long long a = kk == 0 ? xv[r].x : xv[r].y;
 #pragma unroll
-                        for (int j = 0; j < J; j++) acc[r][j] = fmaf(a, wv[j], acc[r][j]);
+                        for (int p = 0; p < JP; p++) acc2[r][p] = fma2(a, wv[p], acc2[r][p]);
                     }
                 }
             }
         } else {
+            const unsigned long long* Xp = reinterpret_cast<const unsigned long long*>(Xs);
             for (int k = 0; k < K; k++) {
-                float wv[J];
+                unsigned long long wv[JP];
 #pragma unroll
-                for (int j = 0; j < J; j++) wv[j] = Ws[k * MP + j * 32 + lane];
+                for (int p = 0; p < JP; p++) wv[p] = Wp[(k * JP + p) * 32 + lane];
 #pragma unroll
                 for (int r = 0; r < FS_ROWS; r++) {
-                    const float a = Xs[r * K + k];
+                    const unsigned long long a = Xp[r * K + k];
 #pragma unroll
-                    for (int j = 0; j < J; j++) acc[r][j] = fmaf(a, wv[j], acc[r][j]);
+                    for (int p = 0; p < JP; p++) acc2[r][p] = fma2(a, wv[p], acc2[r][p]);
                 }
             }
         }
+        // column slot j = 2p (+1) of lane l is column 32j + l, as the softmax and the stores below expect
+        float acc[FS_ROWS][2 * JP];
+#pragma unroll
+        for (int r = 0; r < FS_ROWS; r++)
+#pragma unroll
+            for (int p = 0; p < JP; p++) unpack2(acc2[r][p], acc[r][2 * p], acc[r][2 * p + 1]);
 
         // Softmax of the 8 rows side by side: the shuffle chains of different rows overlap.
         const bool last_ok = lane < M - 32 * (J - 1);      // only the last column slot can run past M
@@ -164,7 +190,8 @@ extern "C" int mggb_dense_softmax_forward(float* out, float* logits, const float
                  (long long)n, dim1, dim2);
     MGGB_REQUIRE(out != x && logits != x, "dense_softmax_forward: outputs must not alias x");
     const int J = (dim2 + 31) / 32;
-    const size_t smem = ((size_t)dim1 * 32 * J + (size_t)FS_WARPS * FS_ROWS * dim1) * sizeof(float);
+    const int JP = (J + 1) / 2;
+    const size_t smem = ((size_t)dim1 * 32 * JP + (size_t)FS_WARPS * FS_ROWS * dim1) * sizeof(float2);
     if (J > 8 || smem > 160 * 1024)
         return mggb::fail(MGGB_ERR_UNSUPPORTED, "dense_softmax_forward: dim1=%d dim2=%d does not fit the fused kernel "
                           "(dim2 <= 256 and %zu bytes of shared memory <= 160 KiB); call mggb_dense_forward then mggb_softmax_forward",

@@ -248,13 +248,19 @@ class FlagBarrier:
         self.slots = SymmetricBuffer(_lib.MAX_PES, group, pe, num_pes)     # zero-filled 4-byte slots: epoch 0
         self.table = (C.c_void_p * num_pes)(*self.slots.peer_ptrs)
         self.timeout_ns = int(timeout_s * 1e9)
-        self.epoch = 0
+        # the epoch lives on the device (this PE's count of barriers so far), so a barrier recorded in a CUDA
+        # graph gets the next epoch at every replay
+        self.counter = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()))
 
     def __call__(self):
-        self.epoch += 1
         api.kernel_launches[0] += 1
-        _lib.check(_lib.lib.mggb_flag_barrier(self.table, self.num_pes, self.pe, self.epoch, self.timeout_ns,
-                                              C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        _lib.check(_lib.lib.mggb_flag_barrier_counted(self.table, self.num_pes, self.pe, C.c_void_p(self.counter.data_ptr()),
+                                                      self.timeout_ns, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    @property
+    def epoch(self) -> int:
+        """Barriers this PE has run so far (synchronises)."""
+        return int(self.counter.item())
 
     def status(self, reset: bool = False) -> int:
         st = C.c_int(0)
@@ -353,6 +359,41 @@ class _Forward:
 
     def forward(self, barrier=None, marks=None):
         run_stages([self], barrier, marks)
+        return self.out
+
+    def capture(self, barrier=None) -> int:
+        """Records one forward pass (its kernels, memsets and barriers, in stream order) as a CUDA graph;
+        :meth:`replay` then enqueues the whole pass with one launch, which is what an 8-GPU pass of a
+        few hundred microseconds needs (a dozen launches from Python cost about as much as its kernels).
+        Returns the number of kernels in the graph.
+
+        The pass is run once on the capture stream first, so that everything the library allocates on first
+        use for a (device, stream) pair exists before recording starts.  ``barrier`` must be recordable: a
+        :class:`FlagBarrier` (its epoch is read from device memory) or None.  Every PE must capture, and
+        later replay, the same number of times.  Buffers, weights and knobs are fixed at capture time."""
+        if self.overlap_blocks > 1:
+            raise ValueError("capture: row blocks on a second stream (overlap_blocks > 1) are not recorded")
+        sink, self.shard.event_sink = self.shard.event_sink, None
+        try:
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                self.forward(barrier)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = api.kernel_launches[0]
+            # thread-local: other threads of the process (a collective library's watchdog, a clock sampler) keep working
+            with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+                self.forward(barrier)
+            self._graph, self._graph_kernels = graph, api.kernel_launches[0] - before
+        finally:
+            self.shard.event_sink = sink
+        return self._graph_kernels
+
+    def replay(self):
+        """One captured pass on the current stream (see :meth:`capture`)."""
+        self._graph.replay()
+        api.kernel_launches[0] += self._graph_kernels
         return self.out
 
     def forward_host(self, x_host: torch.Tensor, barrier=None, chunks: int = 8, marks: Optional[list] = None) -> torch.Tensor:

@@ -48,6 +48,16 @@ def main():
         np.testing.assert_allclose(probs.numpy(), want[sh.lb:sh.ub], rtol=1e-5, atol=1e-4)
         probs = m.forward_host(xh, nccl_barrier)                 # and once with the all-reduce barrier
         np.testing.assert_allclose(probs.numpy(), want[sh.lb:sh.ub], rtol=1e-5, atol=1e-4)
+        # the same pass recorded as a CUDA graph (barriers included) and replayed: same bits as launched one by one
+        m.d_in.copy_(xh.to(dev))
+        m.forward(barrier)
+        eager = m.out.clone()
+        m.capture(barrier)
+        for _ in range(3):
+            m.out.zero_()
+            m.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(m.out, eager), "replayed pass differs"
         barrier()
     assert barrier.status() == 0, "a flag-barrier wait expired"
 

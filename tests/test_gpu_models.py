@@ -303,3 +303,41 @@ def test_back_to_back_passes_never_overwrite_what_a_slow_peer_still_reads(oracle
     assert drivers.SingleAggregation(drivers.Shard(rp, col, 0, G, device=dev), 16, reps[0], drivers.Knobs()).leading_barrier
     ga, gb = _published(G, npp, 16, dev, fetch)
     assert not drivers.GCN2Forward(drivers.Shard(rp, col, 0, G, device=dev), din, 16, dout, ga[0], gb[0], drivers.Knobs()).leading_barrier
+
+
+@pytest.mark.parametrize("kind", ["gcn2", "gin5", "single"])
+def test_captured_pass_replays_to_the_same_bits(oracle, kind):
+    """A forward pass recorded as a CUDA graph: replaying it (with new inputs in the same buffers) gives exactly
+    what launching the kernels one by one gives, replay after replay; rows above the hub threshold included
+    (their work list is cleared by a memset node inside the graph)."""
+    from gpu_util import random_graph
+    n = 3000
+    rp, col = random_graph(n, 20, seed=51, hubs=[(0, 40_000), (17, 17_000), (2999, 1500)])
+    dev = torch.device("cuda")
+    sh = drivers.Shard(rp, col, 0, 1, device=dev)
+    din, hid, dout = 100, 16, 41
+    sym = lambda d: drivers.LocalSym([torch.zeros(n * d, device=dev)], 0)
+    if kind == "gcn2":
+        m = drivers.GCN2Forward(sh, din, hid, dout, sym(hid), sym(hid), drivers.Knobs(16, 2, 1),
+                                w1=(gg.glorot_uniform(din, hid, 1) * 0.01).to(dev), w2=gg.glorot_uniform(hid, dout, 2).to(dev))
+    elif kind == "gin5":
+        ws = [gg.glorot_uniform(din, 64, 10) * 0.01] + [gg.glorot_uniform(64, 64, 11 + k) * 0.01 for k in range(4)] + [gg.glorot_uniform(64, dout, 20)]
+        m = drivers.GIN5Forward(sh, din, 64, dout, sym(64), sym(64), drivers.Knobs(16, 1, 2), eps=0.0, weights=[w.to(dev) for w in ws], sym_c=sym(64))
+    else:
+        m = drivers.SingleAggregation(sh, hid, sym(hid), drivers.Knobs(32, 1, 1, flags=4))
+    inputs = [gg.features(n, m.d_in.shape[1], seed=s_, device=dev) * 0.05 for s_ in (3, 4)]
+    eager = []
+    for xi in inputs:
+        m.d_in.copy_(xi)
+        m.forward()
+        eager.append(m.out.clone())
+    kernels = m.capture()
+    assert kernels >= 2
+    for rnd in range(2):
+        for xi, want in zip(inputs, eager):
+            m.d_in.copy_(xi)
+            m.out.fill_(-1.0)
+            m.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(m.out, want), (kind, rnd)
+    assert not torch.equal(eager[0], eager[1])
