@@ -22,10 +22,17 @@
 // fma.rn.f32x2, two multiply-adds per instruction, each rounding like fmaf (sm_100); w is read from shared
 // memory as ready-made pairs.
 //
-// The lanes load their floats into registers two steps ahead (three buffers in rotation).  A variant that
-// had a ninth warp stage the block's next 32 rows in shared memory with bulk copies (77 KiB in flight per
-// SM) was measured slower (0.27 ms against 0.22 ms on 232,965 x 602 -> 16): one block of eight computing
-// warps per SM does not keep the FMA pipes as busy as sixteen warps with their rows in registers.
+// The lanes load their floats into registers two steps ahead (three buffers in rotation).  What was measured
+// on 232,965 x 602 -> 16 (561 MB of x; 86 us at the measured HBM copy rate), and dropped:
+//   * four or five register buffers instead of three: 231 and 238 us against 206 us;
+//   * x staged in a per-warp shared-memory ring by cp.async (8 bytes per lane and row, 7 KB in flight per
+//     warp): the waits on loads disappear from the profile (long-scoreboard stall 3.2 -> 0.5 cycles per issued
+//     instruction) but the warps then queue for the FMA pipe (math-pipe throttle) with a third more
+//     instructions to issue: 215 us;
+//   * a ninth warp staging the block's next 32 rows with bulk copies (77 KiB in flight per SM): 270 us, one
+//     block of eight computing warps per SM does not keep the FMA pipes as busy as sixteen warps.
+// With sixteen resident warps per SM (128 registers each) the kernel sits between the two limits: issue slots
+// 49 % busy, FMA pipe 24 % (paired instructions), DRAM 34 %.
 #include <algorithm>
 #include "common.h"
 
@@ -76,15 +83,10 @@ __device__ __forceinline__ void fold(float (&a)[RS_COLS * 8], int lane, int mask
     }
 }
 
-// R rows per warp (R * 16 must be a multiple of 64: R = 4 or 8), VEC floats per lane and step.
-template <int VEC, int R, bool PACKED>
-__global__ void __launch_bounds__(RS_THREADS, 2)
-dense_rowstream_kernel(float* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w, long long n, int K, int M,
-                       const float* __restrict__ row_scale, int relu, int steps, const Publish pub) {
-    using V = typename XVec<VEC>::T;
-    extern __shared__ __align__(16) float4 Wt[];     // [steps][VEC][4 column groups][32 lanes] of float4
-    const int lane = threadIdx.x & 31;
-    // w in lane order: slot ((i*VEC + e)*4 + g)*32 + l holds w[k][4g .. 4g+3] for k = (i*32 + l)*VEC + e (zeros past K or M)
+// w into shared memory in lane order: slot ((i*VEC + e)*4 + g)*32 + l holds w[k][4g .. 4g+3] for
+// k = (i*32 + l)*VEC + e (zeros past K or M).  Ends with a block barrier.
+template <int VEC>
+__device__ __forceinline__ void stage_w(float4* Wt, const float* __restrict__ w, int K, int M, int steps) {
     for (int idx = threadIdx.x; idx < steps * VEC * 4 * 32; idx += RS_THREADS) {
         const int l = idx & 31, g = (idx >> 5) & 3, ie = idx >> 7;
         const int i = ie / VEC, e = ie - i * VEC;
@@ -100,6 +102,62 @@ dense_rowstream_kernel(float* __restrict__ out, const float* __restrict__ x, con
         Wt[idx] = v;
     }
     __syncthreads();
+}
+
+// Folds the 32 lanes' R x 16 sums (16*R -> 2 per lane; lane L is left with flat elements 2L, 2L+1, +64 per
+// further block of 64) and stores rows row0 .. row0+R-1 with the epilogue, also to every publish destination.
+template <int R>
+__device__ __forceinline__ void fold_and_store(float (&acc)[RS_COLS * 8], int lane, long long row0, long long n, int M,
+                                               float* __restrict__ out, const float* __restrict__ row_scale, int relu,
+                                               const Publish& pub, bool pair_ok) {
+    constexpr int BLOCKS = RS_COLS * R / 64;
+    float res[2 * BLOCKS];
+#pragma unroll
+    for (int b = 0; b < BLOCKS; b++) {
+        float a[RS_COLS * 8];
+#pragma unroll
+        for (int j = 0; j < 64; j++) a[j] = acc[b * 64 + j];
+        fold<64>(a, lane, 16);
+        fold<32>(a, lane, 8);
+        fold<16>(a, lane, 4);
+        fold<8>(a, lane, 2);
+        fold<4>(a, lane, 1);
+        res[2 * b] = a[0];
+        res[2 * b + 1] = a[1];
+    }
+#pragma unroll
+    for (int b = 0; b < BLOCKS; b++) {
+        // flat element f = b*64 + 2*lane (+1) of the R x 16 block: row f / 16, column f % 16
+        const int f = b * 64 + 2 * lane;
+        const long long row = row0 + f / RS_COLS;
+        const int c = f % RS_COLS;
+        if (row >= n) continue;
+        const float s = row_scale ? row_scale[row] : 1.f;
+        float v0 = res[2 * b] * s, v1 = res[2 * b + 1] * s;
+        if (relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
+        const long long o = row * M + c;
+        if (pair_ok) {
+            // full-width rows and 8-byte aligned destinations: one 8-byte store per lane, so the warp writes
+            // its R rows as one contiguous run (what a peer's replica wants to receive over NVLink)
+            const float2 v = make_float2(v0, v1);
+            *reinterpret_cast<float2*>(out + o) = v;
+            for (int q = 0; q < pub.n; q++) *reinterpret_cast<float2*>(pub.dst[q] + o) = v;
+        } else {
+            if (c < M) { out[o] = v0; for (int q = 0; q < pub.n; q++) pub.dst[q][o] = v0; }
+            if (c + 1 < M) { out[o + 1] = v1; for (int q = 0; q < pub.n; q++) pub.dst[q][o + 1] = v1; }
+        }
+    }
+}
+
+// R rows per warp (R * 16 must be a multiple of 64: R = 4 or 8), VEC floats per lane and step.
+template <int VEC, int R, bool PACKED>
+__global__ void __launch_bounds__(RS_THREADS, 2)
+dense_rowstream_kernel(float* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w, long long n, int K, int M,
+                       const float* __restrict__ row_scale, int relu, int steps, const Publish pub) {
+    using V = typename XVec<VEC>::T;
+    extern __shared__ __align__(16) float4 Wt[];     // [steps][VEC][4 column groups][32 lanes] of float4
+    const int lane = threadIdx.x & 31;
+    stage_w<VEC>(Wt, w, K, M, steps);
 
     bool pair_ok = (M == RS_COLS) && ((uintptr_t)out % 8 == 0);
     for (int q = 0; q < pub.n; q++) pair_ok = pair_ok && ((uintptr_t)pub.dst[q] % 8 == 0);
@@ -144,20 +202,20 @@ dense_rowstream_kernel(float* __restrict__ out, const float* __restrict__ x, con
                         }
                     }
                 }
-                return;
-            }
+            } else {
 #pragma unroll
-            for (int e = 0; e < VEC; e++) {
+                for (int e = 0; e < VEC; e++) {
 #pragma unroll
-                for (int g = 0; g < 4; g++) {
-                    const float4 wv = Wt[((i * VEC + e) * 4 + g) * 32 + lane];
+                    for (int g = 0; g < 4; g++) {
+                        const float4 wv = Wt[((i * VEC + e) * 4 + g) * 32 + lane];
 #pragma unroll
-                    for (int r = 0; r < R; r++) {
-                        const float a = reinterpret_cast<const float*>(&xv[r])[e];
-                        acc[r * RS_COLS + 4 * g + 0] = fmaf(a, wv.x, acc[r * RS_COLS + 4 * g + 0]);
-                        acc[r * RS_COLS + 4 * g + 1] = fmaf(a, wv.y, acc[r * RS_COLS + 4 * g + 1]);
-                        acc[r * RS_COLS + 4 * g + 2] = fmaf(a, wv.z, acc[r * RS_COLS + 4 * g + 2]);
-                        acc[r * RS_COLS + 4 * g + 3] = fmaf(a, wv.w, acc[r * RS_COLS + 4 * g + 3]);
+                        for (int r = 0; r < R; r++) {
+                            const float a = reinterpret_cast<const float*>(&xv[r])[e];
+                            acc[r * RS_COLS + 4 * g + 0] = fmaf(a, wv.x, acc[r * RS_COLS + 4 * g + 0]);
+                            acc[r * RS_COLS + 4 * g + 1] = fmaf(a, wv.y, acc[r * RS_COLS + 4 * g + 1]);
+                            acc[r * RS_COLS + 4 * g + 2] = fmaf(a, wv.z, acc[r * RS_COLS + 4 * g + 2]);
+                            acc[r * RS_COLS + 4 * g + 3] = fmaf(a, wv.w, acc[r * RS_COLS + 4 * g + 3]);
+                        }
                     }
                 }
             }
@@ -180,44 +238,7 @@ dense_rowstream_kernel(float* __restrict__ out, const float* __restrict__ x, con
 #pragma unroll
             for (int j = 0; j < RS_COLS * R / 2; j++) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
         }
-        // fold the 32 lanes' sums: 16*R -> 2 per lane; lane L is left with flat elements 2L, 2L+1 (+64 per further block)
-        constexpr int BLOCKS = RS_COLS * R / 64;
-        float res[2 * BLOCKS];
-#pragma unroll
-        for (int b = 0; b < BLOCKS; b++) {
-            float a[RS_COLS * 8];
-#pragma unroll
-            for (int j = 0; j < 64; j++) a[j] = acc[b * 64 + j];
-            fold<64>(a, lane, 16);
-            fold<32>(a, lane, 8);
-            fold<16>(a, lane, 4);
-            fold<8>(a, lane, 2);
-            fold<4>(a, lane, 1);
-            res[2 * b] = a[0];
-            res[2 * b + 1] = a[1];
-        }
-#pragma unroll
-        for (int b = 0; b < BLOCKS; b++) {
-            // flat element f = b*64 + 2*lane (+1) of the R x 16 block: row f / 16, column f % 16
-            const int f = b * 64 + 2 * lane;
-            const long long row = row0 + f / RS_COLS;
-            const int c = f % RS_COLS;
-            if (row >= n) continue;
-            const float s = row_scale ? row_scale[row] : 1.f;
-            float v0 = res[2 * b] * s, v1 = res[2 * b + 1] * s;
-            if (relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
-            const long long o = row * M + c;
-            if (pair_ok) {
-                // full-width rows and 8-byte aligned destinations: one 8-byte store per lane, so the warp writes
-                // its R rows as one contiguous run (what a peer's replica wants to receive over NVLink)
-                const float2 v = make_float2(v0, v1);
-                *reinterpret_cast<float2*>(out + o) = v;
-                for (int q = 0; q < pub.n; q++) *reinterpret_cast<float2*>(pub.dst[q] + o) = v;
-            } else {
-                if (c < M) { out[o] = v0; for (int q = 0; q < pub.n; q++) pub.dst[q][o] = v0; }
-                if (c + 1 < M) { out[o + 1] = v1; for (int q = 0; q < pub.n; q++) pub.dst[q][o + 1] = v1; }
-            }
-        }
+        fold_and_store<R>(acc, lane, row0, n, M, out, row_scale, relu, pub, pair_ok);
     }
 }
 
