@@ -30,6 +30,10 @@ void clear_error();
     } while (0)
 
 namespace mggb {
+// Internal flag of dense_tc() (never part of the public MGGB_DENSE_* set): the epilogue stores the softmax of every
+// output row instead of the row.  Used by mggb_dense_softmax_forward for shapes the tensor-core kernel takes.
+constexpr int DENSE_TC_SOFTMAX = 1 << 20;
+
 // Multiprocessors of the current device (asked once per device; 1 if the query fails, which only
 // makes a grid smaller).  Grids are sized from this, never from a typed-in count.
 inline int sm_count() {

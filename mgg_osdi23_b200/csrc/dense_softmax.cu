@@ -183,12 +183,26 @@ int launch_fused(float* out, float* logits, const float* x, const float* w, long
 
 }  // namespace
 
+namespace mggb {
+int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, int dim2, const float* row_scale,
+             int flags, float* const* publish_out, int num_publish, cudaStream_t st, bool* launched);
+}
+
 extern "C" int mggb_dense_softmax_forward(float* out, float* logits, const float* x, const float* w, int64_t n,
                                           int dim1, int dim2, void* stream) {
     MGGB_REQUIRE(out && x && w, "dense_softmax_forward: NULL argument");
     MGGB_REQUIRE(n >= 0 && dim1 >= 1 && dim2 >= 1, "dense_softmax_forward: need n >= 0, dim1 >= 1, dim2 >= 1 (n=%lld dim1=%d dim2=%d)",
                  (long long)n, dim1, dim2);
     MGGB_REQUIRE(out != x && logits != x, "dense_softmax_forward: outputs must not alias x");
+    // Wide inputs (dim1 a multiple of 4 above 32, at most 128 classes, logits not wanted): the tcgen05 kernel with the
+    // softmax in its epilogue, where every thread owns a whole accumulator row.  The multiply-adds of such a shape
+    // (2,449,029 x 64 -> 47: 10 G) keep the fp32 pipes busy for 0.95 ms in the kernel below; on the tensor cores the
+    // pass is bound by streaming x and the probabilities.
+    if (n > 0 && logits == nullptr && dim1 % 4 == 0 && ((uintptr_t)x % 16) == 0 && dim2 <= 128) {
+        bool launched = false;
+        const int rc = mggb::dense_tc(out, x, w, n, dim1, dim2, nullptr, mggb::DENSE_TC_SOFTMAX, nullptr, 0, (cudaStream_t)stream, &launched);
+        if (rc != MGGB_OK || launched) return rc;
+    }
     const int J = (dim2 + 31) / 32;
     const int JP = (J + 1) / 2;
     const size_t smem = ((size_t)dim1 * 32 * JP + (size_t)FS_WARPS * FS_ROWS * dim1) * sizeof(float2);

@@ -77,6 +77,7 @@ struct TcParams {
     int K, M, Npad, nchunks, stages, relu, stage_out;
     int tf32;        // 1: one TF32 pass (hi * hi only); the lo halves are neither written nor multiplied
     int vec_store;   // 1: dim2 % 4 == 0 and out and every publish destination are 16-byte aligned (128-bit stores)
+    int softmax;     // 1: the epilogue stores softmax(row) instead of the row (needs stage_out; no row scale, no ReLU)
     unsigned tmem_cols;
     Publish pub;
 };
@@ -459,6 +460,14 @@ __device__ void mma_role(const TcParams& P, uint32_t ring_base, uint32_t w_base,
     }
 }
 
+// e^d for d <= 0 as 2^(d * log2 e) on the special-function unit (relative error below 1e-6 * max(1, |d| / 10), flushed to
+// 0 below d = -87): the same exponential as the CUDA-core fused dense + softmax kernel
+__device__ __forceinline__ float exp_neg(float d) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d * 1.4426950408889634f));
+    return r;
+}
+
 __device__ void epilogue_role(const TcParams& P, float* out_stage, uint32_t tfull0, uint32_t tempty0, uint32_t tmem_base,
                               volatile int* abort_flag, long long first_tile, long long tile_step, long long tiles) {
     const int quarter = (threadIdx.x >> 5) & 3;   // a warp may only read tensor-memory lanes 32*(warp%4) ..
@@ -471,8 +480,9 @@ __device__ void epilogue_role(const TcParams& P, float* out_stage, uint32_t tful
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const long long row = tile * TILE_M + quarter * 32 + lane;
         const float scale = (P.row_scale && row < P.n) ? P.row_scale[row] : 1.f;
-        for (int c0 = 0; c0 < P.Npad; c0 += 16) {
-            // columns c0.. of the accumulator hold x * w_hi, columns Npad + c0.. hold x * w_lo: the product is their sum
+        // 16 columns c0.. of this thread's row: columns c0.. of the accumulator hold x * w_hi, columns Npad + c0.. hold
+        // x * w_lo, and the product is their sum
+        auto load_chunk = [&](int c0, float (&v)[16]) {
             uint32_t r[16], q[16];
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * 2 * P.Npad + c0);
             asm volatile(
@@ -488,15 +498,42 @@ __device__ void epilogue_role(const TcParams& P, float* out_stage, uint32_t tful
                     : "r"(taddr + (uint32_t)P.Npad));
             }
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (!P.tf32) {
 #pragma unroll
-                for (int j = 0; j < 16; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(q[j]));
+            for (int j = 0; j < 16; j++) v[j] = P.tf32 ? __uint_as_float(r[j]) : __uint_as_float(r[j]) + __uint_as_float(q[j]);
+        };
+        if (P.softmax) {
+            // Each thread owns a whole row of the accumulator, so the row's maximum and its sum of exponentials need no
+            // exchange between threads: one pass over tensor memory for the maximum, a second for exp(v - max), which is
+            // parked in the staging rows together with 1 / sum (in the pitch's spare column) for the coalesced store.
+            float m = -3.402823466e38f;
+            for (int c0 = 0; c0 < P.Npad; c0 += 16) {
+                float v[16];
+                load_chunk(c0, v);
+#pragma unroll
+                for (int j = 0; j < 16; j++)
+                    if (c0 + j < P.M) m = fmaxf(m, v[j]);
             }
+            float sum = 0.f;
+            for (int c0 = 0; c0 < P.Npad; c0 += 16) {
+                float v[16];
+                load_chunk(c0, v);
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const float e = (c0 + j < P.M) ? exp_neg(v[j] - m) : 0.f;
+                    sum += e;
+                    out_stage[lane * (P.Npad + 1) + c0 + j] = e;
+                }
+            }
+            out_stage[lane * (P.Npad + 1) + P.Npad] = 1.f / sum;
+        }
+        for (int c0 = 0; !P.softmax && c0 < P.Npad; c0 += 16) {
+            float acc[16];
+            load_chunk(c0, acc);
             if (row < P.n) {
                 float v[16];
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
-                    v[j] = __uint_as_float(r[j]) * scale;
+                    v[j] = acc[j] * scale;
                     if (P.relu) v[j] = fmaxf(v[j], 0.f);
                 }
                 const long long o = row * P.M + c0;
@@ -536,14 +573,15 @@ __device__ void epilogue_role(const TcParams& P, float* out_stage, uint32_t tful
                 for (int i = lane * 4; i < total; i += 128) {
                     const int r = (int)(((float)i + 0.5f) * inv_m);
                     const float* src = out_stage + r * (P.Npad + 1) + (i - r * P.M);
-                    const float4 f = make_float4(src[0], src[1], src[2], src[3]);
+                    const float k = P.softmax ? out_stage[r * (P.Npad + 1) + P.Npad] : 1.f;
+                    const float4 f = make_float4(src[0] * k, src[1] * k, src[2] * k, src[3] * k);
                     *reinterpret_cast<float4*>(P.out + o + i) = f;
                     for (int q = 0; q < P.pub.n; q++) *reinterpret_cast<float4*>(P.pub.dst[q] + o + i) = f;
                 }
             } else {
                 for (int i = lane; i < total; i += 32) {
                     const int r = (int)(((float)i + 0.5f) * inv_m);
-                    const float f = out_stage[r * (P.Npad + 1) + (i - r * P.M)];
+                    const float f = out_stage[r * (P.Npad + 1) + (i - r * P.M)] * (P.softmax ? out_stage[r * (P.Npad + 1) + P.Npad] : 1.f);
                     P.out[o + i] = f;
                     for (int q = 0; q < P.pub.n; q++) P.pub.dst[q][o + i] = f;
                 }
@@ -673,10 +711,14 @@ int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, in
     const size_t w_bytes = 2 * (size_t)nchunks * Npad * 128;
     const size_t budget = 225 * 1024;                                      // of the 227 KiB a CTA may use
     // coalescing buffer: for odd widths, and whenever rows are also published to peers
-    const size_t out_stage_bytes = (dim2 % 4 != 0 || num_publish > 0) ? (size_t)4 * 32 * (Npad + 1) * sizeof(float) : 0;
+    const bool softmax = (flags & DENSE_TC_SOFTMAX) != 0;   // internal: the fused last layer
+    const size_t out_stage_bytes = (dim2 % 4 != 0 || num_publish > 0 || softmax) ? (size_t)4 * 32 * (Npad + 1) * sizeof(float) : 0;
     size_t fixed = w_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + out_stage_bytes;
     bool stage_out = out_stage_bytes != 0;
-    if (stage_out && fixed + 2 * STAGE_BYTES > budget) { fixed -= out_stage_bytes; stage_out = false; }   // no room: strided stores
+    if (stage_out && fixed + 2 * STAGE_BYTES > budget) {
+        if (softmax) return MGGB_OK;     // the softmax epilogue needs the staging rows
+        fixed -= out_stage_bytes; stage_out = false;   // no room: strided stores
+    }
     if (fixed + 2 * STAGE_BYTES > budget) return MGGB_OK;                  // needs at least a 2-stage ring
     const int stages = (int)std::min<size_t>(MAX_STAGES, (budget - fixed) / STAGE_BYTES);
     unsigned tmem_cols = 32;
@@ -689,6 +731,7 @@ int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, in
     P.relu = (flags & MGGB_DENSE_RELU) ? 1 : 0;
     P.tf32 = (flags & MGGB_DENSE_TF32) ? 1 : 0;
     P.stage_out = stage_out ? 1 : 0;
+    P.softmax = softmax ? 1 : 0;
     // 128-bit stores need 16-byte aligned destinations (a view that starts at an odd float offset is
     // not); otherwise the epilogue stores float by float.
     bool vec_store = (dim2 % 4 == 0) && ((uintptr_t)out % 16 == 0);
