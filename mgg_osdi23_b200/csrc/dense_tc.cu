@@ -712,6 +712,8 @@ int dense_tc(float* out, const float* x, const float* w, int64_t n, int dim1, in
     const size_t budget = 225 * 1024;                                      // of the 227 KiB a CTA may use
     // coalescing buffer: for odd widths, and whenever rows are also published to peers
     const bool softmax = (flags & DENSE_TC_SOFTMAX) != 0;   // internal: the fused last layer
+    // (staging every output, also rows of a multiple of 4 floats that nobody else receives, was measured slower than the
+    // epilogue's strided 16-byte stores: 2,449,029 x 64 -> 64 in 0.41 ms against 0.29 ms)
     const size_t out_stage_bytes = (dim2 % 4 != 0 || num_publish > 0 || softmax) ? (size_t)4 * 32 * (Npad + 1) * sizeof(float) : 0;
     size_t fixed = w_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + out_stage_bytes;
     bool stage_out = out_stage_bytes != 0;
