@@ -80,6 +80,7 @@ template <> struct Vec<4> {
     }
     __device__ __forceinline__ void store_smem(float* p) const { *reinterpret_cast<float4*>(p) = v; }
     __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }   // 16-byte aligned destination
+    __device__ __forceinline__ float get(int j) const { return j == 0 ? v.x : j == 1 ? v.y : j == 2 ? v.z : v.w; }
 };
 template <> struct Vec<1> {
     float v;
@@ -89,7 +90,47 @@ template <> struct Vec<1> {
     __device__ __forceinline__ void xor_reduce(int off) { v += __shfl_xor_sync(0xffffffffu, v, off); }
     __device__ __forceinline__ void store_smem(float* p) const { *p = v; }
     __device__ __forceinline__ void store(float* p) const { *p = v; }
+    __device__ __forceinline__ float get(int) const { return v; }
 };
+
+// Adds up the 32/LPR sub-warps' partial rows (each lane holds VEC columns of its sub-warp's sum).  A plain butterfly
+// would shuffle all VEC values at every one of its log2(32/LPR) steps; here a lane sends, at each step, the half of its
+// values that its partner keeps and keeps the other half, until one value is left (then the steps are plain
+// exchanges): VEC - 1 + (steps beyond log2 VEC) shuffles instead of VEC * steps (4 instead of 12 at 16 columns).
+// On return out[0 .. n) are final sums of columns first .. first+n-1 of the lane's VEC columns, and `owner` says whether
+// this lane is the one that should store them (lanes that differ only in the plain-exchange bits hold copies).
+template <int LPR, int VEC>
+struct Folded { float out[VEC]; int first; int n; bool owner; };
+
+template <int LPR, int VEC>
+__device__ __forceinline__ Folded<LPR, VEC> fold_subwarps(const Vec<VEC>& acc, int lane) {
+    Folded<LPR, VEC> f;
+#pragma unroll
+    for (int j = 0; j < VEC; j++) f.out[j] = acc.get(j);
+    f.first = 0; f.n = VEC; f.owner = true;
+    int n = VEC;
+#pragma unroll
+    for (int off = 16; off >= LPR; off >>= 1) {
+        const bool up = (lane & off) != 0;
+        if (n > 1) {
+            n >>= 1;
+#pragma unroll
+            for (int j = 0; j < VEC / 2; j++) {
+                if (j < n) {
+                    const float keep = up ? f.out[j + n] : f.out[j];
+                    const float send = up ? f.out[j] : f.out[j + n];
+                    f.out[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+            }
+            f.first += up ? n : 0;
+        } else {
+            f.out[0] += __shfl_xor_sync(0xffffffffu, f.out[0], off);
+            f.owner = f.owner && !up;
+        }
+    }
+    f.n = n;
+    return f;
+}
 
 // Adds the rows of up to 32 neighbors (ids held one per lane in `my`, -1 = none) into acc.
 // FULL: all 32 ids are valid, so no per-row predicate is needed.
