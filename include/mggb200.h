@@ -57,6 +57,11 @@ enum {
                                 rate for reads of that size), and local rows come 3.7x slower than through the
                                 load/store unit, because an SM's copy engine keeps only about a hundred row copies
                                 in flight.  Kept as an option for other row widths and machines */
+    MGGB_AGG_NO_REMOTE = 64,  /* the remote lists are not read: every neighbor of every row is in its LOCAL list (global ids)
+                                 and peer_input[pe] - lb * dim addresses row 0 of one matrix that holds every PE's rows
+                                 (a local replica: peer_input[p] = base + p * node_per_pe * dim).  This is how the
+                                 aggregation is called in push mode with merged lists; it then runs the single-PE kernel,
+                                 12 % faster per edge than the kernel that also walks (empty) remote lists */
     MGGB_AGG_GIN_COMBINE = 32, /* mggb_sag_np_part only: out = (1+eps) * x_self + sum, as mggb_gin_np_div computes */
     MGGB_AGG_GROUP_PER_NODE = 4 /* dim 16 only (ignored otherwise): a node is aggregated by one group of 4 lanes,
                                  8 nodes per warp, instead of by warp_per_block warps; part_size and

@@ -12,7 +12,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libmggb200.so")
 
 OK, ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_PEER, ERR_IO = range(6)
-AGG_ACCUMULATE, AGG_NO_HUB_SPLIT, AGG_GROUP_PER_NODE, AGG_STAGE_ROWS, AGG_GIN_COMBINE = 1, 2, 4, 8, 32
+AGG_ACCUMULATE, AGG_NO_HUB_SPLIT, AGG_GROUP_PER_NODE, AGG_STAGE_ROWS, AGG_GIN_COMBINE, AGG_NO_REMOTE = 1, 2, 4, 8, 32, 64
 DENSE_RELU, DENSE_TF32, DENSE_SIMT, DENSE_TENSOR = 1, 2, 4, 8
 MAX_PES = 16
 

@@ -364,7 +364,7 @@ int launch_hub_for(const AggParams& P, int remote_mode, cudaStream_t st) {
 
 // 0 = one PE; 2 = the PEs' buffers are consecutive slots of one matrix (a local replica); 1 = buffers anywhere.
 int remote_mode_of(const AggParams& P) {
-    if (P.num_pes == 1) return 0;
+    if (P.num_pes == 1 || P.no_remote) return 0;
     bool one_matrix = true;   // peer[p] == peer[0] + p * node_per_pe * dim for every p
     for (int p = 1; p < P.num_pes; p++)
         one_matrix = one_matrix && (P.peer[p] == P.peer[0] + (long long)p * P.node_per_pe * P.dim);
@@ -507,6 +507,7 @@ int aggregate(float* output, const float* const* peer_input, int num_pes, const 
         P.num_rows = (int32_t)row_count;
     }
     P.dim = dim; P.pe = pe; P.num_pes = num_pes;
+    P.no_remote = (flags & MGGB_AGG_NO_REMOTE) ? 1 : 0;
     P.chunk = (int)std::min<long long>((long long)ps * dist, 1 << 24);  // larger than any useful chunk: same walk
     make_divider((uint32_t)node_per_pe, &P.div_magic, &P.div_shift);
     P.mode = mode; P.self_scale = self_scale;

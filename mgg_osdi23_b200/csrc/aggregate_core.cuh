@@ -44,6 +44,7 @@ struct AggParams {
     int dim;
     int pe;
     int num_pes;
+    int no_remote;         // 1: the remote lists are not read (every neighbor is in the local list, one matrix holds all rows)
     int chunk;             // dist * ps: neighbors a warp takes per turn
     unsigned long long div_magic;  // owner = (id * div_magic) >> div_shift
     int div_shift;

@@ -213,18 +213,25 @@ class Shard:
             self._flag_cache[key] = knobs.flags | (_lib.AGG_NO_HUB_SPLIT if (thr < 0 or self.max_degree <= thr) else 0)
         return self._flag_cache[key]
 
+    def _flags_for(self, lists, knobs: Knobs, dim: int) -> int:
+        # merged lists (a replica is gathered from): nothing is left in the remote half, the single-PE kernel does
+        merged = self._merged is not None and lists is self._merged
+        return self.agg_flags(knobs, dim) | (_lib.AGG_NO_REMOTE if merged else 0)
+
     def aggregate(self, out, sym, dim, knobs: Knobs, accumulate=False, row_scale_=None, publish=None, rows=None):
         """``rows``: a row list from :meth:`row_blocks` (only those rows are computed); None = the whole shard."""
+        lists = self._lists_for(sym)
         self._timed(lambda: api.mgg_SAG_np_div(
-            out, sym, *self._lists_for(sym), self.lb, self.ub, dim, self.node_per_pe, self.pe,
+            out, sym, *lists, self.lb, self.ub, dim, self.node_per_pe, self.pe,
             knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, accumulate=accumulate, row_scale_=row_scale_,
-            publish=publish, row_order=self.row_order, rows=rows, flags=self.agg_flags(knobs, dim)))
+            publish=publish, row_order=self.row_order, rows=rows, flags=self._flags_for(lists, knobs, dim)))
 
     def aggregate_gin(self, out, sym, dim, knobs: Knobs, eps: float, rows=None):
+        lists = self._lists_for(sym)
         self._timed(lambda: api.mgg_GIN_np_div(
-            out, sym, *self._lists_for(sym), self.lb, self.ub, dim, self.node_per_pe, self.pe,
+            out, sym, *lists, self.lb, self.ub, dim, self.node_per_pe, self.pe,
             knobs.partSize, knobs.warpPerBlock, knobs.interleaved_dist, eps, row_order=self.row_order, rows=rows,
-            flags=self.agg_flags(knobs, dim)))
+            flags=self._flags_for(lists, knobs, dim)))
 
 
 def nccl_stream_barrier(group=None) -> Callable[[], None]:

@@ -223,6 +223,39 @@ def test_giant_rows_are_cut_into_segments(oracle, dim, G, knobs):
         np.testing.assert_allclose(emulated_aggregate(rp, col, x, G, knobs=knobs, flags=_lib.AGG_GROUP_PER_NODE), want, rtol=RTOL, atol=ATOL)
 
 
+@pytest.mark.parametrize("dim,knobs,flags", [(16, (32, 4, 2), 0), (16, (16, 1, 1), 4), (64, (16, 1, 2), 0), (7, (8, 2, 1), 0)])
+def test_no_remote_flag_runs_the_single_pe_kernel_on_merged_lists(oracle, dim, knobs, flags):
+    """MGGB_AGG_NO_REMOTE (what a shard passes when it gathers from a replica through merged lists): the remote
+    lists are not read, and the sums are the bits of the call without the flag, for SAG and GIN, hub rows included."""
+    from mgg_osdi23_b200 import _lib
+    n, G, pe = 3000, 3, 1
+    rp, col = random_graph(n, 25, seed=61, hubs=[(1000, 40_000), (1500, 17_000), (1999, 1500)])
+    x = np.random.default_rng(62).uniform(-0.02, 0.02, (n, dim)).astype(np.float32)
+    dev = torch.device("cuda")
+    npp = (n + G - 1) // G
+    reps = drivers.local_replicas(G, npp, dim, dev)
+    for r in reps:
+        r.tensor[: n * dim].copy_(torch.from_numpy(x).to(dev).reshape(-1))
+    sh = drivers.Shard(rp, col, pe, G, device=dev)
+    kn = drivers.Knobs(*knobs, flags=flags)
+    lists = sh.merged_lists()
+    assert sh._lists_for(reps[pe]) is lists and sh._flags_for(lists, kn, dim) & _lib.AGG_NO_REMOTE
+    want = oracle.sag_f64(x, rp, col)[sh.lb:sh.ub]
+    a, b = torch.zeros(sh.rows, dim, device=dev), torch.zeros(sh.rows, dim, device=dev)
+    sh.aggregate(a, reps[pe], dim, kn)                                               # with the flag
+    mgg.mgg_SAG_np_div(b, reps[pe], *lists, sh.lb, sh.ub, dim, sh.node_per_pe, pe, *knobs,
+                       accumulate=False, row_order=sh.row_order, flags=sh.agg_flags(kn, dim))   # without it
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(a.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+    assert torch.equal(a, b)
+    sh.aggregate_gin(a, reps[pe], dim, kn, 0.5)
+    mgg.mgg_GIN_np_div(b, reps[pe], *lists, sh.lb, sh.ub, dim, sh.node_per_pe, pe, *knobs, 0.5,
+                       row_order=sh.row_order, flags=sh.agg_flags(kn, dim))
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(a.cpu().numpy(), want + 1.5 * x[sh.lb:sh.ub], rtol=RTOL, atol=ATOL)
+    assert torch.equal(a, b)
+
+
 def test_row_order_changes_schedule_not_results():
     """Blocks taking rows longest-first (or in any permutation) give bit-identical sums."""
     dev = torch.device("cuda")
