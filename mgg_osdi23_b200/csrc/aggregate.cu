@@ -29,7 +29,9 @@
 // B200: narrow rows (dim <= 16) are served mostly from L2 and want many resident warps, so registers
 // are capped (3 blocks of 512 threads -> 40 registers); wide rows stream from HBM, run one batch
 // per node on typical graphs, and do better without the cap.
-//   MGGB_AGG_MIN_BLOCKS_NARROW  second argument of __launch_bounds__(512, .) for LPR <= 4
+//   MGGB_AGG_MIN_BLOCKS_NARROW  second argument of __launch_bounds__(512, .) for LPR <= 4.  Measured on 115 M 64-byte
+//   rows (232,965 nodes): 2 (64 registers, 32 warps per SM) 0.783 ms; 3 (40 registers, 48 warps) 0.655 ms;
+//   4 (32 registers, 64 warps) 0.685 ms.
 #ifndef MGGB_AGG_MIN_BLOCKS_NARROW
 #define MGGB_AGG_MIN_BLOCKS_NARROW 3
 #endif
