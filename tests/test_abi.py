@@ -22,6 +22,19 @@ def test_header_symbols_are_exported():
     assert set(SIGNATURES) | {"mggb_version", "mggb_last_error"} == set(names)
 
 
+def test_flag_constants_match_the_header():
+    """The Python constants are the header's enumerators (a mismatch would silently select another kernel)."""
+    from mgg_osdi23_b200 import _lib
+    text = open(os.path.join(ROOT, "include", "mggb200.h")).read()
+    enums = {m.group(1): int(m.group(2)) for m in re.finditer(r"\b(MGGB_[A-Z0-9_]+)\s*=\s*(-?\d+)", text)}
+    for name in ("AGG_ACCUMULATE", "AGG_NO_HUB_SPLIT", "AGG_GROUP_PER_NODE", "AGG_STAGE_ROWS", "AGG_GIN_COMBINE", "AGG_NO_REMOTE",
+                 "DENSE_RELU", "DENSE_TF32", "DENSE_SIMT", "DENSE_TENSOR"):
+        assert "MGGB_" + name in enums, name
+        assert getattr(_lib, name) == enums["MGGB_" + name], name
+    flags = [enums[k] for k in enums if k.startswith("MGGB_AGG_")]
+    assert len(set(flags)) == len(flags) and all(f & (f - 1) == 0 for f in flags)      # distinct single bits
+
+
 def test_version_and_error_string():
     from mgg_osdi23_b200._lib import lib
     assert lib.mggb_version() >= 100
