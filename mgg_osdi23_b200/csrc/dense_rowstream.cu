@@ -87,12 +87,15 @@ __device__ __forceinline__ void fold(float (&a)[RS_COLS * 8], int lane, int mask
 // k = (i*32 + l)*VEC + e (zeros past K or M).  Ends with a block barrier.
 template <int VEC>
 __device__ __forceinline__ void stage_w(float4* Wt, const float* __restrict__ w, int K, int M, int steps) {
+    const bool vec_w = (M == RS_COLS) && ((uintptr_t)w % 16 == 0);
     for (int idx = threadIdx.x; idx < steps * VEC * 4 * 32; idx += RS_THREADS) {
         const int l = idx & 31, g = (idx >> 5) & 3, ie = idx >> 7;
         const int i = ie / VEC, e = ie - i * VEC;
         const int k = (i * 32 + l) * VEC + e;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (k < K) {
+        if (k < K && vec_w) {
+            v = __ldg(reinterpret_cast<const float4*>(w + (long long)k * RS_COLS) + g);   // full-width w, 16-byte aligned
+        } else if (k < K) {
             const float* src = w + (long long)k * M + 4 * g;
             if (4 * g + 0 < M) v.x = __ldg(src + 0);
             if (4 * g + 1 < M) v.y = __ldg(src + 1);
